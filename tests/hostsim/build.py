@@ -1,0 +1,43 @@
+"""Builds and loads the test-only single-lane host build of the threshold code."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SO = os.path.join(HERE, "libsdcab_hostsim.so")
+CSRC = os.path.join(HERE, "..", "..", "libsdca_b200", "csrc")
+
+
+def build():
+    deps = [os.path.join(HERE, "hostsim.cpp")] + [
+        os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    if os.path.exists(SO) and all(os.path.getmtime(d) <= os.path.getmtime(SO) for d in deps):
+        return SO
+    subprocess.run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-x", "c++",
+                    os.path.join(HERE, "hostsim.cpp"), "-o", SO], check=True)
+    return SO
+
+
+class HostSim:
+    def __init__(self):
+        self.lib = C.CDLL(build())
+
+    def run(self, name, a, precision="double", **kw):
+        """Returns (prox output, thresholds structured array)."""
+        from libsdca_b200.binding import THR_DTYPE, make_opts
+        a = np.array(a, order="C", copy=True)
+        n, m = a.shape
+        o = make_opts(precision=precision, **kw)
+        two = name.startswith("two_")
+        thr = np.zeros(2 * n if two else n, dtype=THR_DTYPE)
+        rc = self.lib.sdcab_hostsim_prox(
+            name.encode(), 0 if a.dtype == np.float32 else 1, a.ctypes.data_as(C.c_void_p),
+            C.c_int64(m), C.c_int64(n), C.byref(o), thr.ctypes.data_as(C.c_void_p), 1)
+        assert rc == 0, rc
+        return a, thr
+
+
+def load():
+    return HostSim()

@@ -1,0 +1,48 @@
+"""Threshold logic of the CUDA sources, compiled for the host with one lane per
+row (tests/hostsim), against the reference on the regimes of its own tests.
+This checks the algorithms; the warp plumbing is covered by the gpu tests."""
+import numpy as np
+import pytest
+
+from tests.util import PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree
+
+
+@pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex"])
+@pytest.mark.parametrize("dtype,precision", [(np.float64, "double"), (np.float32, "double"),
+                                              (np.float32, "float")])
+def test_matches_reference(ref, hostsim, name, dtype, precision):
+    rng = np.random.default_rng(abs(hash((name, str(dtype), precision))) % (2 ** 31))
+    for kind in ("normal", "pos", "neg", "mixed", "ties"):
+        for m in (1, 2, 3, 5, 33, 200):
+            if name == "two_simplex" and m < 2:
+                continue
+            a = regime(rng, 24, m, dtype, kind)
+            kw = random_opts(rng, name, m)
+            x_ref = ref.prox(name, a, result=precision, **kw)
+            x, _ = hostsim.run(name, a, precision=precision, **kw)
+            err = scaled_error(x, x_ref, a).max()
+            assert err <= tolerance(dtype, precision, m), (name, kind, m, kw, err)
+
+
+@pytest.mark.parametrize("name,kw,cols", [
+    ("topk_simplex", dict(k=5, rhs=1.0), 1000), ("topk_cone", dict(k=5), 1000),
+    ("knapsack_eq", dict(), 100), ("topk_entropy", dict(k=10), 200),
+    ("entropy", dict(hi=0.1), 200)])
+def test_thresholds_and_sets(ref, hostsim, name, kw, cols):
+    rng = np.random.default_rng(17)
+    for dtype in (np.float32, np.float64):
+        a = regime(rng, 64, cols, dtype, "ties")
+        x, thr = hostsim.run(name, a, **kw)
+        rt = ref.thresholds(name, a, **kw)
+        x_ref = ref.prox(name, a, **kw)
+        tol = tolerance(dtype, "double", cols)
+        assert scaled_error(x, x_ref, a).max() <= tol
+        thresholds_agree(thr, rt, x, x_ref, a, tol)
+
+
+def test_lambert(ref, hostsim):
+    for dtype in (np.float32, np.float64):
+        x = np.linspace(-120, 120, 4001).astype(dtype).reshape(1, -1)
+        y, _ = hostsim.run("lambert_w_exp", x)
+        y_ref = ref.prox("lambert_w_exp", x)
+        assert np.array_equal(y, y_ref)

@@ -1,0 +1,119 @@
+"""Parity of the CUDA prox kernels (through the C ABI) with the reference."""
+import numpy as np
+import pytest
+
+from tests.util import PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree
+
+pytestmark = pytest.mark.gpu
+
+
+def run_dev(mod, name, a, **kw):
+    import torch
+    t = torch.from_numpy(a).cuda()
+    mod.prox_(t, name, **kw)
+    torch.cuda.synchronize()
+    return t.cpu().numpy()
+
+
+@pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex"])
+@pytest.mark.parametrize("dtype,precision", [(np.float64, "double"), (np.float32, "double"),
+                                              (np.float32, "float")])
+def test_regimes_match_reference(ref, cuda_lib, name, dtype, precision):
+    rng = np.random.default_rng(abs(hash((name, str(dtype), precision, 1))) % (2 ** 31))
+    for kind in ("normal", "pos", "neg", "mixed", "ties"):
+        for m in (1, 2, 3, 5, 31, 32, 33, 200, 1023, 1024, 1025):
+            if name == "two_simplex" and m < 2:
+                continue
+            n = 37 if m < 1000 else 9
+            a = regime(rng, n, m, dtype, kind)
+            kw = random_opts(rng, name, m)
+            x_ref = ref.prox(name, a, result=precision, **kw)
+            x = run_dev(cuda_lib, name, a, precision=precision, **kw)
+            err = scaled_error(x, x_ref, a).max()
+            assert err <= tolerance(dtype, precision, m), (name, kind, m, kw, err)
+
+
+def test_config1_simplex_f64(ref, cuda_lib):
+    from libsdca_b200 import synth
+    a = synth.simplex_rows(rows=8192)
+    x = run_dev(cuda_lib, "knapsack", a)
+    x_ref = ref.prox("knapsack", a)
+    assert scaled_error(x, x_ref, a).max() <= 1e-12
+    assert np.abs(x.sum(axis=1) - 1).max() < 1e-12
+
+
+@pytest.mark.parametrize("name,kw", [("topk_simplex", dict(k=5, rhs=1.0)), ("topk_cone", dict(k=5))])
+@pytest.mark.parametrize("precision", ["double", "float"])
+def test_config2_topk_f32_with_ties(ref, cuda_lib, name, kw, precision):
+    import torch
+    from libsdca_b200 import synth
+    a = synth.topk_rows(rows=4096)
+    x = run_dev(cuda_lib, name, a, precision=precision, **kw)
+    x_ref = ref.prox(name, a, result=precision, **kw)
+    tol = tolerance(np.float32, precision, 1000)
+    assert scaled_error(x, x_ref, a).max() <= tol
+    # identical index sets of the entries at the upper bound and in the middle
+    thr = cuda_lib.thresholds(torch.from_numpy(a).cuda(), name, precision=precision, **kw)
+    rt = ref.thresholds(name, a, result=precision, **kw)
+    differ = thresholds_agree(thr, rt, x, x_ref, a, tol)
+    if precision == "double":
+        hi = x_ref.max(axis=1, keepdims=True)
+        assert np.array_equal(x == x.max(axis=1, keepdims=True), x_ref == hi)
+        assert np.array_equal(x > 0, x_ref > 0)
+        assert differ <= len(a) // 50
+
+
+@pytest.mark.parametrize("name,kw", [("topk_entropy", dict(k=1)), ("topk_entropy", dict(k=10)),
+                                     ("entropy", dict(hi=1.0, rhs=1.0)),
+                                     ("entropy_norm", dict(hi=1.0, rhs=1.0)),
+                                     ("topk_entropy_biased", dict(k=10, alpha=1.0))])
+def test_config3_entropy_f32(ref, cuda_lib, name, kw):
+    from libsdca_b200 import synth
+    rows = 4096 if "biased" not in name and "norm" not in name else 512
+    a = synth.entropy_rows(rows=rows)
+    x = run_dev(cuda_lib, name, a, **kw)
+    x_ref = ref.prox(name, a, **kw)
+    assert scaled_error(x, x_ref, a).max() <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_config3_lambert(ref, cuda_lib, dtype):
+    import torch
+    from libsdca_b200 import synth
+    x = synth.lambert_inputs(count=200 * 4096 + 3, dtype=dtype)
+    assert x[0] == -30 and x[1] == 30
+    t = torch.from_numpy(x.copy()).cuda()
+    cuda_lib.lambert_w_exp_(t)
+    y = t.cpu().numpy()
+    y_ref = ref.prox("lambert_w_exp", x.reshape(1, -1)).ravel()
+    tol = 1e-5 if dtype == np.float32 else 1e-12
+    assert (np.abs(y - y_ref) <= tol * np.maximum(1, np.abs(y_ref))).all()
+    # known answers of the reference's tests: W(exp(0)) = Omega; residuals
+    z = torch.zeros(4, dtype=t.dtype, device="cuda")
+    cuda_lib.lambert_w_exp_(z)
+    assert abs(float(z[0]) - 0.5671432904097838) <= np.finfo(dtype).eps
+    pos = x > 0
+    w = y[pos].astype(np.float64)
+    assert (np.abs(x[pos] - (w + np.log(w))) < 8 * np.finfo(dtype).eps * np.maximum(1, x[pos])).all()
+
+
+def test_host_buffer_entry_point_matches_device_path(ref, cuda_lib):
+    from libsdca_b200 import synth
+    a = synth.topk_rows(rows=3000)
+    x_host = cuda_lib.prox(a, "topk_simplex", k=5)
+    x_dev = run_dev(cuda_lib, "topk_simplex", a, k=5)
+    assert np.array_equal(x_host, x_dev)
+    thr = cuda_lib.thresholds(a, "topk_simplex", k=5)
+    assert len(thr) == 3000 and (thr["hi"] > 0).all()
+
+
+def test_edge_shapes(ref, cuda_lib):
+    rng = np.random.default_rng(3)
+    # a single row, a single column, an odd number of rows, a row longer than
+    # what fits in shared memory (read straight from global memory)
+    for n, m in [(1, 7), (5, 1), (3, 70001)]:
+        a = rng.standard_normal((n, m)).astype(np.float32)
+        x = run_dev(cuda_lib, "knapsack", a)
+        assert scaled_error(x, ref.prox("knapsack", a), a).max() <= 1e-5
+        x = run_dev(cuda_lib, "topk_cone", a, k=1)
+        assert scaled_error(x, ref.prox("topk_cone", a, k=1), a).max() <= 1e-5

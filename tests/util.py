@@ -1,0 +1,98 @@
+"""Shared helpers of the parity tests: input regimes and the tolerance metric.
+
+Tolerance (stated once, used everywhere): an output element may differ from
+the reference by at most tol * max(1, max|a_row|), tol = 1e-12 for float64 data
+and 1e-5 for float32 data when thresholds are computed in double (the
+reference's default).  When the caller asks for float thresholds the float
+accumulation over m terms is part of both results, so the bound is widened to
+4 * m * FLT_EPSILON.
+"""
+import numpy as np
+
+PROX_SINGLE = ["knapsack_eq", "knapsack_le", "knapsack_le_biased", "topk_simplex",
+               "topk_simplex_biased", "topk_cone", "topk_cone_biased", "entropy",
+               "entropy_norm", "topk_entropy", "topk_entropy_biased"]
+
+
+def tolerance(dtype, precision, m):
+    tol = 1e-5 if np.dtype(dtype) == np.float32 else 1e-12
+    if precision != "double":
+        tol = max(tol, 4 * m * float(np.finfo(np.float32).eps))
+    return tol
+
+
+def scaled_error(x, x_ref, a):
+    scale = np.maximum(1.0, np.abs(a.astype(np.float64)).max(axis=1, keepdims=True))
+    return np.abs(x.astype(np.float64) - x_ref.astype(np.float64)) / scale
+
+
+def regime(rng, n, m, dtype, kind):
+    """Input regimes of the reference's prox tests (test/prox/*.cpp): all
+    positive, all negative, mixed across decades, plus rows with repeated values."""
+    if kind == "normal":
+        a = rng.standard_normal((n, m))
+    elif kind == "pos":
+        a = rng.uniform(0, 1, (n, m)) * 10.0 ** rng.integers(-3, 3, (n, 1))
+    elif kind == "neg":
+        a = -rng.uniform(0, 1, (n, m)) * 10.0 ** rng.integers(-3, 3, (n, 1))
+    elif kind == "mixed":
+        a = rng.standard_normal((n, m)) * 10.0 ** rng.integers(-3, 3, (n, 1))
+    elif kind == "ties":
+        a = rng.standard_normal((n, m))
+        for r in range(n):
+            for _ in range(3):
+                idx = rng.choice(m, size=min(m, int(rng.integers(3, 11))), replace=False)
+                a[r, idx] = a[r, idx[0]]
+            top = np.argsort(-a[r])[:min(m, 4)]
+            a[r, top[1:]] = a[r, top[0]]
+    else:
+        raise ValueError(kind)
+    return a.astype(dtype)
+
+
+def random_opts(rng, name, m):
+    k = int(rng.integers(1, min(m, 10) + 1))
+    rhs = float(rng.uniform(0.01, 10))
+    rho = float(rng.uniform(0, 2))
+    alpha = float(rng.uniform(0.01, 2))
+    hi = float(rng.uniform(0.05, 2))
+    lo = float(rng.uniform(-1, 0)) if rng.random() < 0.5 else 0.0
+    if name in ("knapsack_eq", "knapsack_le"):
+        kw = dict(lo=lo, hi=max(hi, lo + 0.1), rhs=rhs)
+        if name == "knapsack_eq" and not (kw["lo"] * m <= rhs <= kw["hi"] * m):
+            kw["rhs"] = float(0.5 * (kw["lo"] + kw["hi"]) * m)
+        return kw
+    if name == "knapsack_le_biased":
+        return dict(lo=lo, hi=max(hi, lo + 0.1), rhs=rhs, rho=rho)
+    if name == "topk_simplex":
+        return dict(k=k, rhs=rhs)
+    if name == "topk_simplex_biased":
+        return dict(k=k, rhs=rhs, rho=rho)
+    if name == "topk_cone":
+        return dict(k=k)
+    if name == "topk_cone_biased":
+        return dict(k=k, rho=rho)
+    if name in ("entropy", "entropy_norm"):
+        return dict(hi=hi, rhs=min(rhs, hi * m * 0.9))
+    if name == "topk_entropy":
+        return dict(k=k)
+    if name == "topk_entropy_biased":
+        return dict(k=k, alpha=alpha)
+    if name == "two_simplex":
+        return dict(p=int(rng.integers(1, m)), rhs=rhs)
+    return {}
+
+
+def thresholds_agree(thr, ref_thr, x, x_ref, a, tol):
+    """Thresholds must agree wherever the reference's solution is not degenerate;
+    rows whose set sizes differ must still produce the same outputs (equal
+    entries at a set boundary can sit on either side).  Returns the number of
+    rows whose sets differ."""
+    t, hi = thr["t"], thr["hi"]
+    same_sets = (thr["num_hi"] == ref_thr["num_hi"]) & (thr["num_mid"] == ref_thr["num_mid"])
+    nondeg = same_sets & (ref_thr["num_mid"] > 0)
+    dt = np.abs(t - ref_thr["t"]) / np.maximum(1, np.abs(ref_thr["t"]))
+    dh = np.abs(hi - ref_thr["hi"]) / np.maximum(1, np.abs(ref_thr["hi"]))
+    assert (dt[nondeg] <= tol).all(), "t mismatch %g" % dt[nondeg].max()
+    assert (dh[same_sets] <= tol).all(), "hi mismatch %g" % dh[same_sets].max()
+    return int((~same_sets).sum())
