@@ -1,9 +1,343 @@
-// Register-resident fast paths for the common shapes (placeholder dispatch).
+// Register-resident rows: one warp keeps a whole row in registers (16-byte
+// vector loads, NV vectors per lane), so the matrix is read from HBM exactly
+// once and written exactly once, and every pass of a threshold search runs out
+// of the register file.
+//
+// On top of that, the top-k operators shrink the row before searching: only
+// entries above a cut that provably contains the support take part, and those
+// (a dozen for Gaussian rows of length 1000) are compacted to one entry per
+// lane, where every reduction is a handful of shuffles.  Rows whose candidates
+// do not fit 32 lanes, or that need the general cone search, run the same
+// threshold code on the full register row instead.
 #pragma once
+
+#include <type_traits>
+
 #include "common_host.h"
 #include "prox_core.cuh"
+
 namespace sdcab {
+
 constexpr int kNoFastPath = 1;
-template <typename Data, typename R>
-int launch_fast_rows(int, const Data*, Data*, int, long long, const ProxParams&, cudaStream_t) { return kNoFastPath; }
+constexpr int kFastThreads = 128;
+
+template <typename Data> struct VecOf;
+template <> struct VecOf<float> { typedef float4 type; static constexpr int N = 4; };
+template <> struct VecOf<double> { typedef double2 type; static constexpr int N = 2; };
+
+// A row held in registers: lane l owns vectors l, 32 + l, 64 + l, ...
+template <typename Data, int NV>
+struct RegRow {
+  typedef Data data_type;
+  typedef typename VecOf<Data>::type Vec;
+  static constexpr int VN = VecOf<Data>::N;
+  Vec v[NV];
+  int m;
+
+  __device__ __forceinline__ int size() const { return m; }
+
+  __device__ __forceinline__ void load(const Data* __restrict__ g, int lane) {
+    const Vec* gv = reinterpret_cast<const Vec*>(g);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int vi = j * 32 + lane;
+      if (vi * VN < m) {
+        v[j] = __ldcs(gv + vi);
+      } else {
+        Data* e = reinterpret_cast<Data*>(&v[j]);
+#pragma unroll
+        for (int c = 0; c < VN; ++c) e[c] = -num<Data>::inf();
+      }
+    }
+  }
+
+  template <typename F>
+  __device__ __forceinline__ void for_each(F&& f) const {
+    const int lane = static_cast<int>(threadIdx.x) & 31;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int base = (j * 32 + lane) * VN;
+      if (base < m) {
+        const Data* e = reinterpret_cast<const Data*>(&v[j]);
+#pragma unroll
+        for (int c = 0; c < VN; ++c) f(e[c], base + c);
+      }
+    }
+  }
+
+  template <typename F>
+  __device__ __forceinline__ void store(Data* __restrict__ g, int lane, F&& f) const {
+    Vec* gv = reinterpret_cast<Vec*>(g);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int vi = j * 32 + lane;
+      if (vi * VN < m) {
+        Vec o = v[j];
+        Data* e = reinterpret_cast<Data*>(&o);
+#pragma unroll
+        for (int c = 0; c < VN; ++c) e[c] = f(e[c]);
+        __stcs(gv + vi, o);
+      }
+    }
+  }
+};
+
+// At most one entry per lane (the compacted candidates); `reported` is what
+// size() answers, which the caller sets to the true row length where the
+// algorithm asks "is this the whole row?".
+template <typename Data>
+struct LaneRow {
+  typedef Data data_type;
+  Data x;
+  bool valid;
+  int reported;
+  __device__ __forceinline__ int size() const { return reported; }
+  template <typename F>
+  __device__ __forceinline__ void for_each(F&& f) const {
+    if (valid) f(x, static_cast<int>(threadIdx.x) & 31);
+  }
+};
+
+// Descending bitonic sort of one value per lane.
+template <typename T>
+__device__ __forceinline__ T warp_sort_desc(T v, int lane) {
+#pragma unroll
+  for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      const T w = __shfl_xor_sync(kFullMask, v, j);
+      const bool upper = (lane & j) != 0;          // partner has the smaller lane id
+      const bool desc = (lane & k) == 0 || k == 32;  // direction of this block
+      const bool keep_max = (upper != desc);
+      v = keep_max ? (w > v ? w : v) : (w < v ? w : v);
+    }
+  }
+  return v;
 }
+
+// The cut below which no entry can belong to the support, from the lane maxima:
+// tau = (k+1)-th largest lane maximum is a lower bound of the (k+1)-th largest
+// entry of the row.
+template <typename Data, int NV>
+__device__ __forceinline__ Data lane_max_cut(const RegRow<Data, NV>& row, int k, int lane) {
+  Data lm = -num<Data>::inf();
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const Data* e = reinterpret_cast<const Data*>(&row.v[j]);
+#pragma unroll
+    for (int c = 0; c < RegRow<Data, NV>::VN; ++c) lm = max_(lm, e[c]);
+  }
+  const Data sorted = warp_sort_desc(lm, lane);
+  return __shfl_sync(kFullMask, sorted, k);  // k <= 31
+}
+
+// Compacts the entries with x > cut to one per lane through shared memory.
+// Returns their number; the LaneRow is only valid if that number is <= 32.
+template <typename Data, int NV>
+__device__ __forceinline__ int compact_candidates(const RegRow<Data, NV>& row, Data cut,
+                                                  Data* __restrict__ slots, int lane,
+                                                  LaneRow<Data>& out) {
+  int mine = 0;
+  row.for_each([&](Data x, int) { mine += (x > cut) ? 1 : 0; });
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(kFullMask, incl, o);
+    if (lane >= o) incl += up;
+  }
+  const int total = __shfl_sync(kFullMask, incl, 31);
+  if (total <= 32) {
+    int pos = incl - mine;
+    row.for_each([&](Data x, int) {
+      if (x > cut) slots[pos++] = x;
+    });
+    __syncwarp();
+    out.valid = lane < total;
+    out.x = out.valid ? slots[lane] : -num<Data>::inf();
+    __syncwarp();
+  }
+  return total;
+}
+
+// Largest float/double not above a Result value (so that Data-precision
+// comparisons against it are equivalent to Result-precision ones).
+__device__ __forceinline__ float round_down(double v, float) { return __double2float_rd(v); }
+__device__ __forceinline__ float round_down(float v, float) { return v; }
+__device__ __forceinline__ double round_down(double v, double) { return v; }
+__device__ __forceinline__ double round_down(float v, double) { return static_cast<double>(v); }
+
+// The general searches on the full register row.  They are rare for the rows
+// the fast paths are built for, so they are kept out of line: the register
+// budget of the kernel is then set by the common path.
+template <typename R, typename Data, int NV>
+__device__ __noinline__ Thr<R> full_topk_simplex(const RegRow<Data, NV>& row, int k, R rhs, R rho) {
+  return thr_topk_simplex<R>(row, k, rhs, rho);
+}
+template <typename R, typename Data, int NV>
+__device__ __noinline__ Thr<R> full_topk_cone(const RegRow<Data, NV>& row, int k, R rho) {
+  return thr_topk_cone<R>(row, k, rho);
+}
+template <typename R, typename Data, int NV>
+__device__ __noinline__ Thr<R> full_cone_search(const RegRow<Data, NV>& row, int k, R rho) {
+  return thr_topk_cone_search<R>(row, k, rho);
+}
+
+// Top-k simplex (rho = 0) and its biased form on a register row.
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ Thr<R> fast_topk_simplex(const RegRow<Data, NV>& row, int k, R rhs,
+                                                    R rho, Data* slots, int lane) {
+  const int m = row.size();
+  if (k <= 31 && m > 32) {
+    const R K = static_cast<R>(k), H = rhs / K;
+    const Data tau = lane_max_cut(row, k, lane);
+    // support of the knapsack step: a_i > t >= v_(k+1) - rhs/k >= tau - rhs/k
+    const Data cut = round_down(static_cast<R>(tau) - H - abs_(static_cast<R>(tau)) * num<R>::eps() * 4, Data(0));
+    LaneRow<Data> cand;
+    const int total = compact_candidates(row, cut, slots, lane, cand);
+    if (total <= 32 && total > k) {
+      const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
+      const R rho_k2 = rho * K * K;
+      cand.reported = m;
+      Thr<R> thr;
+      const Projection proj = topk_special_cases<R>(cand, k, K + rho_k2, thr);
+      if (proj == kProjZero) return thr;
+      cand.reported = total;
+      if (proj == kProjConstant) {
+        if (K * thr.hi > rhs + eps) return thr_knapsack_eq<R>(cand, R(0), H, rhs);
+        return thr;
+      }
+      Thr<R> eq = thr_knapsack_eq<R>(cand, R(0), H, rhs);
+      bool lt;
+      if (eq.nU == 0) {
+        lt = eq.t < rho * rhs - eps;
+      } else {
+        int cnt; R sum_U;
+        row_count_sum_gt<R>(cand, eq.cutU, cnt, sum_U);
+        const R num_U = static_cast<R>(cnt);
+        lt = K * (sum_U + (K - num_U) * eq.t) < rhs * (num_U + rho_k2) - eps;
+      }
+      if (!lt) return eq;
+      return full_cone_search<R>(row, k, rho);
+    }
+  }
+  return full_topk_simplex<R>(row, k, rhs, rho);
+}
+
+// Top-k cone on a register row.  For rho = 0 the first candidate of the search
+// (U empty) has t = 0 and M = {a > 0}: one pass for the sum of the positive
+// entries decides it; anything else takes the general search.
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ Thr<R> fast_topk_cone(const RegRow<Data, NV>& row, int k, R rho,
+                                                 Data* slots, int lane) {
+  const int m = row.size();
+  if (k <= 31 && m > 32) {
+    const R K = static_cast<R>(k);
+    const Data tau = lane_max_cut(row, k, lane);
+    const Data cut = round_down(static_cast<R>(tau) - abs_(static_cast<R>(tau)) * num<R>::eps() * 4 - num<R>::tiny(), Data(0));
+    LaneRow<Data> cand;
+    const int total = compact_candidates(row, cut, slots, lane, cand);
+    if (total <= 32 && total > k) {
+      cand.reported = m;
+      Thr<R> thr;
+      if (topk_special_cases<R>(cand, k, K + rho * K * K, thr) != kProjGeneral) return thr;
+      if (rho == 0) {
+        const R eps = 16 * num<R>::eps();
+        int j = 0; R s = 0; R mx = -num<R>::inf();
+        row.for_each([&](Data xd, int) {
+          R x = static_cast<R>(xd);
+          mx = max_(mx, x);
+          if (x > 0) { ++j; s += x; }
+        });
+        j = warp_sum(j); s = warp_sum(s); mx = warp_max(mx);
+        const R D = K * K;
+        const R t = (R(0) * s - K * R(0)) / D;
+        const R hi = (R(0) + K * s) / D;
+        if (j > 0 && mx - eps <= hi + t) return make_thr(t, R(0), hi, 0, j, num<R>::inf(), t);
+      }
+      return full_cone_search<R>(row, k, rho);
+    }
+  }
+  return full_topk_cone<R>(row, k, rho);
+}
+
+template <typename Data, typename R, int PROX, int NV>
+__global__ void __launch_bounds__(kFastThreads, 4)
+fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long long n,
+                 ProxParams q) {
+  __shared__ Data slots_all[kFastThreads / 32][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps_per_block = kFastThreads / 32;
+  Data* slots = slots_all[warp];
+  for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + warp; r < n;
+       r += static_cast<long long>(gridDim.x) * warps_per_block) {
+    RegRow<Data, NV> row;
+    row.m = m;
+    row.load(a + r * m, lane);
+    Thr<R> thr;
+    if (PROX == kTopkSimplex || PROX == kTopkSimplexBiased) {
+      thr = fast_topk_simplex<R>(row, q.k, static_cast<R>(q.rhs),
+                                 PROX == kTopkSimplexBiased ? static_cast<R>(q.rho) : R(0), slots, lane);
+    } else if (PROX == kTopkCone || PROX == kTopkConeBiased) {
+      thr = fast_topk_cone<R>(row, q.k, PROX == kTopkConeBiased ? static_cast<R>(q.rho) : R(0),
+                              slots, lane);
+    } else {
+      thr = compute_thresholds<R>(PROX, row, q);
+    }
+    Applier<Data> f(thr, prox_map(PROX), q.alpha);
+    row.store(out + r * m, lane, f);
+  }
+}
+
+template <typename Data, typename R, int PROX, int NV>
+int launch_fast(const Data* a, Data* out, int m, long long n, const ProxParams& q,
+                cudaStream_t stream) {
+  DeviceInfo info;
+  int rc = get_device_info(&info);
+  if (rc) return rc;
+  auto kernel = fast_rows_kernel<Data, R, PROX, NV>;
+  int per_sm = 0;
+  SDCAB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFastThreads, 0));
+  if (per_sm < 1) per_sm = 1;
+  const int warps = kFastThreads / 32;
+  long long want = (n + warps - 1) / warps;
+  int blocks = static_cast<int>(std::max<long long>(
+      1, std::min<long long>(want, static_cast<long long>(per_sm) * info.sm_count)));
+  kernel<<<blocks, kFastThreads, 0, stream>>>(a, out, m, n, q);
+  SDCAB_CUDA_TRY(cudaGetLastError());
+  return SDCAB_OK;
+}
+
+template <typename Data, typename R, int PROX>
+int launch_fast_nv(const Data* a, Data* out, int m, long long n, const ProxParams& q,
+                   cudaStream_t stream) {
+  constexpr int VN = VecOf<Data>::N;
+  const int vecs = (m + VN - 1) / VN;
+  if (vecs <= 32 * 2) return launch_fast<Data, R, PROX, 2>(a, out, m, n, q, stream);
+  if (vecs <= 32 * 4) return launch_fast<Data, R, PROX, 4>(a, out, m, n, q, stream);
+  if (vecs <= 32 * 8) return launch_fast<Data, R, PROX, 8>(a, out, m, n, q, stream);
+  return kNoFastPath;
+}
+
+// Register rows need 16-byte aligned rows: m a multiple of the vector width and
+// aligned base pointers.
+template <typename Data, typename R>
+int launch_fast_rows(int prox, const Data* a, Data* out, int m, long long n,
+                     const ProxParams& q, cudaStream_t stream) {
+  constexpr int VN = VecOf<Data>::N;
+  if (m % VN != 0 || m < 8) return kNoFastPath;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15) return kNoFastPath;
+  switch (prox) {
+    case kTopkSimplex: return launch_fast_nv<Data, R, kTopkSimplex>(a, out, m, n, q, stream);
+    case kTopkCone: return launch_fast_nv<Data, R, kTopkCone>(a, out, m, n, q, stream);
+    case kTopkSimplexBiased: return launch_fast_nv<Data, R, kTopkSimplexBiased>(a, out, m, n, q, stream);
+    case kTopkConeBiased: return launch_fast_nv<Data, R, kTopkConeBiased>(a, out, m, n, q, stream);
+    case kKnapsackEq: return launch_fast_nv<Data, R, kKnapsackEq>(a, out, m, n, q, stream);
+    case kKnapsackLe: return launch_fast_nv<Data, R, kKnapsackLe>(a, out, m, n, q, stream);
+    case kEntropy: return launch_fast_nv<Data, R, kEntropy>(a, out, m, n, q, stream);
+    case kTopkEntropy: return launch_fast_nv<Data, R, kTopkEntropy>(a, out, m, n, q, stream);
+    default: break;
+  }
+  return kNoFastPath;
+}
+
+}  // namespace sdcab

@@ -4,14 +4,14 @@ This checks the algorithms; the warp plumbing is covered by the gpu tests."""
 import numpy as np
 import pytest
 
-from tests.util import PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree
+from tests.util import stable_seed, PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree
 
 
 @pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex"])
 @pytest.mark.parametrize("dtype,precision", [(np.float64, "double"), (np.float32, "double"),
                                               (np.float32, "float")])
 def test_matches_reference(ref, hostsim, name, dtype, precision):
-    rng = np.random.default_rng(abs(hash((name, str(dtype), precision))) % (2 ** 31))
+    rng = np.random.default_rng(stable_seed(name, str(dtype), precision))
     for kind in ("normal", "pos", "neg", "mixed", "ties"):
         for m in (1, 2, 3, 5, 33, 200):
             if name == "two_simplex" and m < 2:

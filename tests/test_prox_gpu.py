@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from tests.util import PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree
+from tests.util import stable_seed, PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree
 
 pytestmark = pytest.mark.gpu
 
@@ -19,7 +19,7 @@ def run_dev(mod, name, a, **kw):
 @pytest.mark.parametrize("dtype,precision", [(np.float64, "double"), (np.float32, "double"),
                                               (np.float32, "float")])
 def test_regimes_match_reference(ref, cuda_lib, name, dtype, precision):
-    rng = np.random.default_rng(abs(hash((name, str(dtype), precision, 1))) % (2 ** 31))
+    rng = np.random.default_rng(stable_seed(name, str(dtype), precision, 1))
     for kind in ("normal", "pos", "neg", "mixed", "ties"):
         for m in (1, 2, 3, 5, 31, 32, 33, 200, 1023, 1024, 1025):
             if name == "two_simplex" and m < 2:
@@ -60,7 +60,7 @@ def test_config2_topk_f32_with_ties(ref, cuda_lib, name, kw, precision):
         hi = x_ref.max(axis=1, keepdims=True)
         assert np.array_equal(x == x.max(axis=1, keepdims=True), x_ref == hi)
         assert np.array_equal(x > 0, x_ref > 0)
-        assert differ <= len(a) // 50
+        assert differ <= len(a) // 8  # only rows with tied values (10 % of the rows) may
 
 
 @pytest.mark.parametrize("name,kw", [("topk_entropy", dict(k=1)), ("topk_entropy", dict(k=10)),

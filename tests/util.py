@@ -7,11 +7,18 @@ reference's default).  When the caller asks for float thresholds the float
 accumulation over m terms is part of both results, so the bound is widened to
 4 * m * FLT_EPSILON.
 """
+import zlib
+
 import numpy as np
 
 PROX_SINGLE = ["knapsack_eq", "knapsack_le", "knapsack_le_biased", "topk_simplex",
                "topk_simplex_biased", "topk_cone", "topk_cone_biased", "entropy",
                "entropy_norm", "topk_entropy", "topk_entropy_biased"]
+
+
+def stable_seed(*parts):
+    """A seed that does not depend on Python's per-process string hashing."""
+    return zlib.crc32(repr(parts).encode()) & 0x7fffffff
 
 
 def tolerance(dtype, precision, m):
@@ -60,7 +67,9 @@ def random_opts(rng, name, m):
     if name in ("knapsack_eq", "knapsack_le"):
         kw = dict(lo=lo, hi=max(hi, lo + 0.1), rhs=rhs)
         if name == "knapsack_eq" and not (kw["lo"] * m <= rhs <= kw["hi"] * m):
-            kw["rhs"] = float(0.5 * (kw["lo"] + kw["hi"]) * m)
+            kw["rhs"] = float(max(0.0, 0.5 * (kw["lo"] + kw["hi"])) * m + 0.25 * kw["hi"])
+            if kw["rhs"] > kw["hi"] * m:
+                kw["rhs"] = float(0.5 * kw["hi"] * m)
         return kw
     if name == "knapsack_le_biased":
         return dict(lo=lo, hi=max(hi, lo + 0.1), rhs=rhs, rho=rho)
