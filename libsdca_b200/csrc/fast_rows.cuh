@@ -166,120 +166,218 @@ __device__ __forceinline__ float round_down(float v, float) { return v; }
 __device__ __forceinline__ double round_down(double v, double) { return v; }
 __device__ __forceinline__ double round_down(float v, double) { return static_cast<double>(v); }
 
-// The general searches on the full register row.  They are rare for the rows
-// the fast paths are built for, so they are kept out of line: the register
-// budget of the kernel is then set by the common path.
-template <typename R, typename Data, int NV>
-__device__ __noinline__ Thr<R> full_topk_simplex(const RegRow<Data, NV>& row, int k, R rhs, R rho) {
-  return thr_topk_simplex<R>(row, k, rhs, rho);
-}
-template <typename R, typename Data, int NV>
-__device__ __noinline__ Thr<R> full_topk_cone(const RegRow<Data, NV>& row, int k, R rho) {
-  return thr_topk_cone<R>(row, k, rho);
-}
-template <typename R, typename Data, int NV>
-__device__ __noinline__ Thr<R> full_cone_search(const RegRow<Data, NV>& row, int k, R rho) {
-  return thr_topk_cone_search<R>(row, k, rho);
+// ---- the compacted candidates, sorted ---------------------------------------
+// Lane i holds the i-th largest candidate (lanes >= n hold -inf) and the sum
+// of the first i + 1 of them, so a sum or a count over any value range is one
+// ballot plus one or two shuffles.
+template <typename R>
+struct Sorted {
+  R s, P;
+  int n;
+  __device__ __forceinline__ R at(int i) const { return __shfl_sync(kFullMask, s, i); }
+  // sum of the i largest candidates
+  __device__ __forceinline__ R pre(int i) const {
+    const R v = __shfl_sync(kFullMask, P, i > 0 ? i - 1 : 0);
+    return i > 0 ? v : R(0);
+  }
+  __device__ __forceinline__ int count_gt(R c) const {
+    return __popc(__ballot_sync(kFullMask, s > c));
+  }
+};
+
+template <typename R, typename Data>
+__device__ __forceinline__ Sorted<R> sort_candidates(const LaneRow<Data>& cand, int n, int lane) {
+  Sorted<R> out;
+  const Data v = warp_sort_desc(cand.x, lane);
+  out.s = static_cast<R>(v);
+  out.n = n;
+  R p = (lane < n) ? out.s : R(0);
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const R up = __shfl_up_sync(kFullMask, p, o);
+    if (lane >= o) p += up;
+  }
+  out.P = p;
+  return out;
 }
 
-// Top-k simplex (rho = 0) and its biased form on a register row.
-template <typename R, typename Data, int NV>
-__device__ __forceinline__ Thr<R> fast_topk_simplex(const RegRow<Data, NV>& row, int k, R rhs,
-                                                    R rho, Data* slots, int lane) {
-  const int m = row.size();
-  if (k <= 31 && m > 32) {
-    const R K = static_cast<R>(k), H = rhs / K;
-    const Data tau = lane_max_cut(row, k, lane);
-    // support of the knapsack step: a_i > t >= v_(k+1) - rhs/k >= tau - rhs/k
-    const Data cut = round_down(static_cast<R>(tau) - H - abs_(static_cast<R>(tau)) * num<R>::eps() * 4, Data(0));
-    LaneRow<Data> cand;
-    const int total = compact_candidates(row, cut, slots, lane, cand);
-    if (total <= 32 && total > k) {
-      const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
-      const R rho_k2 = rho * K * K;
-      cand.reported = m;
-      Thr<R> thr;
-      const Projection proj = topk_special_cases<R>(cand, k, K + rho_k2, thr);
-      if (proj == kProjZero) return thr;
-      cand.reported = total;
-      if (proj == kProjConstant) {
-        if (K * thr.hi > rhs + eps) return thr_knapsack_eq<R>(cand, R(0), H, rhs);
-        return thr;
-      }
-      Thr<R> eq = thr_knapsack_eq<R>(cand, R(0), H, rhs);
-      bool lt;
-      if (eq.nU == 0) {
-        lt = eq.t < rho * rhs - eps;
-      } else {
-        int cnt; R sum_U;
-        row_count_sum_gt<R>(cand, eq.cutU, cnt, sum_U);
-        const R num_U = static_cast<R>(cnt);
-        lt = K * (sum_U + (K - num_U) * eq.t) < rhs * (num_U + rho_k2) - eps;
-      }
-      if (!lt) return eq;
-      return full_cone_search<R>(row, k, rho);
-    }
+// Zero / constant / general classification on sorted candidates
+// (include/sdca/prox/topk_cone.h:18-55 of the reference); `m` is the length of
+// the whole row.  Needs more than k candidates.
+template <typename R>
+__device__ __forceinline__ Projection sorted_special_cases(const Sorted<R>& c, int m, int k, R div,
+                                                           Thr<R>& thr) {
+  const R eps = 16 * num<R>::eps();
+  const R sum_k = c.pre(k);
+  if (sum_k <= eps) {
+    thr = make_thr(R(0), R(0), R(0), 0, 0, num<R>::inf(), num<R>::inf());
+    return kProjZero;
   }
-  return full_topk_simplex<R>(row, k, rhs, rho);
+  const R v_k = c.at(k - 1);
+  const R hi = sum_k / div;
+  const R t = v_k - hi;
+  if (k == m || t >= c.at(k) - eps) {
+    thr = make_thr(t, R(0), hi, k, 0, v_k, v_k);
+    return kProjConstant;
+  }
+  return kProjGeneral;
 }
 
-// Top-k cone on a register row.  For rho = 0 the first candidate of the search
-// (U empty) has t = 0 and M = {a > 0}: one pass for the sum of the positive
-// entries decides it; anything else takes the general search.
-template <typename R, typename Data, int NV>
-__device__ __forceinline__ Thr<R> fast_topk_cone(const RegRow<Data, NV>& row, int k, R rho,
-                                                 Data* slots, int lane) {
-  const int m = row.size();
-  if (k <= 31 && m > 32) {
-    const R K = static_cast<R>(k);
-    const Data tau = lane_max_cut(row, k, lane);
-    const Data cut = round_down(static_cast<R>(tau) - abs_(static_cast<R>(tau)) * num<R>::eps() * 4 - num<R>::tiny(), Data(0));
-    LaneRow<Data> cand;
-    const int total = compact_candidates(row, cut, slots, lane, cand);
-    if (total <= 32 && total > k) {
-      cand.reported = m;
-      Thr<R> thr;
-      if (topk_special_cases<R>(cand, k, K + rho * K * K, thr) != kProjGeneral) return thr;
-      if (rho == 0) {
-        const R eps = 16 * num<R>::eps();
-        int j = 0; R s = 0; R mx = -num<R>::inf();
-        row.for_each([&](Data xd, int) {
-          R x = static_cast<R>(xd);
-          mx = max_(mx, x);
-          if (x > 0) { ++j; s += x; }
-        });
-        j = warp_sum(j); s = warp_sum(s); mx = warp_max(mx);
-        const R D = K * K;
-        const R t = (R(0) * s - K * R(0)) / D;
-        const R hi = (R(0) + K * s) / D;
-        if (j > 0 && mx - eps <= hi + t) return make_thr(t, R(0), hi, 0, j, num<R>::inf(), t);
-      }
-      return full_cone_search<R>(row, k, rho);
+// Variable fixing for  <1,x> = rhs, 0 <= x <= hi  on sorted candidates: the
+// iteration of thr_knapsack_eq with the free entries kept as the index range
+// [f0, f1) of the sorted order.  Entries that are not candidates are below
+// every threshold the iteration can reach and contribute lo = 0.
+template <typename R>
+__device__ __forceinline__ Thr<R> sorted_knapsack_eq(const Sorted<R>& c, R hi, R rhs, R& sum_U) {
+  const int n = c.n;
+  const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
+  int f0 = 0, f1 = n, mfree = n;
+  R S0 = 0, S1 = c.pre(n);
+  R t = (S1 - rhs) / static_cast<R>(n);
+  for (int it = 0;; ++it) {
+    const R thi = hi + t;
+    int a = c.count_gt(t);
+    a = min(max(a, f0), f1);           // lo-set: [a, f1)
+    int b = min(c.count_gt(thi), a);
+    b = max(b, f0);                    // hi-set: [f0, b)
+    const R Pa = c.pre(a), Pb = c.pre(b);
+    const int n_lo = f1 - a, n_hi = b - f0;
+    const R sum_lo = S1 - Pa, sum_hi = Pb - S0;
+    const R s_hi = static_cast<R>(n_hi) * hi;
+    const R infeas = sum_hi + sum_lo - s_hi - static_cast<R>(n_hi + n_lo) * t;
+    R tt;
+    if (n_hi > 0 && infeas > eps && it <= n) {
+      tt = static_cast<R>(mfree) * t - sum_hi + s_hi;
+      mfree -= n_hi; f0 = b; S0 = Pb;
+    } else if (n_lo > 0 && infeas < -eps && it <= n) {
+      tt = static_cast<R>(mfree) * t - sum_lo;
+      mfree -= n_lo; f1 = a; S1 = Pa;
+    } else {
+      sum_U = Pb;
+      return make_thr(t, R(0), hi, b, a - b, min_(thi, b > 0 ? c.at(b - 1) : num<R>::inf()), t);
+    }
+    if (mfree > 0) {
+      t = tt / static_cast<R>(mfree);
+    } else {
+      sum_U = S0;
+      return make_thr(t, R(0), hi, f0, 0, thi, thi);
     }
   }
-  return full_topk_cone<R>(row, k, rho);
+}
+
+enum FastStatus { kFastDone = 0, kFastNeedsFullRow = 1 };
+
+// Top-k simplex (rho = 0) and its biased form.  Returns kFastNeedsFullRow when
+// the row has to go through the general search on the full row.
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& row, int k, R rhs,
+                                                        R rho, Data* slots, int lane, Thr<R>& thr) {
+  const int m = row.size();
+  if (k > 31 || m <= 32) return kFastNeedsFullRow;
+  const R K = static_cast<R>(k), H = rhs / K;
+  const Data tau = lane_max_cut(row, k, lane);
+  // support of the knapsack step: a_i > t >= v_(k+1) - rhs/k >= tau - rhs/k
+  const Data cut = round_down(static_cast<R>(tau) - H - abs_(static_cast<R>(tau)) * num<R>::eps() * 4,
+                              Data(0));
+  LaneRow<Data> cand;
+  const int total = compact_candidates(row, cut, slots, lane, cand);
+  if (total > 32 || total <= k) return kFastNeedsFullRow;
+  const Sorted<R> c = sort_candidates<R>(cand, total, lane);
+  const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
+  const R rho_k2 = rho * K * K;
+  const Projection proj = sorted_special_cases<R>(c, m, k, K + rho_k2, thr);
+  if (proj == kProjZero) return kFastDone;
+  R sum_U;
+  if (proj == kProjConstant) {
+    if (K * thr.hi > rhs + eps) thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
+    return kFastDone;
+  }
+  thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
+  bool lt;
+  if (thr.nU == 0) {
+    lt = thr.t < rho * rhs - eps;
+  } else {
+    const R num_U = static_cast<R>(thr.nU);
+    lt = K * (sum_U + (K - num_U) * thr.t) < rhs * (num_U + rho_k2) - eps;
+  }
+  return lt ? kFastNeedsFullRow : kFastDone;
+}
+
+// Top-k cone.  For rho = 0 the first candidate of the search (U empty) has
+// t = 0 and M = {a > 0}: one pass for the sum of the positive entries decides
+// it; anything else takes the general search.
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row, int k, R rho,
+                                                     Data* slots, int lane, Thr<R>& thr) {
+  const int m = row.size();
+  if (k > 31 || m <= 32 || rho != 0) return kFastNeedsFullRow;
+  const R K = static_cast<R>(k);
+  const Data tau = lane_max_cut(row, k, lane);
+  const Data cut = round_down(static_cast<R>(tau) - abs_(static_cast<R>(tau)) * num<R>::eps() * 4
+                              - num<R>::tiny(), Data(0));
+  LaneRow<Data> cand;
+  const int total = compact_candidates(row, cut, slots, lane, cand);
+  if (total > 32 || total <= k) return kFastNeedsFullRow;
+  const Sorted<R> c = sort_candidates<R>(cand, total, lane);
+  if (sorted_special_cases<R>(c, m, k, K, thr) != kProjGeneral) return kFastDone;
+  const R eps = 16 * num<R>::eps();
+  int j = 0; R s = 0;
+  row.for_each([&](Data xd, int) {
+    if (xd > Data(0)) { ++j; s += static_cast<R>(xd); }
+  });
+  j = warp_sum(j); s = warp_sum(s);
+  const R D = K * K;
+  const R t = (R(0) * s - K * R(0)) / D;
+  const R hi = (R(0) + K * s) / D;
+  if (j > 0 && c.at(0) - eps <= hi + t) {
+    thr = make_thr(t, R(0), hi, 0, j, num<R>::inf(), t);
+    return kFastDone;
+  }
+  return kFastNeedsFullRow;
+}
+
+// The general search for one row staged in shared memory; out of line so that
+// the register budget of the kernel is set by the common path.
+template <typename R, typename Data, int PROX>
+__device__ __noinline__ Thr<R> full_row_thresholds(const Data* buf, int m, const ProxParams* q) {
+  StridedRow<Data> view(buf, m);
+  return compute_thresholds<R>(PROX, view, *q);
 }
 
 template <typename Data, typename R, int PROX, int NV>
-__global__ void __launch_bounds__(kFastThreads, 4)
+__global__ void __launch_bounds__(kFastThreads)
 fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long long n,
-                 ProxParams q) {
+                 ProxParams q, int m_pad) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ Data slots_all[kFastThreads / 32][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps_per_block = kFastThreads / 32;
   Data* slots = slots_all[warp];
+  Data* stage = reinterpret_cast<Data*>(smem_raw) + static_cast<size_t>(warp) * m_pad;
+  constexpr bool kTopk = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased ||
+                          PROX == kTopkCone || PROX == kTopkConeBiased);
   for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + warp; r < n;
        r += static_cast<long long>(gridDim.x) * warps_per_block) {
     RegRow<Data, NV> row;
     row.m = m;
     row.load(a + r * m, lane);
     Thr<R> thr;
+    FastStatus st = kFastNeedsFullRow;
     if (PROX == kTopkSimplex || PROX == kTopkSimplexBiased) {
-      thr = fast_topk_simplex<R>(row, q.k, static_cast<R>(q.rhs),
-                                 PROX == kTopkSimplexBiased ? static_cast<R>(q.rho) : R(0), slots, lane);
+      st = fast_topk_simplex<R>(row, q.k, static_cast<R>(q.rhs),
+                                PROX == kTopkSimplexBiased ? static_cast<R>(q.rho) : R(0),
+                                slots, lane, thr);
     } else if (PROX == kTopkCone || PROX == kTopkConeBiased) {
-      thr = fast_topk_cone<R>(row, q.k, PROX == kTopkConeBiased ? static_cast<R>(q.rho) : R(0),
-                              slots, lane);
+      st = fast_topk_cone<R>(row, q.k, PROX == kTopkConeBiased ? static_cast<R>(q.rho) : R(0),
+                             slots, lane, thr);
+    }
+    if (kTopk) {
+      if (st != kFastDone) {
+        row.for_each([&](Data x, int i) { stage[i] = x; });
+        __syncwarp();
+        thr = full_row_thresholds<R, Data, PROX>(stage, m, &q);
+        __syncwarp();
+      }
     } else {
       thr = compute_thresholds<R>(PROX, row, q);
     }
@@ -295,14 +393,18 @@ int launch_fast(const Data* a, Data* out, int m, long long n, const ProxParams& 
   int rc = get_device_info(&info);
   if (rc) return rc;
   auto kernel = fast_rows_kernel<Data, R, PROX, NV>;
+  constexpr bool kTopk = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased ||
+                          PROX == kTopkCone || PROX == kTopkConeBiased);
+  const int m_pad = (m + 15) & ~15;
+  const size_t smem = kTopk ? static_cast<size_t>(kFastThreads / 32) * m_pad * sizeof(Data) : 0;
   int per_sm = 0;
-  SDCAB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFastThreads, 0));
+  SDCAB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFastThreads, smem));
   if (per_sm < 1) per_sm = 1;
   const int warps = kFastThreads / 32;
   long long want = (n + warps - 1) / warps;
   int blocks = static_cast<int>(std::max<long long>(
       1, std::min<long long>(want, static_cast<long long>(per_sm) * info.sm_count)));
-  kernel<<<blocks, kFastThreads, 0, stream>>>(a, out, m, n, q);
+  kernel<<<blocks, kFastThreads, smem, stream>>>(a, out, m, n, q, m_pad);
   SDCAB_CUDA_TRY(cudaGetLastError());
   return SDCAB_OK;
 }

@@ -1,11 +1,17 @@
 """Shared helpers of the parity tests: input regimes and the tolerance metric.
 
 Tolerance (stated once, used everywhere): an output element may differ from
-the reference by at most tol * max(1, max|a_row|), tol = 1e-12 for float64 data
-and 1e-5 for float32 data when thresholds are computed in double (the
-reference's default).  When the caller asks for float thresholds the float
-accumulation over m terms is part of both results, so the bound is widened to
-4 * m * FLT_EPSILON.
+the reference by at most tol * max(1, max|a_row|) with
+  tol = 1e-12 for float64 data (widened to 8 * m * DBL_EPSILON for long rows:
+        both sides round sums of m terms, in different orders),
+  tol = 1e-5  for float32 data with thresholds computed in double (the
+        reference's default).
+When the caller asks for float thresholds, the float accumulation (and for the
+Lambert-based operators a float Newton iteration) is part of both results and
+the reference's own float result is only that accurate; the bound is then
+4 * m * FLT_EPSILON against the float reference, or -- see
+``float_precision_ok`` -- twice the reference's own distance from its double
+result.
 """
 import zlib
 
@@ -22,7 +28,7 @@ def stable_seed(*parts):
 
 
 def tolerance(dtype, precision, m):
-    tol = 1e-5 if np.dtype(dtype) == np.float32 else 1e-12
+    tol = 1e-5 if np.dtype(dtype) == np.float32 else max(1e-12, 8 * m * float(np.finfo(np.float64).eps))
     if precision != "double":
         tol = max(tol, 4 * m * float(np.finfo(np.float32).eps))
     return tol
@@ -31,6 +37,18 @@ def tolerance(dtype, precision, m):
 def scaled_error(x, x_ref, a):
     scale = np.maximum(1.0, np.abs(a.astype(np.float64)).max(axis=1, keepdims=True))
     return np.abs(x.astype(np.float64) - x_ref.astype(np.float64)) / scale
+
+
+def float_precision_ok(x, x_ref_float, x_ref_double, a, tol):
+    """Acceptance for float thresholds: within tol of the reference's float
+    result, or as close to the reference's double result as twice the
+    reference's own float result is."""
+    e_float = scaled_error(x, x_ref_float, a).max()
+    if e_float <= tol:
+        return True, e_float
+    own = scaled_error(x_ref_float, x_ref_double, a).max()
+    e_double = scaled_error(x, x_ref_double, a).max()
+    return e_double <= max(tol, 2 * own), e_double
 
 
 def regime(rng, n, m, dtype, kind):
