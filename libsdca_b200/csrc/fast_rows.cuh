@@ -20,6 +20,9 @@ namespace sdcab {
 
 constexpr int kNoFastPath = 1;
 constexpr int kFastThreads = 128;
+#ifndef SDCAB_FAST_MIN_BLOCKS
+#define SDCAB_FAST_MIN_BLOCKS 6
+#endif
 
 template <typename Data> struct VecOf;
 template <> struct VecOf<float> { typedef float4 type; static constexpr int N = 4; };
@@ -120,42 +123,48 @@ __device__ __forceinline__ T warp_sort_desc(T v, int lane) {
 // entry of the row.
 template <typename Data, int NV>
 __device__ __forceinline__ Data lane_max_cut(const RegRow<Data, NV>& row, int k, int lane) {
-  Data lm = -num<Data>::inf();
+  // balanced tree: short dependency chains
+  Data vm[NV];
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const Data* e = reinterpret_cast<const Data*>(&row.v[j]);
+    Data a = e[0];
 #pragma unroll
-    for (int c = 0; c < RegRow<Data, NV>::VN; ++c) lm = max_(lm, e[c]);
+    for (int c = 1; c < RegRow<Data, NV>::VN; ++c) a = max_(a, e[c]);
+    if (RegRow<Data, NV>::VN == 4) a = max_(max_(e[0], e[1]), max_(e[2], e[3]));
+    vm[j] = a;
   }
+#pragma unroll
+  for (int w = 1; w < NV; w <<= 1) {
+#pragma unroll
+    for (int j = 0; j + w < NV; j += 2 * w) vm[j] = max_(vm[j], vm[j + w]);
+  }
+  const Data lm = vm[0];
   const Data sorted = warp_sort_desc(lm, lane);
   return __shfl_sync(kFullMask, sorted, k);  // k <= 31
 }
 
-// Compacts the entries with x > cut to one per lane through shared memory.
-// Returns their number; the LaneRow is only valid if that number is <= 32.
+// Compacts the entries with x > cut to one per lane through shared memory;
+// slots are handed out by a shared-memory counter (the order is irrelevant, the
+// candidates are sorted afterwards).  Returns their number; the LaneRow is only
+// valid if that number is <= 32.  *counter must be 0 on entry and is left at 0.
 template <typename Data, int NV>
 __device__ __forceinline__ int compact_candidates(const RegRow<Data, NV>& row, Data cut,
-                                                  Data* __restrict__ slots, int lane,
-                                                  LaneRow<Data>& out) {
-  int mine = 0;
-  row.for_each([&](Data x, int) { mine += (x > cut) ? 1 : 0; });
-  int incl = mine;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int up = __shfl_up_sync(kFullMask, incl, o);
-    if (lane >= o) incl += up;
-  }
-  const int total = __shfl_sync(kFullMask, incl, 31);
-  if (total <= 32) {
-    int pos = incl - mine;
-    row.for_each([&](Data x, int) {
-      if (x > cut) slots[pos++] = x;
-    });
-    __syncwarp();
-    out.valid = lane < total;
-    out.x = out.valid ? slots[lane] : -num<Data>::inf();
-    __syncwarp();
-  }
+                                                  Data* __restrict__ slots, int* counter,
+                                                  int lane, LaneRow<Data>& out) {
+  row.for_each([&](Data x, int) {
+    if (x > cut) {
+      const int pos = atomicAdd(counter, 1);
+      if (pos < 32) slots[pos] = x;
+    }
+  });
+  __syncwarp();
+  const int total = *counter;
+  out.valid = lane < total;
+  out.x = (lane < total && total <= 32) ? slots[lane] : -num<Data>::inf();
+  __syncwarp();
+  if (lane == 0) *counter = 0;
+  __syncwarp();
   return total;
 }
 
@@ -265,13 +274,57 @@ __device__ __forceinline__ Thr<R> sorted_knapsack_eq(const Sorted<R>& c, R hi, R
   }
 }
 
+// For float data with double thresholds the variable fixing first runs in
+// float (same iteration, cheap arithmetic) to find the sets U and M; t is then
+// computed once in double from those sets and the four conditions that make
+// (U, M, t) the exact solution are checked in double.  Only if a check fails
+// (an entry within float rounding of a threshold) the double iteration runs.
+template <typename R, typename Data>
+__device__ __forceinline__ Thr<R> solve_knapsack_on_candidates(const Sorted<R>& c, R hi, R rhs,
+                                                                R& sum_U, int lane) {
+  if (std::is_same<R, double>::value && std::is_same<Data, float>::value) {
+    Sorted<float> cf;
+    cf.s = static_cast<float>(c.s);
+    cf.n = c.n;
+    float p = (lane < c.n) ? cf.s : 0.0f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(kFullMask, p, o);
+      if (lane >= o) p += up;
+    }
+    cf.P = p;
+    float sum_Uf;
+    const Thr<float> tf = sorted_knapsack_eq<float>(cf, static_cast<float>(hi),
+                                                   static_cast<float>(rhs), sum_Uf);
+    const int u = tf.nU, j = tf.nM, n = c.n;
+    const R Pu = c.pre(u);
+    R t;
+    if (j > 0) {
+      t = (c.pre(u + j) - Pu - rhs + static_cast<R>(u) * hi) / static_cast<R>(j);
+    } else {
+      t = static_cast<R>(tf.t);
+    }
+    const R thi = hi + t;
+    const R inf = num<R>::inf();
+    const R min_U = (u > 0) ? c.at(u - 1) : inf;
+    const R max_M = (j > 0) ? c.at(u) : -inf;
+    const R min_M = (j > 0) ? c.at(u + j - 1) : inf;
+    const R max_L = (u + j < n) ? c.at(u + j) : -inf;
+    if (min_U > thi && max_M <= thi && min_M > t && max_L <= t) {
+      sum_U = Pu;
+      return make_thr(t, R(0), hi, u, j, min_(thi, min_U), t);
+    }
+  }
+  return sorted_knapsack_eq<R>(c, hi, rhs, sum_U);
+}
+
 enum FastStatus { kFastDone = 0, kFastNeedsFullRow = 1 };
 
 // Top-k simplex (rho = 0) and its biased form.  Returns kFastNeedsFullRow when
 // the row has to go through the general search on the full row.
 template <typename R, typename Data, int NV>
 __device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& row, int k, R rhs,
-                                                        R rho, Data* slots, int lane, Thr<R>& thr) {
+                                                        R rho, Data* slots, int* counter, int lane, Thr<R>& thr) {
   const int m = row.size();
   if (k > 31 || m <= 32) return kFastNeedsFullRow;
   const R K = static_cast<R>(k), H = rhs / K;
@@ -280,7 +333,7 @@ __device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& 
   const Data cut = round_down(static_cast<R>(tau) - H - abs_(static_cast<R>(tau)) * num<R>::eps() * 4,
                               Data(0));
   LaneRow<Data> cand;
-  const int total = compact_candidates(row, cut, slots, lane, cand);
+  const int total = compact_candidates(row, cut, slots, counter, lane, cand);
   if (total > 32 || total <= k) return kFastNeedsFullRow;
   const Sorted<R> c = sort_candidates<R>(cand, total, lane);
   const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
@@ -289,10 +342,10 @@ __device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& 
   if (proj == kProjZero) return kFastDone;
   R sum_U;
   if (proj == kProjConstant) {
-    if (K * thr.hi > rhs + eps) thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
+    if (K * thr.hi > rhs + eps) thr = solve_knapsack_on_candidates<R, Data>(c, H, rhs, sum_U, lane);
     return kFastDone;
   }
-  thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
+  thr = solve_knapsack_on_candidates<R, Data>(c, H, rhs, sum_U, lane);
   bool lt;
   if (thr.nU == 0) {
     lt = thr.t < rho * rhs - eps;
@@ -308,7 +361,7 @@ __device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& 
 // it; anything else takes the general search.
 template <typename R, typename Data, int NV>
 __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row, int k, R rho,
-                                                     Data* slots, int lane, Thr<R>& thr) {
+                                                     Data* slots, int* counter, int lane, Thr<R>& thr) {
   const int m = row.size();
   if (k > 31 || m <= 32 || rho != 0) return kFastNeedsFullRow;
   const R K = static_cast<R>(k);
@@ -316,16 +369,40 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
   const Data cut = round_down(static_cast<R>(tau) - abs_(static_cast<R>(tau)) * num<R>::eps() * 4
                               - num<R>::tiny(), Data(0));
   LaneRow<Data> cand;
-  const int total = compact_candidates(row, cut, slots, lane, cand);
+  const int total = compact_candidates(row, cut, slots, counter, lane, cand);
   if (total > 32 || total <= k) return kFastNeedsFullRow;
   const Sorted<R> c = sort_candidates<R>(cand, total, lane);
   if (sorted_special_cases<R>(c, m, k, K, thr) != kProjGeneral) return kFastDone;
   const R eps = 16 * num<R>::eps();
+  // sum and count of the positive entries.  U is empty on this branch, so no
+  // output attains hi and only the acceptance test below depends on the sum:
+  // float data is summed per lane in float (four chains), across lanes in R,
+  // and a test that is not clear-cut is left to the general search.
   int j = 0; R s = 0;
-  row.for_each([&](Data xd, int) {
-    if (xd > Data(0)) { ++j; s += static_cast<R>(xd); }
-  });
-  j = warp_sum(j); s = warp_sum(s);
+  bool clear_cut = true;
+  if (std::is_same<Data, float>::value && std::is_same<R, double>::value) {
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    int cnt[4] = {0, 0, 0, 0};
+    int slot = 0;
+    row.for_each([&](Data xd, int) {
+      const float x = static_cast<float>(xd);
+      acc[slot & 3] += fmaxf(x, 0.0f);
+      cnt[slot & 3] += (x > 0.0f) ? 1 : 0;
+      ++slot;
+    });
+    j = warp_sum((cnt[0] + cnt[1]) + (cnt[2] + cnt[3]));
+    s = warp_sum((static_cast<R>(acc[0]) + static_cast<R>(acc[1])) +
+                 (static_cast<R>(acc[2]) + static_cast<R>(acc[3])));
+    const R hi_est = s / K;
+    const R mx = c.at(0);
+    clear_cut = abs_(mx - hi_est) > R(1e-4) * max_(abs_(hi_est), abs_(mx));
+  } else {
+    row.for_each([&](Data xd, int) {
+      if (xd > Data(0)) { ++j; s += static_cast<R>(xd); }
+    });
+    j = warp_sum(j); s = warp_sum(s);
+  }
+  if (!clear_cut) return kFastNeedsFullRow;
   const R D = K * K;
   const R t = (R(0) * s - K * R(0)) / D;
   const R hi = (R(0) + K * s) / D;
@@ -345,14 +422,18 @@ __device__ __noinline__ Thr<R> full_row_thresholds(const Data* buf, int m, const
 }
 
 template <typename Data, typename R, int PROX, int NV>
-__global__ void __launch_bounds__(kFastThreads)
+__global__ void __launch_bounds__(kFastThreads, SDCAB_FAST_MIN_BLOCKS)
 fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long long n,
                  ProxParams q, int m_pad) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ Data slots_all[kFastThreads / 32][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps_per_block = kFastThreads / 32;
+  __shared__ int counters[kFastThreads / 32];
   Data* slots = slots_all[warp];
+  int* counter = &counters[warp];
+  if (lane == 0) *counter = 0;
+  __syncwarp();
   Data* stage = reinterpret_cast<Data*>(smem_raw) + static_cast<size_t>(warp) * m_pad;
   constexpr bool kTopk = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased ||
                           PROX == kTopkCone || PROX == kTopkConeBiased);
@@ -366,10 +447,10 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
     if (PROX == kTopkSimplex || PROX == kTopkSimplexBiased) {
       st = fast_topk_simplex<R>(row, q.k, static_cast<R>(q.rhs),
                                 PROX == kTopkSimplexBiased ? static_cast<R>(q.rho) : R(0),
-                                slots, lane, thr);
+                                slots, counter, lane, thr);
     } else if (PROX == kTopkCone || PROX == kTopkConeBiased) {
       st = fast_topk_cone<R>(row, q.k, PROX == kTopkConeBiased ? static_cast<R>(q.rho) : R(0),
-                             slots, lane, thr);
+                             slots, counter, lane, thr);
     }
     if (kTopk) {
       if (st != kFastDone) {

@@ -1,0 +1,183 @@
+/*
+ * Test infrastructure: a plain-C restatement of the reference's CPU algorithms
+ * for the batched proximal operators and the objective / duality-gap
+ * evaluation (mlapin/libsdca: include/sdca/prox, include/sdca/math,
+ * include/sdca/solver/eval*, include/sdca/solver/objective).  The body is
+ * sdca_oracle_impl.inc, compiled here for float/double data and float/double
+ * accumulators; each function there cites the file:line it follows.
+ *
+ * Parity of this restatement is pinned by tests/test_oracle_restatement.py,
+ * which checks it against the reference's own headers (oracle/_ref) on the
+ * regimes of the reference's tests, and against the committed golden vectors.
+ *
+ * Only tests, the smoke check and bench.py's CPU-baseline legs may call this;
+ * the product library never does.
+ */
+#include <float.h>
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+typedef struct {
+  double lo, hi, rhs, rho, alpha;
+  int64_t k, p;
+} oracle_opts;
+
+typedef struct {
+  int objective;
+  double c, gamma;
+  int64_t k;
+  int input_kind;
+  int64_t d, n, m;
+  const void* X;
+  void* A;
+  void* W;
+  const void* W0;
+  const int64_t* labels;
+  const int64_t* offsets;
+  int is_train;
+  int nthreads;
+  double epsilon;
+  int64_t max_epoch, eval_epoch;
+  int eval_on_start;
+} oracle_eval_args;
+
+#define CAT2(a, b) a##_##b
+#define CAT(a, b) CAT2(a, b)
+
+/* float data, float accumulators */
+#define D float
+#define R float
+#define FN(x) CAT(x, ff)
+#define R_EPS FLT_EPSILON
+#define R_MIN FLT_MIN
+#define R_EXP_MIN_ARG (-8.733654022216796875000000e+01f) /* math/log_exp.h:47-52 */
+#define R_EXP expf
+#define R_LOG logf
+#define R_LOG1P log1pf
+#define R_FABS fabsf
+#define R_LAMBERT lambert_w_exp_f
+#define D_EXP expf
+#define D_LAMBERT lambert_w_exp_f
+#include "sdca_oracle_impl.inc"
+#undef D
+#undef R
+#undef FN
+#undef R_EPS
+#undef R_MIN
+#undef R_EXP_MIN_ARG
+#undef R_EXP
+#undef R_LOG
+#undef R_LOG1P
+#undef R_FABS
+#undef R_LAMBERT
+#undef D_EXP
+#undef D_LAMBERT
+
+/* float data, double accumulators (the reference's default for float input) */
+#define D float
+#define R double
+#define FN(x) CAT(x, fd)
+#define R_EPS DBL_EPSILON
+#define R_MIN DBL_MIN
+#define R_EXP_MIN_ARG (log(DBL_MIN)) /* math/log_exp.h:33-35 */
+#define R_EXP exp
+#define R_LOG log
+#define R_LOG1P log1p
+#define R_FABS fabs
+#define R_LAMBERT lambert_w_exp_d
+#define D_EXP expf
+#define D_LAMBERT lambert_w_exp_f
+#include "sdca_oracle_impl.inc"
+#undef D
+#undef R
+#undef FN
+#undef R_EPS
+#undef R_MIN
+#undef R_EXP_MIN_ARG
+#undef R_EXP
+#undef R_LOG
+#undef R_LOG1P
+#undef R_FABS
+#undef R_LAMBERT
+#undef D_EXP
+#undef D_LAMBERT
+
+/* double data, float accumulators */
+#define D double
+#define R float
+#define FN(x) CAT(x, df)
+#define R_EPS FLT_EPSILON
+#define R_MIN FLT_MIN
+#define R_EXP_MIN_ARG (-8.733654022216796875000000e+01f)
+#define R_EXP expf
+#define R_LOG logf
+#define R_LOG1P log1pf
+#define R_FABS fabsf
+#define R_LAMBERT lambert_w_exp_f
+#define D_EXP exp
+#define D_LAMBERT lambert_w_exp_d
+#include "sdca_oracle_impl.inc"
+#undef D
+#undef R
+#undef FN
+#undef R_EPS
+#undef R_MIN
+#undef R_EXP_MIN_ARG
+#undef R_EXP
+#undef R_LOG
+#undef R_LOG1P
+#undef R_FABS
+#undef R_LAMBERT
+#undef D_EXP
+#undef D_LAMBERT
+
+/* double data, double accumulators */
+#define D double
+#define R double
+#define FN(x) CAT(x, dd)
+#define R_EPS DBL_EPSILON
+#define R_MIN DBL_MIN
+#define R_EXP_MIN_ARG (log(DBL_MIN))
+#define R_EXP exp
+#define R_LOG log
+#define R_LOG1P log1p
+#define R_FABS fabs
+#define R_LAMBERT lambert_w_exp_d
+#define D_EXP exp
+#define D_LAMBERT lambert_w_exp_d
+#include "sdca_oracle_impl.inc"
+
+/* dtype / result: 0 = float, 1 = double (same convention as oracle/ref_shim.cpp) */
+int sdca_oracle_prox(const char* prox, int dtype, int result, void* a, int64_t m, int64_t n,
+                     const oracle_opts* o, int nthreads) {
+  (void)nthreads;
+  if (dtype == 0 && result == 0) return run_ff(prox, (float*)a, m, n, o, 0, 0, 0, 0, 0, 1);
+  if (dtype == 0 && result == 1) return run_fd(prox, (float*)a, m, n, o, 0, 0, 0, 0, 0, 1);
+  if (dtype == 1 && result == 0) return run_df(prox, (double*)a, m, n, o, 0, 0, 0, 0, 0, 1);
+  if (dtype == 1 && result == 1) return run_dd(prox, (double*)a, m, n, o, 0, 0, 0, 0, 0, 1);
+  return -2;
+}
+
+int sdca_oracle_thresholds(const char* prox, int dtype, int result, const void* a, int64_t m,
+                           int64_t n, const oracle_opts* o, double* t, double* lo, double* hi,
+                           int64_t* nU, int64_t* nM) {
+  if (dtype == 0 && result == 0) return run_ff(prox, (float*)a, m, n, o, t, lo, hi, nU, nM, 0);
+  if (dtype == 0 && result == 1) return run_fd(prox, (float*)a, m, n, o, t, lo, hi, nU, nM, 0);
+  if (dtype == 1 && result == 0) return run_df(prox, (double*)a, m, n, o, t, lo, hi, nU, nM, 0);
+  if (dtype == 1 && result == 1) return run_dd(prox, (double*)a, m, n, o, t, lo, hi, nU, nM, 0);
+  return -2;
+}
+
+int sdca_oracle_eval(const oracle_eval_args* a, int dtype, int result, double* out, double* acc) {
+  if (dtype == 0 && result == 0) return eval_ff(a, out, acc);
+  if (dtype == 0 && result == 1) return eval_fd(a, out, acc);
+  if (dtype == 1 && result == 0) return eval_df(a, out, acc);
+  if (dtype == 1 && result == 1) return eval_dd(a, out, acc);
+  return -2;
+}
+
+double sdca_oracle_lambert_w_exp_f64(double x) { return lambert_w_exp_d(x); }
+float sdca_oracle_lambert_w_exp_f32(float x) { return lambert_w_exp_f(x); }
