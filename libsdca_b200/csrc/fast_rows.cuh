@@ -118,6 +118,32 @@ __device__ __forceinline__ T warp_sort_desc(T v, int lane) {
   return v;
 }
 
+// Warp-wide maximum in one instruction (redux.sync on sm_100a handles f32;
+// doubles take the shuffle butterfly).
+__device__ __forceinline__ float warp_max_fast(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ double warp_max_fast(double v) { return warp_max(v); }
+
+// The (k+1)-th largest of the 32 lane values (k <= 31), counting repeats:
+// repeatedly take the warp maximum and retire the lanes that hold it.
+template <typename T>
+__device__ __forceinline__ T kth_largest_of_lanes(T v, int k, int lane) {
+  (void)lane;
+  int seen = 0;
+  T cur = v, top = -num<T>::inf();
+  for (int round = 0; round <= k; ++round) {
+    top = warp_max_fast(cur);
+    const unsigned hit = __ballot_sync(kFullMask, cur == top);
+    seen += __popc(hit);
+    if (seen > k || top == -num<T>::inf()) break;
+    cur = (cur == top) ? -num<T>::inf() : cur;
+  }
+  return top;
+}
+
 // The cut below which no entry can belong to the support, from the lane maxima:
 // tau = (k+1)-th largest lane maximum is a lower bound of the (k+1)-th largest
 // entry of the row.
@@ -140,8 +166,7 @@ __device__ __forceinline__ Data lane_max_cut(const RegRow<Data, NV>& row, int k,
     for (int j = 0; j + w < NV; j += 2 * w) vm[j] = max_(vm[j], vm[j + w]);
   }
   const Data lm = vm[0];
-  const Data sorted = warp_sort_desc(lm, lane);
-  return __shfl_sync(kFullMask, sorted, k);  // k <= 31
+  return kth_largest_of_lanes(lm, k, lane);
 }
 
 // Compacts the entries with x > cut to one per lane through shared memory;
@@ -274,50 +299,6 @@ __device__ __forceinline__ Thr<R> sorted_knapsack_eq(const Sorted<R>& c, R hi, R
   }
 }
 
-// For float data with double thresholds the variable fixing first runs in
-// float (same iteration, cheap arithmetic) to find the sets U and M; t is then
-// computed once in double from those sets and the four conditions that make
-// (U, M, t) the exact solution are checked in double.  Only if a check fails
-// (an entry within float rounding of a threshold) the double iteration runs.
-template <typename R, typename Data>
-__device__ __forceinline__ Thr<R> solve_knapsack_on_candidates(const Sorted<R>& c, R hi, R rhs,
-                                                                R& sum_U, int lane) {
-  if (std::is_same<R, double>::value && std::is_same<Data, float>::value) {
-    Sorted<float> cf;
-    cf.s = static_cast<float>(c.s);
-    cf.n = c.n;
-    float p = (lane < c.n) ? cf.s : 0.0f;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float up = __shfl_up_sync(kFullMask, p, o);
-      if (lane >= o) p += up;
-    }
-    cf.P = p;
-    float sum_Uf;
-    const Thr<float> tf = sorted_knapsack_eq<float>(cf, static_cast<float>(hi),
-                                                   static_cast<float>(rhs), sum_Uf);
-    const int u = tf.nU, j = tf.nM, n = c.n;
-    const R Pu = c.pre(u);
-    R t;
-    if (j > 0) {
-      t = (c.pre(u + j) - Pu - rhs + static_cast<R>(u) * hi) / static_cast<R>(j);
-    } else {
-      t = static_cast<R>(tf.t);
-    }
-    const R thi = hi + t;
-    const R inf = num<R>::inf();
-    const R min_U = (u > 0) ? c.at(u - 1) : inf;
-    const R max_M = (j > 0) ? c.at(u) : -inf;
-    const R min_M = (j > 0) ? c.at(u + j - 1) : inf;
-    const R max_L = (u + j < n) ? c.at(u + j) : -inf;
-    if (min_U > thi && max_M <= thi && min_M > t && max_L <= t) {
-      sum_U = Pu;
-      return make_thr(t, R(0), hi, u, j, min_(thi, min_U), t);
-    }
-  }
-  return sorted_knapsack_eq<R>(c, hi, rhs, sum_U);
-}
-
 enum FastStatus { kFastDone = 0, kFastNeedsFullRow = 1 };
 
 // Top-k simplex (rho = 0) and its biased form.  Returns kFastNeedsFullRow when
@@ -342,10 +323,10 @@ __device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& 
   if (proj == kProjZero) return kFastDone;
   R sum_U;
   if (proj == kProjConstant) {
-    if (K * thr.hi > rhs + eps) thr = solve_knapsack_on_candidates<R, Data>(c, H, rhs, sum_U, lane);
+    if (K * thr.hi > rhs + eps) thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
     return kFastDone;
   }
-  thr = solve_knapsack_on_candidates<R, Data>(c, H, rhs, sum_U, lane);
+  thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
   bool lt;
   if (thr.nU == 0) {
     lt = thr.t < rho * rhs - eps;
@@ -383,13 +364,16 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
   if (std::is_same<Data, float>::value && std::is_same<R, double>::value) {
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     int cnt[4] = {0, 0, 0, 0};
-    int slot = 0;
-    row.for_each([&](Data xd, int) {
-      const float x = static_cast<float>(xd);
-      acc[slot & 3] += fmaxf(x, 0.0f);
-      cnt[slot & 3] += (x > 0.0f) ? 1 : 0;
-      ++slot;
-    });
+#pragma unroll
+    for (int jv = 0; jv < NV; ++jv) {
+      // vectors past the end of the row hold -inf and add nothing
+      const float* e = reinterpret_cast<const float*>(&row.v[jv]);
+#pragma unroll
+      for (int cc = 0; cc < RegRow<Data, NV>::VN; ++cc) {
+        acc[cc & 3] += fmaxf(e[cc], 0.0f);
+        cnt[cc & 3] += (e[cc] > 0.0f) ? 1 : 0;
+      }
+    }
     j = warp_sum((cnt[0] + cnt[1]) + (cnt[2] + cnt[3]));
     s = warp_sum((static_cast<R>(acc[0]) + static_cast<R>(acc[1])) +
                  (static_cast<R>(acc[2]) + static_cast<R>(acc[3])));

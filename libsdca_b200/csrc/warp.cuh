@@ -64,6 +64,15 @@ SDCAB_D T warp_sum(T v) {
   return v;
 }
 
+// integer sums and maxima are single redux.sync instructions
+SDCAB_D int warp_sum(int v) {
+#if defined(__CUDA_ARCH__)
+  return __reduce_add_sync(kFullMask, v);
+#else
+  return v;
+#endif
+}
+
 template <typename T>
 SDCAB_D T warp_max(T v) {
 #if defined(__CUDA_ARCH__)
