@@ -134,6 +134,120 @@ int sdcab_thresholds_f64(const char* prox, const double* a, int64_t m, int64_t n
 int sdcab_lambert_w_exp_f32_dev(float* x_dev, int64_t count, void* stream);
 int sdcab_lambert_w_exp_f64_dev(double* x_dev, int64_t count, void* stream);
 
+/* ---------------------------------------------------------------- eval ---- */
+
+/* Objectives of matsdca_fit (src/matlab/mex_solve.cpp:643-715).  The ids name the
+ * reference's objective classes (include/sdca/solver/objective/\*.h). */
+enum {
+  SDCAB_OBJ_L2_ENTROPY = 0,             /* softmax                                   */
+  SDCAB_OBJ_L2_ENTROPY_TOPK = 1,        /* l2_entropy_topk                           */
+  SDCAB_OBJ_L2_HINGE_TOPK = 2,          /* topk_hinge_alpha, gamma == 0              */
+  SDCAB_OBJ_L2_HINGE_TOPK_SMOOTH = 3,   /* topk_hinge_alpha, gamma > 0               */
+  SDCAB_OBJ_L2_TOPK_HINGE = 4,          /* topk_hinge_beta / msvm, gamma == 0        */
+  SDCAB_OBJ_L2_TOPK_HINGE_SMOOTH = 5,   /* topk_hinge_beta / msvm_smooth, gamma > 0  */
+  SDCAB_OBJ_L2_MULTILABEL_HINGE = 6,    /* mlsvm                                     */
+  SDCAB_OBJ_L2_MULTILABEL_HINGE_SMOOTH = 7, /* mlsvm_smooth                          */
+  SDCAB_OBJ_L2_MULTILABEL_ENTROPY = 8   /* mlsoftmax                                 */
+};
+
+typedef struct sdcab_objective {
+  int32_t id;
+  int32_t precision;  /* SDCAB_PRECISION_*: type of losses and accumulators */
+  double c, gamma;
+  int64_t k;
+} sdcab_objective;
+
+/* Maps an objective name and its parameters the way matsdca_fit does
+ * (src/matlab/mex_solve.cpp:622-719): synonyms, gamma == 0 selecting the
+ * non-smooth class, k == 1 for msvm / msvm_smooth / softmax, c > 0, gamma >= 0. */
+int sdcab_objective_from_name(const char* name, double c, double gamma, int64_t k,
+                              sdcab_objective* out);
+
+enum { SDCAB_INPUT_FEATURES = 0, SDCAB_INPUT_KERNEL = 1 };
+
+/* The evaluation record of the reference (include/sdca/solver/eval/types.h:12-172):
+ * primal = primal_loss + primal_regularizer, dual = dual_loss - dual_regularizer;
+ * rank_loss is used by the multilabel objectives, the accuracy histogram
+ * (m entries, cumulative: entry j = top-(j+1) accuracy) by the multiclass ones. */
+typedef struct sdcab_eval_record {
+  double primal, dual, primal_loss, dual_loss, primal_regularizer, dual_regularizer;
+  double rank_loss;
+  double relative_gap;
+} sdcab_eval_record;
+
+/* Problem description shared by the evaluation and fit entry points.  Memory is
+ * the reference's (include/sdca/solver/data/input.h): features are d x n
+ * column major (example i at X + d*i), a kernel matrix is n_train x n column
+ * major (column i at K + n_train*i), dual variables A are m x n_train column
+ * major (example i at A + m*i), primal variables W are d x m column major.
+ * Labels are 0-based; multilabel examples list their labels, sorted, at
+ * labels[offsets[i] .. offsets[i+1]) (data/output.h:76-166). */
+typedef struct sdcab_problem {
+  int32_t input_kind;      /* SDCAB_INPUT_FEATURES or SDCAB_INPUT_KERNEL            */
+  int32_t is_train;        /* 0: held-out set, only primal loss and accuracy        */
+  int64_t d;               /* num_dimensions, or num_train_examples for a kernel    */
+  int64_t n;               /* examples in this call (this rank's shard)             */
+  int64_t m;               /* classes                                               */
+  int64_t a_row_offset;    /* index of this shard's first example in A (train only) */
+  const void* x;           /* features or kernel columns of the n examples          */
+  const void* a;           /* dual variables (train sets, and kernel scores)        */
+  const void* w;           /* primal variables (features)                           */
+  const void* w0;          /* optional proximal centre W0 (features), or NULL       */
+  const int64_t* labels;
+  const int64_t* offsets;  /* multilabel only, n + 1 entries, offsets[0] == 0       */
+  int32_t include_primal_regularizer; /* sharded runs: set on one rank only          */
+  int32_t reserved;
+} sdcab_problem;
+
+/* Number of doubles in the sums vector of one evaluation: 8 scalars followed by
+ * the m rank counts. */
+#define SDCAB_EVAL_SUMS(m) (8 + (m))
+
+/* Bytes of device scratch sdcab_eval_sums_*_dev needs (the score tile and the
+ * per-block partial sums). */
+size_t sdcab_eval_workspace_bytes(int64_t n, int64_t m, int64_t elem_size);
+
+/*
+ * Sums of one evaluation over the n examples described by `p` (all pointers in
+ * p are device pointers): scores = W'x_i or A K_i for every example on the
+ * device, then per-example loss, conjugate and rank.  Replaces the loop of
+ * evaluate_dataset (include/sdca/solver/eval.h:15-51 with eval/scores.h,
+ * eval/regularizer.h, eval/dual.h, eval/primal.h).  sums_dev receives
+ * SDCAB_EVAL_SUMS(m) doubles:
+ *   [0] sum of primal losses (before the objective's coefficient)
+ *   [1] sum of dual losses   [2] primal regularizer   [3] dual regularizer
+ *   [4] sum of rank losses   [5] number of examples   [6], [7] unused
+ *   [8 + r] number of examples whose label is outranked by exactly r classes.
+ * Rows are independent, so shards of examples are evaluated separately and
+ * their sums added (one all-reduce over the ranks) before sdcab_eval_finish.
+ * workspace_dev must hold sdcab_eval_workspace_bytes(...) bytes; NULL lets the
+ * library use its own grow-only scratch (the first call then allocates).
+ */
+int sdcab_eval_sums_f32_dev(const sdcab_objective* obj, const sdcab_problem* p,
+                            double* sums_dev, void* workspace_dev,
+                            size_t workspace_bytes, void* stream);
+int sdcab_eval_sums_f64_dev(const sdcab_objective* obj, const sdcab_problem* p,
+                            double* sums_dev, void* workspace_dev,
+                            size_t workspace_bytes, void* stream);
+
+/* Turns summed-up sums (host memory) into the record: applies the objective's
+ * coefficient, forms primal / dual, normalises the accuracy histogram into
+ * cumulative top-k accuracies (include/sdca/solver/eval/core.h:43-132,
+ * objective/objective_base.h:108-128).  accuracy may be NULL. */
+int sdcab_eval_finish(const sdcab_objective* obj, int64_t m, const double* sums,
+                      sdcab_eval_record* record, double* accuracy);
+
+/* Whole evaluation with host buffers on the current device (copies inside). */
+int sdcab_eval_f32(const sdcab_objective* obj, const sdcab_problem* host_problem,
+                   sdcab_eval_record* record, double* accuracy);
+int sdcab_eval_f64(const sdcab_objective* obj, const sdcab_problem* host_problem,
+                   sdcab_eval_record* record, double* accuracy);
+
+/* scores (n x m, example i at scores + m*i) = W'x_i or A K_i, device pointers:
+ * the batched form of eval_scores (include/sdca/solver/eval/scores.h:9-47). */
+int sdcab_scores_f32_dev(const sdcab_problem* p, float* scores_dev, void* stream);
+int sdcab_scores_f64_dev(const sdcab_problem* p, double* scores_dev, void* stream);
+
 /* ------------------------------------------------------------- memory ---- */
 
 /* Page-locked host memory for callers that want the host-buffer entry points

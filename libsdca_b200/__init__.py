@@ -19,4 +19,9 @@ from .binding import (  # noqa: F401
     lambert_w_exp_,
     status_string,
     PROX_NAMES,
+    evaluate,
+    eval_sums_,
+    eval_finish,
+    make_objective,
+    make_problem,
 )

@@ -176,3 +176,120 @@ def lambert_w_exp_(x):
     flat = x.reshape(1, -1)
     prox_(flat, "lambert_w_exp")
     return x
+
+
+# ---------------------------------------------------------------- evaluation ----
+class Objective(C.Structure):
+    _fields_ = [("id", C.c_int32), ("precision", C.c_int32), ("c", C.c_double),
+                ("gamma", C.c_double), ("k", C.c_int64)]
+
+
+class EvalRecord(C.Structure):
+    _fields_ = [("primal", C.c_double), ("dual", C.c_double), ("primal_loss", C.c_double),
+                ("dual_loss", C.c_double), ("primal_regularizer", C.c_double),
+                ("dual_regularizer", C.c_double), ("rank_loss", C.c_double),
+                ("relative_gap", C.c_double)]
+
+
+class Problem(C.Structure):
+    _fields_ = [("input_kind", C.c_int32), ("is_train", C.c_int32), ("d", C.c_int64),
+                ("n", C.c_int64), ("m", C.c_int64), ("a_row_offset", C.c_int64),
+                ("x", C.c_void_p), ("a", C.c_void_p), ("w", C.c_void_p), ("w0", C.c_void_p),
+                ("labels", C.c_void_p), ("offsets", C.c_void_p),
+                ("include_primal_regularizer", C.c_int32), ("reserved", C.c_int32)]
+
+
+RECORD_FIELDS = ("primal", "dual", "primal_loss", "dual_loss", "primal_regularizer",
+                 "dual_regularizer", "rank_loss", "relative_gap")
+
+
+def make_objective(name, c=1.0, gamma=1.0, k=1, precision="double", from_name=None):
+    """Objective by the names matsdca_fit accepts (src/matlab/mex_solve.cpp:643-715)."""
+    o = Objective()
+    if isinstance(name, int):
+        # an objective class of the reference chosen directly (SDCAB_OBJ_* id)
+        o.id = name; o.c = c; o.gamma = gamma; o.k = int(k)
+        o.precision = {"double": 0, "single": 1, "float": 1}[precision]
+        return o
+    fn = from_name or lib().sdcab_objective_from_name
+    _check(fn(name.encode(), C.c_double(c), C.c_double(gamma), C.c_int64(k), C.byref(o)),
+           "sdcab_objective_from_name(%s)" % name)
+    o.precision = {"double": 0, "single": 1, "float": 1}[precision]
+    return o
+
+
+def _ptr_of(x):
+    if x is None:
+        return None
+    if _is_torch(x):
+        return x.data_ptr()
+    return x.ctypes.data
+
+
+def make_problem(X, labels, A=None, W=None, W0=None, offsets=None, kernel=False, is_train=True,
+                 a_row_offset=0, include_primal_regularizer=True):
+    """X: (n, d) rows = examples (features) or kernel columns; A: (n_train, m); W: (m, d)."""
+    n, d = X.shape
+    m = A.shape[1] if A is not None else W.shape[0]
+    p = Problem()
+    p.input_kind = 1 if kernel else 0
+    p.is_train = 1 if is_train else 0
+    p.d = d; p.n = n; p.m = m; p.a_row_offset = a_row_offset
+    p.x = _ptr_of(X); p.a = _ptr_of(A); p.w = _ptr_of(W); p.w0 = _ptr_of(W0)
+    p.labels = _ptr_of(labels); p.offsets = _ptr_of(offsets)
+    p.include_primal_regularizer = 1 if include_primal_regularizer else 0
+    p._keep = (X, labels, A, W, W0, offsets)
+    return p
+
+
+def record_to_dict(rec, acc):
+    out = {f: getattr(rec, f) for f in RECORD_FIELDS}
+    out["accuracy"] = acc
+    return out
+
+
+def evaluate(objective, X, labels, A=None, W=None, W0=None, offsets=None, kernel=False,
+             is_train=True, c=1.0, gamma=1.0, k=1, precision="double"):
+    """Like one evaluate_dataset of the reference: returns the evaluation record.
+
+    numpy inputs use the host-buffer entry point; torch CUDA tensors the device
+    one (sums on the device, finish on the host)."""
+    obj = objective if isinstance(objective, Objective) else make_objective(objective, c, gamma, k, precision)
+    prob = make_problem(X, labels, A, W, W0, offsets, kernel, is_train)
+    m = prob.m
+    rec = EvalRecord()
+    acc = np.zeros(m)
+    if _is_torch(X):
+        import torch
+        sums = torch.zeros(8 + m, dtype=torch.float64, device=X.device)
+        fn = getattr(lib(), "sdcab_eval_sums_%s_dev" % _suffix(str(X.dtype)))
+        _check(fn(C.byref(obj), C.byref(prob), C.c_void_p(sums.data_ptr()), None, C.c_size_t(0),
+                  _torch_stream()), "sdcab_eval_sums_dev")
+        host = sums.cpu().numpy()
+        _check(lib().sdcab_eval_finish(C.byref(obj), C.c_int64(m), host.ctypes.data_as(C.c_void_p),
+                                       C.byref(rec), acc.ctypes.data_as(C.c_void_p)),
+               "sdcab_eval_finish")
+    else:
+        fn = getattr(lib(), "sdcab_eval_%s" % _suffix(X.dtype.name))
+        _check(fn(C.byref(obj), C.byref(prob), C.byref(rec), acc.ctypes.data_as(C.c_void_p)),
+               "sdcab_eval")
+    return record_to_dict(rec, acc)
+
+
+def eval_sums_(objective, problem, sums, dtype_suffix, workspace=None, workspace_bytes=0):
+    """Device sums of one shard (torch tensors inside ``problem``); for sharded runs."""
+    fn = getattr(lib(), "sdcab_eval_sums_%s_dev" % dtype_suffix)
+    _check(fn(C.byref(objective), C.byref(problem), C.c_void_p(sums.data_ptr()),
+              C.c_void_p(workspace.data_ptr()) if workspace is not None else None,
+              C.c_size_t(workspace_bytes), _torch_stream()), "sdcab_eval_sums_dev")
+    return sums
+
+
+def eval_finish(objective, m, sums_host):
+    rec = EvalRecord()
+    acc = np.zeros(m)
+    sums_host = np.ascontiguousarray(sums_host, dtype=np.float64)
+    _check(lib().sdcab_eval_finish(C.byref(objective), C.c_int64(m),
+                                   sums_host.ctypes.data_as(C.c_void_p), C.byref(rec),
+                                   acc.ctypes.data_as(C.c_void_p)), "sdcab_eval_finish")
+    return record_to_dict(rec, acc)

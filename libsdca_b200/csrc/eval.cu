@@ -1,0 +1,626 @@
+// Objective / duality-gap evaluation on the device.
+//
+//   scores   S (n x m, example-major) = X' W   (features: both operands have the
+//            contraction index contiguous)  or  K' A' (kernel input), by a tiled
+//            register-blocked GEMM written here;
+//   losses   one warp per example: the score row is staged in shared memory and
+//            the objective's loss, conjugate and rank come from the threshold
+//            code of thresholds.cuh / losses.cuh; per-warp sums are combined per
+//            block in a fixed order and the block partials by a single-block
+//            kernel, so a run is reproducible bit for bit;
+//   record   eval_finish on the host (eval_host.h).
+//
+// Examples are processed in chunks so that the score tile stays a few hundred
+// megabytes whatever n is.  Replaces evaluate_dataset of the reference
+// (include/sdca/solver/eval.h:15-51).
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include "common_host.h"
+#include "eval_host.h"
+#include "losses.cuh"
+
+namespace sdcab {
+
+// ------------------------------------------------------------------ GEMM ----
+// C (M x N, row major) = A (M x K, row major) * op(B), with
+//   B_KMAJOR:  B is N x K row major  (C = A B')   -- scores = X' W
+//   otherwise: B is K x N row major  (C = A B)    -- scores = K' A'
+// Thread block tile BM x BN x BK, TM x TN outputs per thread, register
+// prefetch of the next tile while the current one is consumed from shared
+// memory.  Arithmetic is plain FMA in the data type, accumulating over the
+// contraction index in increasing order, like a reference BLAS gemv.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> { typedef float4 type; };
+template <> struct Vec16<double> { typedef double2 type; };
+
+// Loads this thread's share of a rows x BK tile whose contraction index is
+// contiguous in memory (16-byte vectors where alignment allows, zero fill past
+// the edges).
+template <typename T, int BK, int NT, int PER>
+__device__ __forceinline__ void load_kmajor_tile(const T* __restrict__ base, long long ld,
+                                                 int rows_total, int K, int r0, int k0,
+                                                 int vec_ok, int tid, T (&dst)[PER][16 / sizeof(T)]) {
+  constexpr int V = 16 / sizeof(T);
+  typedef typename Vec16<T>::type Vec;
+#pragma unroll
+  for (int it = 0; it < PER; ++it) {
+    const int idx = tid + it * NT;
+    const int r = idx / (BK / V), kv = (idx % (BK / V)) * V;
+    const int gr = r0 + r, gk = k0 + kv;
+    if (gr < rows_total && vec_ok && gk + V <= K) {
+      const Vec v = *reinterpret_cast<const Vec*>(base + static_cast<long long>(gr) * ld + gk);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int c = 0; c < V; ++c) dst[it][c] = e[c];
+    } else {
+#pragma unroll
+      for (int c = 0; c < V; ++c)
+        dst[it][c] = (gr < rows_total && gk + c < K) ? base[static_cast<long long>(gr) * ld + gk + c] : T(0);
+    }
+  }
+}
+
+template <typename T, int BM, int BN, int BK, int TM, int TN, bool B_KMAJOR>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int M, int N,
+            int K, long long lda, long long ldb, long long ldc, int a_vec, int b_vec, int c_vec) {
+  constexpr int NT = (BM / TM) * (BN / TN);
+  constexpr int V = 16 / sizeof(T);
+  constexpr int PAD = V;
+  typedef typename Vec16<T>::type Vec;
+  __shared__ __align__(16) T As[2][BK][BM + PAD];
+  __shared__ __align__(16) T Bs[2][BK][BN + PAD];
+  const int tid = threadIdx.x;
+  const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+  const int row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+
+  constexpr int A_PER = (BM * BK / V) / NT;
+  constexpr int B_PER = (BN * BK / V) / NT;
+  static_assert(A_PER >= 1 && B_PER >= 1, "tile too small for the thread count");
+  T ra[A_PER][V], rb[B_PER][V];
+
+  auto load_b_nmajor = [&](int k0) {
+#pragma unroll
+    for (int it = 0; it < B_PER; ++it) {
+      const int idx = tid + it * NT;
+      const int kk = idx / (BN / V), nv = (idx % (BN / V)) * V;
+      const int gk = k0 + kk, gn = col0 + nv;
+      if (gk < K && b_vec && gn + V <= N) {
+        const Vec v = *reinterpret_cast<const Vec*>(B + static_cast<long long>(gk) * ldb + gn);
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int c = 0; c < V; ++c) rb[it][c] = e[c];
+      } else {
+#pragma unroll
+        for (int c = 0; c < V; ++c)
+          rb[it][c] = (gk < K && gn + c < N) ? B[static_cast<long long>(gk) * ldb + gn + c] : T(0);
+      }
+    }
+  };
+  auto store_tiles = [&](int buf) {
+#pragma unroll
+    for (int it = 0; it < A_PER; ++it) {
+      const int idx = tid + it * NT;
+      const int r = idx / (BK / V), kv = (idx % (BK / V)) * V;
+#pragma unroll
+      for (int c = 0; c < V; ++c) As[buf][kv + c][r] = ra[it][c];
+    }
+#pragma unroll
+    for (int it = 0; it < B_PER; ++it) {
+      const int idx = tid + it * NT;
+      if (B_KMAJOR) {
+        const int r = idx / (BK / V), kv = (idx % (BK / V)) * V;
+#pragma unroll
+        for (int c = 0; c < V; ++c) Bs[buf][kv + c][r] = rb[it][c];
+      } else {
+        const int kk = idx / (BN / V), nv = (idx % (BN / V)) * V;
+#pragma unroll
+        for (int c = 0; c < V; ++c) Bs[buf][kk][nv + c] = rb[it][c];
+      }
+    }
+  };
+  auto load_tiles = [&](int k0) {
+    load_kmajor_tile<T, BK, NT, A_PER>(A, lda, M, K, row0, k0, a_vec, tid, ra);
+    if (B_KMAJOR) load_kmajor_tile<T, BK, NT, B_PER>(B, ldb, N, K, col0, k0, b_vec, tid, rb);
+    else load_b_nmajor(k0);
+  };
+
+  T acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = T(0);
+
+  constexpr int HM = TM / 2, HN = TN / 2;  // each thread owns two strips per dimension
+  load_tiles(0);
+  store_tiles(0);
+  __syncthreads();
+  const int ktiles = (K + BK - 1) / BK;
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < ktiles) load_tiles((kt + 1) * BK);
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      T a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < HM; ++i) {
+        a[i] = As[buf][kk][ty * HM + i];
+        a[HM + i] = As[buf][kk][BM / 2 + ty * HM + i];
+      }
+#pragma unroll
+      for (int j = 0; j < HN; ++j) {
+        b[j] = Bs[buf][kk][tx * HN + j];
+        b[HN + j] = Bs[buf][kk][BN / 2 + tx * HN + j];
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+    }
+    if (kt + 1 < ktiles) {
+      store_tiles(buf ^ 1);
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = row0 + ((i < HM) ? ty * HM + i : BM / 2 + ty * HM + (i - HM));
+    if (r >= M) continue;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c0 = col0 + (h ? BN / 2 : 0) + tx * HN;
+      T* dst = C + static_cast<long long>(r) * ldc + c0;
+      if (c_vec && HN == V && c0 + HN <= N) {
+        Vec v;
+        T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+        for (int j = 0; j < HN; ++j) e[j] = acc[i][h * HN + j];
+        *reinterpret_cast<Vec*>(dst) = v;
+      } else {
+#pragma unroll
+        for (int j = 0; j < HN; ++j)
+          if (c0 + j < N) dst[j] = acc[i][h * HN + j];
+      }
+    }
+  }
+}
+
+template <typename T> struct GemmTile;
+template <> struct GemmTile<float> { static constexpr int BM = 128, BN = 128, BK = 16, TM = 8, TN = 8; };
+template <> struct GemmTile<double> { static constexpr int BM = 64, BN = 64, BK = 8, TM = 4, TN = 4; };
+
+template <typename T>
+int launch_gemm(const T* A, const T* B, T* C, int M, int N, int K, long long lda, long long ldb,
+                long long ldc, bool b_kmajor, cudaStream_t stream) {
+  typedef GemmTile<T> G;
+  constexpr int V = 16 / sizeof(T);
+  auto aligned = [&](const void* p, long long ld) {
+    return ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && ld % V == 0) ? 1 : 0;
+  };
+  const int a_vec = aligned(A, lda), b_vec = aligned(B, ldb), c_vec = aligned(C, ldc);
+  dim3 grid((N + G::BN - 1) / G::BN, (M + G::BM - 1) / G::BM);
+  const int threads = (G::BM / G::TM) * (G::BN / G::TN);
+  if (b_kmajor)
+    gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, true><<<grid, threads, 0, stream>>>(
+        A, B, C, M, N, K, lda, ldb, ldc, a_vec, b_vec, c_vec);
+  else
+    gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, false><<<grid, threads, 0, stream>>>(
+        A, B, C, M, N, K, lda, ldb, ldc, a_vec, b_vec, c_vec);
+  SDCAB_CUDA_TRY(cudaGetLastError());
+  return SDCAB_OK;
+}
+
+// ---------------------------------------------------------------- losses ----
+constexpr int kLossThreads = 128;
+constexpr int kHistLocal = 256;  // ranks below this are counted per block first
+
+struct LossArgs {
+  ObjectiveParams obj;
+  int m;
+  long long n;             // examples in this chunk
+  long long first;         // index of the chunk's first example within the call
+  long long a_row_offset;  // index of the call's first example within A
+  const long long* labels;
+  const long long* offsets;
+  int is_train, kernel_input;
+  int m_pad, mask_words;
+};
+
+// block_partials[block][0..3] = primal loss, dual loss, dual regulariser term
+// (0.5 <a_i, scores_i>, kernel input), rank loss; hist[r] += examples of rank r.
+template <typename Data, typename R>
+__global__ void __launch_bounds__(kLossThreads)
+eval_loss_kernel(LossArgs g, const Data* __restrict__ scores, const Data* __restrict__ A,
+                 double* __restrict__ block_partials, unsigned long long* __restrict__ hist) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ double warp_sums[kLossThreads / 32][4];
+  __shared__ unsigned int local_hist[kHistLocal];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = kLossThreads / 32;
+  Data* srow = reinterpret_cast<Data*>(smem_raw) + static_cast<size_t>(warp) * g.m_pad;
+  unsigned* mask = reinterpret_cast<unsigned*>(reinterpret_cast<Data*>(smem_raw) +
+                                               static_cast<size_t>(warps) * g.m_pad) +
+                   static_cast<size_t>(warp) * g.mask_words;
+  for (int i = threadIdx.x; i < kHistLocal; i += kLossThreads) local_hist[i] = 0;
+  __syncthreads();
+  const bool ml = objective_is_multilabel(g.obj.id);
+  const int m = g.m;
+  double primal = 0, dual = 0, reg = 0, rank_loss = 0;
+  for (long long e = static_cast<long long>(blockIdx.x) * warps + warp; e < g.n;
+       e += static_cast<long long>(gridDim.x) * warps) {
+    const Data* s_g = scores + e * m;
+    for (int i = lane; i < m; i += 32) srow[i] = s_g[i];
+    const long long ex = g.first + e;  // example index within the call
+    const Data* a = (g.is_train && A) ? A + (g.a_row_offset + ex) * m : nullptr;
+    __syncwarp();
+    if (!ml) {
+      const int y = static_cast<int>(g.labels[ex]);
+      int rank;
+      primal += static_cast<double>(multiclass_primal_loss<R, Data>(g.obj, srow, m, y, rank));
+      if (lane == 0) {
+        if (rank < kHistLocal) atomicAdd(&local_hist[rank], 1u);
+        else atomicAdd(&hist[rank], 1ull);
+      }
+      if (a) dual += static_cast<double>(multiclass_dual_loss<R, Data>(g.obj, a, m, y));
+    } else {
+      const long long off = g.offsets[ex];
+      const int nl = static_cast<int>(g.offsets[ex + 1] - off);
+      for (int w = lane; w < g.mask_words; w += 32) mask[w] = 0u;
+      __syncwarp();
+      for (int q = lane; q < nl; q += 32) {
+        const int c = static_cast<int>(g.labels[off + q]);
+        atomicOr(&mask[c >> 5], 1u << (c & 31));
+      }
+      __syncwarp();
+      R rl;
+      primal += static_cast<double>(
+          multilabel_primal_loss<R, Data>(g.obj, srow, m, mask, g.labels + off, nl, rl));
+      rank_loss += static_cast<double>(rl);
+      if (a) dual += static_cast<double>(multilabel_dual_loss<R, Data>(g.obj, a, m, mask, nl));
+    }
+    if (a && g.kernel_input) {
+      // 0.5 <a_i, scores_i>: eval/regularizer.h:82-98, objective_base.h:92-105
+      R dot = 0;
+      for (int i = lane; i < m; i += 32) dot += static_cast<R>(a[i]) * static_cast<R>(srow[i]);
+      reg += static_cast<double>(warp_sum(dot)) * 0.5;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    warp_sums[warp][0] = primal; warp_sums[warp][1] = dual;
+    warp_sums[warp][2] = reg; warp_sums[warp][3] = rank_loss;
+  }
+  __syncthreads();
+  if (threadIdx.x < 4) {
+    double s = 0;
+    for (int w = 0; w < warps; ++w) s += warp_sums[w][threadIdx.x];
+    block_partials[static_cast<size_t>(blockIdx.x) * 4 + threadIdx.x] = s;
+  }
+  for (int i = threadIdx.x; i < kHistLocal && i < m; i += kLossThreads)
+    if (local_hist[i]) atomicAdd(&hist[i], static_cast<unsigned long long>(local_hist[i]));
+}
+
+// sums[0..3] += block partials in block order (one block, fixed order)
+__global__ void combine_partials_kernel(const double* __restrict__ partials, int blocks,
+                                        double* __restrict__ sums) {
+  const int t = threadIdx.x;
+  if (t < 4) {
+    double s = 0;
+    for (int b = 0; b < blocks; ++b) s += partials[static_cast<size_t>(b) * 4 + t];
+    // [0] primal loss, [1] dual loss, [2]+[3] regularisers, [4] rank loss
+    if (t == 0) sums[0] += s;
+    if (t == 1) sums[1] += s;
+    if (t == 2) { sums[2] += s; sums[3] += s; }
+    if (t == 3) sums[4] += s;
+  }
+}
+
+__global__ void hist_to_sums_kernel(const unsigned long long* __restrict__ hist, int m,
+                                    double* __restrict__ sums) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < m; i += gridDim.x * blockDim.x)
+    sums[8 + i] = static_cast<double>(hist[i]);
+}
+
+// 0.5 <W, W> and <W0, W> with double accumulation: two-stage, fixed order.
+template <typename Data>
+__global__ void __launch_bounds__(256)
+dot_partials_kernel(const Data* __restrict__ w, const Data* __restrict__ w0, long long count,
+                    double* __restrict__ partials) {
+  __shared__ double sh[2][256];
+  double ww = 0, w0w = 0;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const double v = static_cast<double>(w[i]);
+    ww += v * v;
+    if (w0) w0w += static_cast<double>(w0[i]) * v;
+  }
+  sh[0][threadIdx.x] = ww; sh[1][threadIdx.x] = w0w;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      sh[0][threadIdx.x] += sh[0][threadIdx.x + o];
+      sh[1][threadIdx.x] += sh[1][threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    partials[2 * blockIdx.x] = sh[0][0];
+    partials[2 * blockIdx.x + 1] = sh[1][0];
+  }
+}
+
+// eval/regularizer.h:22-63 with objective_base.h:59-89
+__global__ void regularizer_combine_kernel(const double* __restrict__ partials, int blocks,
+                                           int has_w0, double* __restrict__ sums) {
+  if (threadIdx.x == 0) {
+    double ww = 0, w0w = 0;
+    for (int b = 0; b < blocks; ++b) { ww += partials[2 * b]; w0w += partials[2 * b + 1]; }
+    const double regul = ww / 2;
+    sums[2] += has_w0 ? regul - w0w : regul;
+    sums[3] += regul;
+  }
+}
+
+__global__ void set_count_kernel(double* sums, double n) {
+  if (threadIdx.x == 0) sums[5] = n;
+}
+
+// ----------------------------------------------------------------- layout ----
+struct EvalLayout {
+  long long chunk;       // examples per chunk
+  size_t scores_bytes;   // chunk * m * elem, rounded up
+  int max_blocks;
+  size_t partials_bytes, hist_bytes, total;
+};
+
+static EvalLayout eval_layout(long long n, long long m, long long elem, int sm_count) {
+  EvalLayout L;
+  const long long budget = 256LL << 20;
+  long long chunk = std::max<long long>(128, budget / std::max<long long>(1, m * elem));
+  // test hook: a small chunk exercises the chunk loop on small problems
+  if (const char* env = std::getenv("SDCAB_EVAL_CHUNK")) {
+    const long long forced = std::atoll(env);
+    if (forced > 0) chunk = forced;
+  }
+  chunk = std::min(chunk, std::max<long long>(n, 1));
+  L.chunk = chunk;
+  L.scores_bytes = (static_cast<size_t>(chunk) * m * elem + 255) & ~static_cast<size_t>(255);
+  L.max_blocks = std::max(1, sm_count) * 16;
+  L.partials_bytes = (static_cast<size_t>(L.max_blocks) * 4 * sizeof(double) + 255) & ~static_cast<size_t>(255);
+  L.hist_bytes = (static_cast<size_t>(m) * sizeof(unsigned long long) + 255) & ~static_cast<size_t>(255);
+  L.total = L.scores_bytes + L.partials_bytes + L.hist_bytes;
+  return L;
+}
+
+static int check_problem(const sdcab_objective* obj, const sdcab_problem* p) {
+  if (!obj || !p) return SDCAB_ERR_ARG;
+  if (p->n <= 0 || p->m <= 0 || p->d <= 0) return SDCAB_ERR_NOT_EMPTY;
+  if (p->m > 0x7fffffffLL || p->d > 0x7fffffffLL) return SDCAB_ERR_TOO_LARGE;
+  if (p->m < 2) return SDCAB_ERR_NUM_DIM;
+  int rc = check_objective(obj, p->m);
+  if (rc) return rc;
+  if (!p->x || !p->labels) return SDCAB_ERR_ARG;
+  if (p->input_kind == SDCAB_INPUT_FEATURES) {
+    if (!p->w) return SDCAB_ERR_ARG;
+  } else if (p->input_kind == SDCAB_INPUT_KERNEL) {
+    if (!p->a) return SDCAB_ERR_ARG;
+  } else {
+    return SDCAB_ERR_ARG;
+  }
+  if (p->is_train && !p->a) return SDCAB_ERR_ARG;
+  if (objective_is_multilabel(obj->id) && !p->offsets) return SDCAB_ERR_ARG;
+  return SDCAB_OK;
+}
+
+// scores of examples [first, first + count) into `out` (count x m)
+template <typename Data>
+int scores_chunk(const sdcab_problem* p, long long first, long long count, Data* out,
+                 cudaStream_t stream) {
+  const Data* X = static_cast<const Data*>(p->x) + first * p->d;
+  const int M = static_cast<int>(count), N = static_cast<int>(p->m), K = static_cast<int>(p->d);
+  if (p->input_kind == SDCAB_INPUT_FEATURES) {
+    // S[i][j] = sum_l X[i][l] W[j][l]   (eval/scores.h:9-26)
+    return launch_gemm<Data>(X, static_cast<const Data*>(p->w), out, M, N, K, p->d, p->d, p->m,
+                             true, stream);
+  }
+  // S[i][j] = sum_l K[i][l] A[l][j]     (eval/scores.h:30-47)
+  return launch_gemm<Data>(X, static_cast<const Data*>(p->a), out, M, N, K, p->d, p->m, p->m,
+                           false, stream);
+}
+
+template <typename Data>
+int eval_sums_dev(const sdcab_objective* obj, const sdcab_problem* p, double* sums,
+                  void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  int rc = check_problem(obj, p);
+  if (rc) return rc;
+  if (!sums) return SDCAB_ERR_ARG;
+  DeviceInfo info;
+  rc = get_device_info(&info);
+  if (rc) return rc;
+  const long long m = p->m, n = p->n;
+  const EvalLayout L = eval_layout(n, m, sizeof(Data), info.sm_count);
+  if (!workspace) {
+    rc = workspace_reserve(2, L.total, &workspace);
+    if (rc) return rc;
+  } else if (workspace_bytes < L.total) {
+    return SDCAB_ERR_ARG_RANGE;
+  }
+  unsigned char* base = static_cast<unsigned char*>(workspace);
+  Data* scores = reinterpret_cast<Data*>(base);
+  double* partials = reinterpret_cast<double*>(base + L.scores_bytes);
+  unsigned long long* hist = reinterpret_cast<unsigned long long*>(base + L.scores_bytes + L.partials_bytes);
+
+  SDCAB_CUDA_TRY(cudaMemsetAsync(sums, 0, sizeof(double) * SDCAB_EVAL_SUMS(m), stream));
+  SDCAB_CUDA_TRY(cudaMemsetAsync(hist, 0, sizeof(unsigned long long) * m, stream));
+  set_count_kernel<<<1, 32, 0, stream>>>(sums, static_cast<double>(n));
+
+  if (p->is_train && p->input_kind == SDCAB_INPUT_FEATURES && p->include_primal_regularizer) {
+    const long long count = p->d * m;
+    const int blocks = static_cast<int>(std::min<long long>(L.max_blocks / 2, (count + 255) / 256));
+    dot_partials_kernel<Data><<<blocks, 256, 0, stream>>>(
+        static_cast<const Data*>(p->w), static_cast<const Data*>(p->w0), count, partials);
+    regularizer_combine_kernel<<<1, 32, 0, stream>>>(partials, blocks, p->w0 ? 1 : 0, sums);
+  }
+
+  LossArgs g;
+  g.obj = to_params(obj);
+  g.m = static_cast<int>(m);
+  g.a_row_offset = p->a_row_offset;
+  g.labels = reinterpret_cast<const long long*>(p->labels);
+  g.offsets = reinterpret_cast<const long long*>(p->offsets);
+  g.is_train = p->is_train;
+  g.kernel_input = (p->input_kind == SDCAB_INPUT_KERNEL);
+  g.m_pad = static_cast<int>((m + 15) & ~15LL);
+  g.mask_words = static_cast<int>((m + 31) / 32);
+  const int warps = kLossThreads / 32;
+  const size_t smem = static_cast<size_t>(warps) * g.m_pad * sizeof(Data) +
+                      static_cast<size_t>(warps) * g.mask_words * sizeof(unsigned);
+  if (smem > info.smem_optin) return SDCAB_ERR_TOO_LARGE;
+  const bool fl = (obj->precision == SDCAB_PRECISION_FLOAT);
+  auto kd = eval_loss_kernel<Data, double>;
+  auto kf = eval_loss_kernel<Data, float>;
+  if (smem > 48 * 1024) {
+    SDCAB_CUDA_TRY(cudaFuncSetAttribute(kd, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    SDCAB_CUDA_TRY(cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  }
+  for (long long first = 0; first < n; first += L.chunk) {
+    const long long count = std::min(L.chunk, n - first);
+    rc = scores_chunk<Data>(p, first, count, scores, stream);
+    if (rc) return rc;
+    g.n = count; g.first = first;
+    const int blocks = static_cast<int>(std::max<long long>(
+        1, std::min<long long>(L.max_blocks, (count + warps - 1) / warps)));
+    const Data* A = static_cast<const Data*>(p->a);
+    if (fl) kf<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+    else kd<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+    combine_partials_kernel<<<1, 32, 0, stream>>>(partials, blocks, sums);
+  }
+  hist_to_sums_kernel<<<std::max(1, static_cast<int>((m + 255) / 256)), 256, 0, stream>>>(
+      hist, static_cast<int>(m), sums);
+  SDCAB_CUDA_TRY(cudaGetLastError());
+  return SDCAB_OK;
+}
+
+// Host buffers: examples are uploaded chunk by chunk; W (or A for a kernel
+// input) stays on the device for the whole call.
+template <typename Data>
+int eval_host(const sdcab_objective* obj, const sdcab_problem* hp, sdcab_eval_record* rec,
+              double* accuracy) {
+  int rc = check_problem(obj, hp);
+  if (rc) return rc;
+  if (!rec) return SDCAB_ERR_ARG;
+  const long long m = hp->m, n = hp->n, d = hp->d;
+  const bool kernel = (hp->input_kind == SDCAB_INPUT_KERNEL);
+  const bool ml = objective_is_multilabel(obj->id);
+  const long long n_a = kernel ? d : n;  // rows of A that matter
+  const size_t elem = sizeof(Data);
+  long long chunk = std::max<long long>(1, (128LL << 20) / std::max<long long>(1, d * static_cast<long long>(elem)));
+  chunk = std::min(chunk, n);
+  const long long num_labels = ml ? hp->offsets[n] : n;
+  const size_t sums_count = SDCAB_EVAL_SUMS(m);
+  void *dX = nullptr, *dA = nullptr, *dW = nullptr, *dW0 = nullptr, *dLab = nullptr,
+       *dOff = nullptr, *dSums = nullptr;
+  auto release = [&]() {
+    cudaFree(dX); cudaFree(dA); cudaFree(dW); cudaFree(dW0); cudaFree(dLab); cudaFree(dOff);
+    cudaFree(dSums);
+  };
+#define EVAL_TRY(expr)                                                   \
+  do {                                                                   \
+    cudaError_t e__ = (expr);                                            \
+    if (e__ != cudaSuccess) { release(); return record_cuda_error(e__, #expr); } \
+  } while (0)
+  EVAL_TRY(cudaMalloc(&dX, static_cast<size_t>(chunk) * d * elem));
+  if (hp->a) {
+    EVAL_TRY(cudaMalloc(&dA, static_cast<size_t>(n_a) * m * elem));
+    EVAL_TRY(cudaMemcpy(dA, hp->a, static_cast<size_t>(n_a) * m * elem, cudaMemcpyHostToDevice));
+  }
+  if (hp->w) {
+    EVAL_TRY(cudaMalloc(&dW, static_cast<size_t>(d) * m * elem));
+    EVAL_TRY(cudaMemcpy(dW, hp->w, static_cast<size_t>(d) * m * elem, cudaMemcpyHostToDevice));
+  }
+  if (hp->w0) {
+    EVAL_TRY(cudaMalloc(&dW0, static_cast<size_t>(d) * m * elem));
+    EVAL_TRY(cudaMemcpy(dW0, hp->w0, static_cast<size_t>(d) * m * elem, cudaMemcpyHostToDevice));
+  }
+  EVAL_TRY(cudaMalloc(&dLab, static_cast<size_t>(num_labels) * sizeof(int64_t)));
+  EVAL_TRY(cudaMemcpy(dLab, hp->labels, static_cast<size_t>(num_labels) * sizeof(int64_t), cudaMemcpyHostToDevice));
+  if (ml) {
+    EVAL_TRY(cudaMalloc(&dOff, static_cast<size_t>(n + 1) * sizeof(int64_t)));
+    EVAL_TRY(cudaMemcpy(dOff, hp->offsets, static_cast<size_t>(n + 1) * sizeof(int64_t), cudaMemcpyHostToDevice));
+  }
+  EVAL_TRY(cudaMalloc(&dSums, sums_count * sizeof(double)));
+  std::vector<double> total(sums_count, 0.0), part(sums_count);
+  for (long long first = 0; first < n; first += chunk) {
+    const long long count = std::min(chunk, n - first);
+    EVAL_TRY(cudaMemcpy(dX, static_cast<const Data*>(hp->x) + first * d,
+                        static_cast<size_t>(count) * d * elem, cudaMemcpyHostToDevice));
+    sdcab_problem dp = *hp;
+    dp.x = dX; dp.a = dA; dp.w = dW; dp.w0 = dW0;
+    dp.n = count;
+    dp.a_row_offset = hp->a_row_offset + first;
+    dp.labels = ml ? static_cast<const int64_t*>(dLab)
+                   : static_cast<const int64_t*>(dLab) + first;
+    dp.offsets = ml ? static_cast<const int64_t*>(dOff) + first : nullptr;
+    dp.include_primal_regularizer = (first == 0) ? 1 : 0;
+    rc = eval_sums_dev<Data>(obj, &dp, static_cast<double*>(dSums), nullptr, 0, nullptr);
+    if (rc) { release(); return rc; }
+    EVAL_TRY(cudaMemcpy(part.data(), dSums, sums_count * sizeof(double), cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < sums_count; ++i) total[i] += part[i];
+  }
+#undef EVAL_TRY
+  release();
+  return eval_finish(obj, m, total.data(), rec, accuracy);
+}
+
+}  // namespace sdcab
+
+extern "C" {
+
+int sdcab_objective_from_name(const char* name, double c, double gamma, int64_t k,
+                              sdcab_objective* out) {
+  return sdcab::objective_from_name(name, c, gamma, k, out);
+}
+
+size_t sdcab_eval_workspace_bytes(int64_t n, int64_t m, int64_t elem_size) {
+  sdcab::DeviceInfo info;
+  int sm = 148;
+  if (sdcab::get_device_info(&info) == SDCAB_OK) sm = info.sm_count;
+  return sdcab::eval_layout(n, m, elem_size, sm).total;
+}
+
+int sdcab_eval_sums_f32_dev(const sdcab_objective* obj, const sdcab_problem* p, double* sums,
+                            void* ws, size_t ws_bytes, void* stream) {
+  return sdcab::eval_sums_dev<float>(obj, p, sums, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+int sdcab_eval_sums_f64_dev(const sdcab_objective* obj, const sdcab_problem* p, double* sums,
+                            void* ws, size_t ws_bytes, void* stream) {
+  return sdcab::eval_sums_dev<double>(obj, p, sums, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int sdcab_eval_finish(const sdcab_objective* obj, int64_t m, const double* sums,
+                      sdcab_eval_record* rec, double* accuracy) {
+  return sdcab::eval_finish(obj, m, sums, rec, accuracy);
+}
+
+int sdcab_eval_f32(const sdcab_objective* obj, const sdcab_problem* hp, sdcab_eval_record* rec,
+                   double* accuracy) {
+  return sdcab::eval_host<float>(obj, hp, rec, accuracy);
+}
+int sdcab_eval_f64(const sdcab_objective* obj, const sdcab_problem* hp, sdcab_eval_record* rec,
+                   double* accuracy) {
+  return sdcab::eval_host<double>(obj, hp, rec, accuracy);
+}
+
+int sdcab_scores_f32_dev(const sdcab_problem* p, float* scores, void* stream) {
+  if (!p || !scores || !p->x) return SDCAB_ERR_ARG;
+  return sdcab::scores_chunk<float>(p, 0, p->n, scores, static_cast<cudaStream_t>(stream));
+}
+int sdcab_scores_f64_dev(const sdcab_problem* p, double* scores, void* stream) {
+  if (!p || !scores || !p->x) return SDCAB_ERR_ARG;
+  return sdcab::scores_chunk<double>(p, 0, p->n, scores, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -39,5 +39,25 @@ class HostSim:
         return a, thr
 
 
+    def evaluate(self, objective, X, labels, A=None, W=None, W0=None, offsets=None, kernel=False,
+                 is_train=True, c=1.0, gamma=1.0, k=1, precision="double"):
+        from libsdca_b200 import binding as b
+        obj = b.make_objective(objective, c, gamma, k, precision,
+                               from_name=self.lib.sdcab_hostsim_objective_from_name)
+        prob = b.make_problem(X, labels, A, W, W0, offsets, kernel, is_train)
+        m = prob.m
+        sums = np.zeros(8 + m)
+        rc = self.lib.sdcab_hostsim_eval(C.byref(obj), C.byref(prob),
+                                         0 if X.dtype == np.float32 else 1,
+                                         sums.ctypes.data_as(C.c_void_p))
+        assert rc == 0, rc
+        rec = b.EvalRecord(); acc = np.zeros(m)
+        rc = self.lib.sdcab_hostsim_eval_finish(C.byref(obj), C.c_int64(m),
+                                                sums.ctypes.data_as(C.c_void_p), C.byref(rec),
+                                                acc.ctypes.data_as(C.c_void_p))
+        assert rc == 0, rc
+        return b.record_to_dict(rec, acc)
+
+
 def load():
     return HostSim()

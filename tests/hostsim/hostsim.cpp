@@ -62,3 +62,90 @@ extern "C" int sdcab_hostsim_prox(const char* name, int dtype, void* a, int64_t 
   return f ? run<double, float>(prox, (double*)a, m, n, q, thr, apply)
            : run<double, double>(prox, (double*)a, m, n, q, thr, apply);
 }
+
+// ---- evaluation: the per-example loss code of losses.cuh with one lane -------
+#include <vector>
+
+#include "../../libsdca_b200/csrc/eval_host.h"
+
+namespace {
+
+template <typename Data, typename R>
+int run_eval(const sdcab_objective* obj, const sdcab_problem* p, double* sums) {
+  using namespace sdcab;
+  const ObjectiveParams q = to_params(obj);
+  const int m = static_cast<int>(p->m);
+  const long long n = p->n, d = p->d;
+  const Data* X = static_cast<const Data*>(p->x);
+  const Data* A = static_cast<const Data*>(p->a);
+  const Data* W = static_cast<const Data*>(p->w);
+  const Data* W0 = static_cast<const Data*>(p->w0);
+  for (int i = 0; i < SDCAB_EVAL_SUMS(m); ++i) sums[i] = 0;
+  sums[5] = static_cast<double>(n);
+  if (p->is_train && p->input_kind == SDCAB_INPUT_FEATURES && p->include_primal_regularizer) {
+    double ww = 0, w0w = 0;
+    for (long long i = 0; i < d * m; ++i) {
+      ww += double(W[i]) * double(W[i]);
+      if (W0) w0w += double(W0[i]) * double(W[i]);
+    }
+    sums[2] += W0 ? ww / 2 - w0w : ww / 2;
+    sums[3] += ww / 2;
+  }
+  std::vector<Data> s(m);
+  std::vector<unsigned> mask((m + 31) / 32);
+  const bool ml = objective_is_multilabel(q.id);
+  for (long long e = 0; e < n; ++e) {
+    for (int j = 0; j < m; ++j) {
+      Data acc = 0;
+      if (p->input_kind == SDCAB_INPUT_FEATURES) {
+        for (long long l = 0; l < d; ++l) acc = std::fma(X[e * d + l], W[j * d + l], acc);
+      } else {
+        for (long long l = 0; l < d; ++l) acc = std::fma(X[e * d + l], A[l * m + j], acc);
+      }
+      s[j] = acc;
+    }
+    const Data* a = (p->is_train && A) ? A + (p->a_row_offset + e) * m : nullptr;
+    if (!ml) {
+      const int y = static_cast<int>(p->labels[e]);
+      int rank;
+      sums[0] += double(multiclass_primal_loss<R, Data>(q, s.data(), m, y, rank));
+      sums[8 + rank] += 1;
+      if (a) sums[1] += double(multiclass_dual_loss<R, Data>(q, a, m, y));
+    } else {
+      const long long off = p->offsets[e];
+      const int nl = static_cast<int>(p->offsets[e + 1] - off);
+      std::fill(mask.begin(), mask.end(), 0u);
+      for (int g = 0; g < nl; ++g) mask[p->labels[off + g] >> 5] |= 1u << (p->labels[off + g] & 31);
+      R rl;
+      sums[0] += double(multilabel_primal_loss<R, Data>(
+          q, s.data(), m, mask.data(), reinterpret_cast<const long long*>(p->labels + off), nl, rl));
+      sums[4] += double(rl);
+      if (a) sums[1] += double(multilabel_dual_loss<R, Data>(q, a, m, mask.data(), nl));
+    }
+    if (a && p->input_kind == SDCAB_INPUT_KERNEL) {
+      R dot = 0;
+      for (int j = 0; j < m; ++j) dot += R(a[j]) * R(s[j]);
+      sums[2] += double(dot) * 0.5; sums[3] += double(dot) * 0.5;
+    }
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int sdcab_hostsim_eval(const sdcab_objective* obj, const sdcab_problem* p, int dtype,
+                                  double* sums) {
+  const bool f = (obj->precision == SDCAB_PRECISION_FLOAT);
+  if (dtype == 0) return f ? run_eval<float, float>(obj, p, sums) : run_eval<float, double>(obj, p, sums);
+  return f ? run_eval<double, float>(obj, p, sums) : run_eval<double, double>(obj, p, sums);
+}
+
+extern "C" int sdcab_hostsim_eval_finish(const sdcab_objective* obj, int64_t m, const double* sums,
+                                         sdcab_eval_record* rec, double* acc) {
+  return sdcab::eval_finish(obj, m, sums, rec, acc);
+}
+
+extern "C" int sdcab_hostsim_objective_from_name(const char* name, double c, double gamma,
+                                                 int64_t k, sdcab_objective* out) {
+  return sdcab::objective_from_name(name, c, gamma, k, out);
+}

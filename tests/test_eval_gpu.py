@@ -1,0 +1,137 @@
+"""Parity of the device evaluation (score GEMM + loss kernels, through the C ABI)
+with the reference's evaluate_dataset, term by term."""
+import os
+
+import numpy as np
+import pytest
+
+from tests.golden_util import eval_cases
+from tests.test_oracle_restatement import OBJECTIVES, random_problem
+from tests.util import stable_seed
+
+pytestmark = pytest.mark.gpu
+
+FIELDS = ("primal", "dual", "primal_loss", "dual_loss", "primal_regularizer",
+          "dual_regularizer", "rank_loss")
+
+
+def compare(rec, ref_rec, tol, what=""):
+    for f in FIELDS:
+        assert abs(rec[f] - ref_rec[f]) <= tol * max(1, abs(ref_rec[f])), (what, f, rec[f], ref_rec[f])
+    assert np.allclose(rec["accuracy"], ref_rec["accuracy"], atol=1e-12), what
+
+
+def dev(x):
+    import torch
+    return None if x is None else torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def gpu_eval(mod, objective, X, labels, A=None, W=None, W0=None, offsets=None, device=True, **kw):
+    from oracle.refapi import OBJECTIVES as IDS
+    oid = IDS[objective]
+    if device:
+        return mod.evaluate(oid, dev(X), dev(labels), A=dev(A), W=dev(W), W0=dev(W0),
+                            offsets=dev(offsets), **kw)
+    return mod.evaluate(oid, X, labels, A=A, W=W, W0=W0, offsets=offsets, **kw)
+
+
+@pytest.mark.parametrize("objective", OBJECTIVES)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+@pytest.mark.parametrize("kernel", [False, True])
+def test_every_objective_matches_reference(ref, cuda_lib, objective, dtype, kernel):
+    from oracle.refapi import MULTILABEL, OBJECTIVES as IDS
+    rng = np.random.default_rng(stable_seed("gpu-eval", objective, str(dtype), kernel))
+    ml = IDS[objective] in MULTILABEL
+    for n, d, m, k in ((130, 12, 7, 2), (70, 37, 133, 5), (9, 3, 2, 1), (300, 64, 1000, 5)):
+        if ml and m == 2:
+            continue
+        X, labels, offsets = random_problem(rng, n, d, m, dtype, ml)
+        A = np.zeros((n, m), dtype=dtype); W = np.zeros((m, d), dtype=dtype)
+        kw = dict(c=1.5, gamma=0.7, k=k)
+        ref.fit(objective, X, A, labels, W=W, offsets=offsets, max_epoch=2, eval_epoch=10, **kw)
+        tol = 1e-12 if dtype == np.float64 else 1e-5
+        if kernel:
+            K = (X.astype(np.float64) @ X.astype(np.float64).T).astype(dtype)
+            r = ref.evaluate(objective, K, A.copy(), labels, kernel=True, offsets=offsets, **kw)
+            g = gpu_eval(cuda_lib, objective, K, labels, A=A, offsets=offsets, kernel=True, **kw)
+            h = gpu_eval(cuda_lib, objective, K, labels, A=A, offsets=offsets, kernel=True,
+                         device=False, **kw)
+        else:
+            r = ref.evaluate(objective, X, A.copy(), labels, W=W, offsets=offsets, **kw)
+            g = gpu_eval(cuda_lib, objective, X, labels, A=A, W=W, offsets=offsets, **kw)
+            h = gpu_eval(cuda_lib, objective, X, labels, A=A, W=W, offsets=offsets, device=False, **kw)
+        compare(g, r, tol, (objective, n, d, m, "device"))
+        compare(h, r, tol, (objective, n, d, m, "host"))
+
+
+def test_golden_eval_records(cuda_lib):
+    from oracle.refapi import EVAL_FIELDS
+    for c in eval_cases():
+        kw = dict(c=c["c"], gamma=c["gamma"], k=c["k"], offsets=c["offsets"])
+        if c["kernel"]:
+            g = gpu_eval(cuda_lib, c["objective"], c["data"], c["labels"], A=c["A"], kernel=True, **kw)
+        else:
+            g = gpu_eval(cuda_lib, c["objective"], c["data"], c["labels"], A=c["A"], W=c["W"], **kw)
+        tol = 1e-12 if c["data"].dtype == np.float64 else 1e-5
+        ref_rec = {f: c["record"][i] for i, f in enumerate(EVAL_FIELDS)}
+        ref_rec["accuracy"] = c["accuracy"]
+        compare(g, ref_rec, tol, c["objective"])
+
+
+def test_held_out_set_and_prox_regularizer(ref, cuda_lib):
+    rng = np.random.default_rng(4)
+    n, d, m = 90, 20, 11
+    X, labels, _ = random_problem(rng, n, d, m, np.float64, False)
+    A = np.zeros((n, m)); W = np.zeros((m, d))
+    ref.fit("msvm_smooth", X, A, labels, W=W, max_epoch=2, eval_epoch=10, c=1.0, gamma=1.0, k=1)
+    W0 = rng.standard_normal((m, d)) * 0.1
+    r = ref.evaluate("msvm_smooth", X, A.copy(), labels, W=W, W0=W0, c=1.0, gamma=1.0, k=1)
+    g = gpu_eval(cuda_lib, "msvm_smooth", X, labels, A=A, W=W, W0=W0, c=1.0, gamma=1.0, k=1)
+    compare(g, r, 1e-12, "W0")
+    rt = ref.evaluate("msvm_smooth", X[:30], A, labels[:30], W=W, is_train=False, c=1.0, gamma=1.0, k=1)
+    gt = gpu_eval(cuda_lib, "msvm_smooth", X[:30], labels[:30], W=W, A=None, is_train=False,
+                  c=1.0, gamma=1.0, k=1)
+    assert abs(rt["primal_loss"] - gt["primal_loss"]) <= 1e-12 * max(1, abs(rt["primal_loss"]))
+    assert np.allclose(rt["accuracy"], gt["accuracy"], atol=1e-12)
+
+
+def test_config4_gap_terms_reduced_n(ref, cuda_lib):
+    """Config 4 at reduced N: top-k hinge alpha, k = 5, d = 4096, m = 1000, float32;
+    every term of the record is compared separately (the regulariser dwarfs the losses)."""
+    from libsdca_b200 import synth
+    n = 1024
+    X, A, W, labels = synth.gap_problem(
+        n=n, d=4096, m=1000, k=5, c=1.0,
+        project=lambda v, k, rhs: ref.prox("topk_simplex", v, k=k, rhs=rhs))
+    for objective, gamma in (("l2_hinge_topk", 0.0), ("l2_hinge_topk_smooth", 1.0)):
+        r = ref.evaluate(objective, X, A.copy(), labels, W=W, c=1.0, gamma=gamma, k=5)
+        g = gpu_eval(cuda_lib, objective, X, labels, A=A, W=W, c=1.0, gamma=gamma, k=5)
+        # the reference sums ||W||^2 over 4.1e6 float products in float; that one
+        # term is compared at the accuracy of that sum
+        for f in FIELDS:
+            tol = 2e-4 if "regularizer" in f or f in ("primal", "dual") else 1e-5
+            assert abs(g[f] - r[f]) <= tol * max(1, abs(r[f])), (objective, f, g[f], r[f])
+        assert np.abs(g["accuracy"] - r["accuracy"]).max() <= 2.0 / n
+
+
+def test_chunked_evaluation_is_the_same(ref, cuda_lib):
+    import subprocess
+    import sys
+    code = (
+        "import numpy as np, sys; sys.path.insert(0, %r)\n"
+        "import libsdca_b200 as sd, torch\n"
+        "from tests.test_oracle_restatement import random_problem\n"
+        "rng = np.random.default_rng(8)\n"
+        "X, labels, _ = random_problem(rng, 700, 16, 9, np.float64, False)\n"
+        "A = rng.standard_normal((700, 9)) * 0.01; W = rng.standard_normal((9, 16))\n"
+        "t = lambda a: torch.from_numpy(a).cuda()\n"
+        "r = sd.evaluate(5, t(X), t(labels), A=t(A), W=t(W), c=1.0, gamma=0.5, k=1)\n"
+        "print(repr([r[f] for f in ('primal','dual','primal_loss','dual_loss')] + r['accuracy'][:3].tolist()))\n"
+    ) % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    outs = []
+    for chunk in ("", "128"):
+        env = dict(os.environ, SDCAB_EVAL_CHUNK=chunk)
+        res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
+        outs.append(np.array(eval(res.stdout.strip().splitlines()[-1])))
+    assert np.allclose(outs[0], outs[1], rtol=1e-13, atol=0)
