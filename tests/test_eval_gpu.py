@@ -15,10 +15,21 @@ FIELDS = ("primal", "dual", "primal_loss", "dual_loss", "primal_regularizer",
           "dual_regularizer", "rank_loss")
 
 
-def compare(rec, ref_rec, tol, what=""):
+def compare(rec, ref_rec, tol, what="", reg_tol=None, acc_atol=1e-12):
+    """Term-by-term comparison.  For float32 data the reference sums ||W||^2 (and
+    <a_i, scores_i>) in float, in index order; that sum is only accurate to about
+    count * FLT_EPSILON / 4, so the regulariser terms (and the totals that contain
+    them) get that bound (reg_tol) while the loss terms keep the plain tolerance."""
     for f in FIELDS:
-        assert abs(rec[f] - ref_rec[f]) <= tol * max(1, abs(ref_rec[f])), (what, f, rec[f], ref_rec[f])
-    assert np.allclose(rec["accuracy"], ref_rec["accuracy"], atol=1e-12), what
+        t = tol
+        if reg_tol is not None and ("regularizer" in f or f in ("primal", "dual")):
+            t = max(tol, reg_tol)
+        assert abs(rec[f] - ref_rec[f]) <= t * max(1, abs(ref_rec[f])), (what, f, rec[f], ref_rec[f])
+    assert np.allclose(rec["accuracy"], ref_rec["accuracy"], atol=acc_atol), what
+
+
+def float_sum_tol(dtype, count):
+    return None if np.dtype(dtype) == np.float64 else count * float(np.finfo(np.float32).eps) / 4
 
 
 def dev(x):
@@ -60,8 +71,13 @@ def test_every_objective_matches_reference(ref, cuda_lib, objective, dtype, kern
             r = ref.evaluate(objective, X, A.copy(), labels, W=W, offsets=offsets, **kw)
             g = gpu_eval(cuda_lib, objective, X, labels, A=A, W=W, offsets=offsets, **kw)
             h = gpu_eval(cuda_lib, objective, X, labels, A=A, W=W, offsets=offsets, device=False, **kw)
-        compare(g, r, tol, (objective, n, d, m, "device"))
-        compare(h, r, tol, (objective, n, d, m, "host"))
+        reg_tol = float_sum_tol(dtype, m * (n if kernel else d))
+        compare(g, r, tol, (objective, n, d, m, "device"), reg_tol)
+        compare(h, r, tol, (objective, n, d, m, "host"), reg_tol)
+        if not kernel:
+            # the regulariser itself is exact: 0.5 ||W||^2 accumulated in double
+            exact = 0.5 * float((W.astype(np.float64) ** 2).sum())
+            assert abs(g["primal_regularizer"] - exact) <= 1e-12 * max(1, exact)
 
 
 def test_golden_eval_records(cuda_lib):
@@ -106,12 +122,20 @@ def test_config4_gap_terms_reduced_n(ref, cuda_lib):
     for objective, gamma in (("l2_hinge_topk", 0.0), ("l2_hinge_topk_smooth", 1.0)):
         r = ref.evaluate(objective, X, A.copy(), labels, W=W, c=1.0, gamma=gamma, k=5)
         g = gpu_eval(cuda_lib, objective, X, labels, A=A, W=W, c=1.0, gamma=gamma, k=5)
-        # the reference sums ||W||^2 over 4.1e6 float products in float; that one
-        # term is compared at the accuracy of that sum
-        for f in FIELDS:
-            tol = 2e-4 if "regularizer" in f or f in ("primal", "dual") else 1e-5
-            assert abs(g[f] - r[f]) <= tol * max(1, abs(r[f])), (objective, f, g[f], r[f])
+        # the reference sums ||W||^2 over 4.1e6 float products in a float accumulator
+        # (its value is off by about half a percent here); the regulariser is
+        # therefore checked against the exact double sum, the reference only
+        # bounds it, and the loss terms are compared at the plain tolerance
+        compare(g, r, 1e-5, objective, float_sum_tol(np.float32, 4096 * 1000), acc_atol=2.0 / n)
+        exact = 0.5 * float((W.astype(np.float64) ** 2).sum())
+        assert abs(g["primal_regularizer"] - exact) <= 1e-12 * exact
+        assert abs(g["dual_regularizer"] - exact) <= 1e-12 * exact
+        assert abs(g["primal"] - (g["primal_loss"] + exact)) <= 1e-9 * exact
+        assert abs(g["dual"] - (g["dual_loss"] - exact)) <= 1e-9 * exact
+        for f in ("primal_loss", "dual_loss"):
+            assert abs(g[f] - r[f]) <= 1e-5 * max(1, abs(r[f])), (objective, f, g[f], r[f])
         assert np.abs(g["accuracy"] - r["accuracy"]).max() <= 2.0 / n
+
 
 
 def test_chunked_evaluation_is_the_same(ref, cuda_lib):
