@@ -230,6 +230,35 @@ int sdcab_eval_sums_f64_dev(const sdcab_objective* obj, const sdcab_problem* p,
                             double* sums_dev, void* workspace_dev,
                             size_t workspace_bytes, void* stream);
 
+/*
+ * sdcab_eval_sums_*_dev without any allocation (this entry point has no
+ * counterpart in the reference).  Same arguments, same sums, but the scratch is
+ * a fixed array of sdcab_eval_fixed_scratch_bytes() (16 MiB) that ships inside
+ * the library and sits on every GPU that loads it until the process ends; no
+ * cudaMalloc, cudaFree or other allocating call is made.  Meant for hosts that
+ * must not allocate while they run -- a plug-in inside an application whose own
+ * allocator already owns the device, or a loop that cannot take the device-wide
+ * synchronisation of cudaMalloc.
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and caches it; make that
+ *     first call before any stream capture begins.
+ *   - The number of classes is limited: 32 score rows, the rank histogram and
+ *     the partial sums must fit the array (about 130 000 float or 65 000 double
+ *     classes).  Beyond that the call returns SDCAB_ERR_TOO_LARGE and
+ *     sdcab_eval_fixed_scratch_error() holds the reason.  n is not limited:
+ *     examples go through the array in chunks.
+ *   - All calls on a device share the one array, which keeps what the last call
+ *     left in it; the call clears what it accumulates into.  Two calls that
+ *     overlap on the GPU (different streams, different host threads) race on
+ *     it: run them one after the other.
+ */
+int sdcab_eval_sums_fixed_scratch_f32_dev(const sdcab_objective* obj, const sdcab_problem* p,
+                                          double* sums_dev, void* stream);
+int sdcab_eval_sums_fixed_scratch_f64_dev(const sdcab_objective* obj, const sdcab_problem* p,
+                                          double* sums_dev, void* stream);
+size_t sdcab_eval_fixed_scratch_bytes(void);
+const char* sdcab_eval_fixed_scratch_error(void);
+
 /* Turns summed-up sums (host memory) into the record: applies the objective's
  * coefficient, forms primal / dual, normalises the accuracy histogram into
  * cumulative top-k accuracies (include/sdca/solver/eval/core.h:43-132,

@@ -16,6 +16,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 #include <vector>
 
 #include "common_host.h"
@@ -23,6 +24,8 @@
 #include "losses.cuh"
 
 namespace sdcab {
+
+static thread_local char g_fixed_scratch_error[160] = "";
 
 // ------------------------------------------------------------------ GEMM ----
 // C (M x N, row major) = A (M x K, row major) * op(B), with
@@ -575,6 +578,124 @@ int eval_host(const sdcab_objective* obj, const sdcab_problem* hp, sdcab_eval_re
   return eval_finish(obj, m, total.data(), rec, accuracy);
 }
 
+// ------------------------------------------------- fixed-scratch variant ----
+// The evaluation above needs device scratch (the score tile, the per-block
+// partial sums and the rank histogram).  This variant keeps that scratch in a
+// fixed array that is part of the library image, so it never asks the CUDA
+// runtime (or anybody else) for memory.  It serves hosts that may not allocate
+// while they run: a plug-in living inside an application whose own allocator
+// has already claimed the device and treats every foreign cudaMalloc as a
+// failure or a fragmentation hazard, and control loops that cannot afford the
+// device-wide synchronisation a cudaMalloc / cudaFree implies.
+//
+// The array exists once per GPU that loads the library and stays resident until
+// the process exits.  In host code its name is only a handle: the device address
+// is looked up with cudaGetSymbolAddress the first time the entry point runs on
+// a device (with that device current) and cached.
+constexpr size_t kFixedScratchBytes = static_cast<size_t>(16) << 20;
+static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchBytes];
+
+static void* g_fixed_scratch_ptr[64] = {nullptr};
+static std::mutex g_fixed_scratch_mutex;
+
+static int fixed_scratch_address(void** out) {
+  int dev = -1;
+  SDCAB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return SDCAB_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(g_fixed_scratch_mutex);
+  if (!g_fixed_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    SDCAB_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_fixed_scratch));
+    g_fixed_scratch_ptr[dev] = ptr;
+  }
+  *out = g_fixed_scratch_ptr[dev];
+  return SDCAB_OK;
+}
+
+// Same sequence of kernels as eval_sums_dev, with the chunk length derived from
+// the fixed scratch instead of from a budget.
+template <typename Data>
+int eval_sums_fixed_scratch(const sdcab_objective* obj, const sdcab_problem* p, double* sums,
+                            cudaStream_t stream) {
+  int rc = check_problem(obj, p);
+  if (rc) return rc;
+  if (!sums) return SDCAB_ERR_ARG;
+  DeviceInfo info;
+  rc = get_device_info(&info);
+  if (rc) return rc;
+  void* scratch = nullptr;
+  rc = fixed_scratch_address(&scratch);
+  if (rc) return rc;
+  const long long m = p->m, n = p->n;
+  const int max_blocks = std::max(1, info.sm_count) * 16;
+  const size_t partials_bytes = (static_cast<size_t>(max_blocks) * 4 * sizeof(double) + 255) & ~static_cast<size_t>(255);
+  const size_t hist_bytes = (static_cast<size_t>(m) * sizeof(unsigned long long) + 255) & ~static_cast<size_t>(255);
+  const size_t row_bytes = static_cast<size_t>(m) * sizeof(Data);
+  // at least 32 score rows must fit beside the partial sums and the histogram
+  if (partials_bytes + hist_bytes + 32 * row_bytes + 256 > kFixedScratchBytes) {
+    std::snprintf(g_fixed_scratch_error, sizeof(g_fixed_scratch_error),
+                  "the fixed scratch of %zu bytes cannot hold 32 score rows of %lld classes",
+                  kFixedScratchBytes, m);
+    return SDCAB_ERR_TOO_LARGE;
+  }
+  const size_t scores_room = (kFixedScratchBytes - partials_bytes - hist_bytes) & ~static_cast<size_t>(255);
+  const long long chunk = std::min<long long>(n, static_cast<long long>(scores_room / row_bytes));
+  unsigned char* base = static_cast<unsigned char*>(scratch);
+  Data* scores = reinterpret_cast<Data*>(base);
+  double* partials = reinterpret_cast<double*>(base + scores_room);
+  unsigned long long* hist = reinterpret_cast<unsigned long long*>(base + scores_room + partials_bytes);
+
+  // the array keeps whatever the previous call left: everything that is
+  // accumulated into starts from zero here, the rest is overwritten before use
+  SDCAB_CUDA_TRY(cudaMemsetAsync(sums, 0, sizeof(double) * SDCAB_EVAL_SUMS(m), stream));
+  SDCAB_CUDA_TRY(cudaMemsetAsync(hist, 0, sizeof(unsigned long long) * m, stream));
+  set_count_kernel<<<1, 32, 0, stream>>>(sums, static_cast<double>(n));
+  if (p->is_train && p->input_kind == SDCAB_INPUT_FEATURES && p->include_primal_regularizer) {
+    const long long count = p->d * m;
+    const int blocks = static_cast<int>(std::min<long long>(max_blocks / 2, (count + 255) / 256));
+    dot_partials_kernel<Data><<<blocks, 256, 0, stream>>>(
+        static_cast<const Data*>(p->w), static_cast<const Data*>(p->w0), count, partials);
+    regularizer_combine_kernel<<<1, 32, 0, stream>>>(partials, blocks, p->w0 ? 1 : 0, sums);
+  }
+  LossArgs g;
+  g.obj = to_params(obj);
+  g.m = static_cast<int>(m);
+  g.a_row_offset = p->a_row_offset;
+  g.labels = reinterpret_cast<const long long*>(p->labels);
+  g.offsets = reinterpret_cast<const long long*>(p->offsets);
+  g.is_train = p->is_train;
+  g.kernel_input = (p->input_kind == SDCAB_INPUT_KERNEL);
+  g.m_pad = static_cast<int>((m + 15) & ~15LL);
+  g.mask_words = static_cast<int>((m + 31) / 32);
+  const int warps = kLossThreads / 32;
+  const size_t smem = static_cast<size_t>(warps) * g.m_pad * sizeof(Data) +
+                      static_cast<size_t>(warps) * g.mask_words * sizeof(unsigned);
+  if (smem > info.smem_optin) return SDCAB_ERR_TOO_LARGE;
+  const bool fl = (obj->precision == SDCAB_PRECISION_FLOAT);
+  auto kd = eval_loss_kernel<Data, double>;
+  auto kf = eval_loss_kernel<Data, float>;
+  if (smem > 48 * 1024) {
+    SDCAB_CUDA_TRY(cudaFuncSetAttribute(kd, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    SDCAB_CUDA_TRY(cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  }
+  for (long long first = 0; first < n; first += chunk) {
+    const long long count = std::min(chunk, n - first);
+    rc = scores_chunk<Data>(p, first, count, scores, stream);
+    if (rc) return rc;
+    g.n = count; g.first = first;
+    const int blocks = static_cast<int>(std::max<long long>(
+        1, std::min<long long>(max_blocks, (count + warps - 1) / warps)));
+    const Data* A = static_cast<const Data*>(p->a);
+    if (fl) kf<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+    else kd<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+    combine_partials_kernel<<<1, 32, 0, stream>>>(partials, blocks, sums);
+  }
+  hist_to_sums_kernel<<<std::max(1, static_cast<int>((m + 255) / 256)), 256, 0, stream>>>(
+      hist, static_cast<int>(m), sums);
+  SDCAB_CUDA_TRY(cudaGetLastError());
+  return SDCAB_OK;
+}
+
 }  // namespace sdcab
 
 extern "C" {
@@ -613,6 +734,17 @@ int sdcab_eval_f64(const sdcab_objective* obj, const sdcab_problem* hp, sdcab_ev
                    double* accuracy) {
   return sdcab::eval_host<double>(obj, hp, rec, accuracy);
 }
+
+int sdcab_eval_sums_fixed_scratch_f32_dev(const sdcab_objective* obj, const sdcab_problem* p,
+                                          double* sums, void* stream) {
+  return sdcab::eval_sums_fixed_scratch<float>(obj, p, sums, static_cast<cudaStream_t>(stream));
+}
+int sdcab_eval_sums_fixed_scratch_f64_dev(const sdcab_objective* obj, const sdcab_problem* p,
+                                          double* sums, void* stream) {
+  return sdcab::eval_sums_fixed_scratch<double>(obj, p, sums, static_cast<cudaStream_t>(stream));
+}
+size_t sdcab_eval_fixed_scratch_bytes(void) { return sdcab::kFixedScratchBytes; }
+const char* sdcab_eval_fixed_scratch_error(void) { return sdcab::g_fixed_scratch_error; }
 
 int sdcab_scores_f32_dev(const sdcab_problem* p, float* scores, void* stream) {
   if (!p || !scores || !p->x) return SDCAB_ERR_ARG;
