@@ -35,6 +35,18 @@ FULL_ROWS = 262144
 BYTES_PER_ROW = 2 * M * 4  # one read + one write of a float32 row
 OPS = (("topk_simplex", dict(k=K_TOP, rhs=1.0)), ("topk_cone", dict(k=K_TOP)))
 
+# The other configurations of the benchmark definition, selectable with --config;
+# the default (2) is the one the metric is quoted on.
+PROX_CONFIGS = {
+    1: dict(rows=65536, m=100, dtype="float64", gen="simplex_rows",
+            ops=(("knapsack", dict()),),
+            name="config 1: simplex projection, 65536 x 100 float64, N(0,1)"),
+    3: dict(rows=1048576, m=200, dtype="float32", gen="entropy_rows",
+            ops=(("topk_entropy", dict(k=1)), ("topk_entropy", dict(k=10)),
+                 ("entropy", dict(hi=1.0, rhs=1.0)), ("lambert_w_exp", dict())),
+            name="config 3: top-k entropy k=1,10, entropy, Lambert W(exp x), 1048576 x 200 float32"),
+}
+
 
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -152,6 +164,178 @@ def workload_config(rows, world, note):
             "note": note}
 
 
+def _time_op(torch, fn, reps):
+    evs = []
+    for _ in range(reps):
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        evs.append((e0, e1))
+    torch.cuda.synchronize()
+    return float(np.median([a.elapsed_time(b) for a, b in evs]))
+
+
+def other_prox_config(args, rank, world, local_rank):
+    """Configs 1 and 3: per-operator device throughput and achieved HBM bandwidth."""
+    import torch
+    import libsdca_b200 as sd
+    from libsdca_b200 import synth
+    from oracle import refapi
+    cfg = PROX_CONFIGS[args.config]
+    torch.cuda.set_device(local_rank)
+    rows = cfg["rows"] if args.rows == FULL_ROWS else args.rows
+    m = cfg["m"]
+    dtype = np.dtype(cfg["dtype"])
+    host = getattr(synth, cfg["gen"])(rows=rows)
+    a = torch.from_numpy(host).cuda()
+    if args.config == 3:
+        lam = torch.from_numpy(synth.lambert_inputs(count=rows * m)).cuda().view(rows, m)
+    out = torch.empty_like(a)
+    peak, peak_kind = measured_peak_gbs()
+    bytes_per_row = 2 * m * dtype.itemsize
+    per_op = {}
+    for name, kw in cfg["ops"]:
+        src = lam if name == "lambert_w_exp" else a
+        okw = dict(kw) if name == "lambert_w_exp" else dict(kw, precision=args.precision)
+        fn = lambda: sd.prox_to(src, out, name, **okw)
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        # inputs smaller than L2 (config 1): rotate over copies so that every launch reads HBM
+        if rows * m * dtype.itemsize < (256 << 20):
+            copies = [src.clone() for _ in range(8)]
+            outs = [torch.empty_like(src) for _ in range(8)]
+            it = {"i": 0}
+
+            def fn():
+                i = it["i"] = (it["i"] + 1) % 8
+                sd.prox_to(copies[i], outs[i], name, **okw)
+        ms = _time_op(torch, fn, max(args.steps, 10))
+        label = name + ("(k=%d)" % kw["k"] if "k" in kw else "")
+        gbs = rows * bytes_per_row / (ms * 1e-3) / 1e9
+        per_op[label] = {"ms": ms, "rows_per_s": rows / (ms * 1e-3), "gbs": gbs, "frac": gbs / peak}
+    cpu = None
+    if not args.no_cpu_baseline and refapi.have_reference():
+        threads = max(1, min(os.cpu_count() or 1, 64))
+        sample = host[: min(rows, 65536)]
+        cpu = {}
+        for name, kw in cfg["ops"]:
+            t0 = time.perf_counter()
+            refapi.reference().prox(name, sample, nthreads=threads, **kw)
+            label = name + ("(k=%d)" % kw["k"] if "k" in kw else "")
+            cpu[label] = {"rows_per_s": len(sample) / (time.perf_counter() - t0), "cores": threads}
+    slow = min(per_op, key=lambda k_: per_op[k_]["gbs"])
+    total_ms = sum(v["ms"] for v in per_op.values())
+    print(json.dumps({
+        "metric": "prox rows/s", "value": len(per_op) * rows / (total_ms * 1e-3), "unit": "rows/s",
+        "n_gpus": 1, "steps": max(args.steps, 10), "warmup": max(3, args.warmup),
+        "ms_per_step": total_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f64" if dtype == np.float64 else "f32", "data": "synthetic",
+        "config": {"workload": cfg["name"], "rows": rows, "m": m,
+                   "thresholds_precision": args.precision,
+                   "l2": "rotating buffers" if rows * m * dtype.itemsize < (256 << 20) else "inputs exceed L2"},
+        "roofline": {"bound": "hbm", "achieved": per_op[slow]["gbs"], "peak": peak, "unit": "GB/s",
+                     "frac": per_op[slow]["frac"], "traffic": None, "kernel": slow,
+                     "peak_kind": "of " + peak_kind, "per_operator": per_op},
+        "cpu_baseline": cpu, "gpu_launches": len(per_op) * max(args.steps, 10)}))
+
+
+def gap_config(args, rank, world, local_rank):
+    """Config 4: duality-gap evaluation, top-k hinge alpha (k = 5), feature input,
+    d = 4096, m = 1000, float32; examples sharded over the ranks, one all-reduce
+    of the sums vector.  --rows sets the examples per GPU (default 1048576 / N)."""
+    import torch
+    import libsdca_b200 as sd
+    from libsdca_b200 import binding as b
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    d, m, k, c = 4096, 1000, 5, 1.0
+    n_total = 1048576
+    n = args.rows if args.rows != FULL_ROWS else n_total // world
+    gen = torch.Generator(device="cuda").manual_seed(5)          # same class means on every rank
+    means = torch.randn((m, d), generator=gen, device="cuda")
+    gen.manual_seed(50 + rank)
+    labels = torch.randint(0, m, (n,), generator=gen, device="cuda")
+    X = torch.empty((n, d), device="cuda")
+    step_rows = 65536
+    for i in range(0, n, step_rows):                                # x_i = mean[y_i] + 2 N(0, I)
+        j = min(n, i + step_rows)
+        X[i:j] = means[labels[i:j]] + 2.0 * torch.randn((j - i, d), generator=gen, device="cuda")
+    # a random feasible dual point: v ~ N(0,1)^(m-1) projected onto the top-k simplex
+    v = torch.randn((n, m - 1), generator=gen, device="cuda")
+    # rows of 999 floats are not 16-byte aligned: the general kernel handles them
+    sd.prox_(v, "topk_simplex", k=k, rhs=c)
+    A = torch.zeros((n, m), device="cuda")
+    cols = torch.arange(m - 1, device="cuda")[None, :] + (torch.arange(m - 1, device="cuda")[None, :] >= labels[:, None])
+    A.scatter_(1, cols, -v)
+    A[torch.arange(n, device="cuda"), labels] = torch.clamp(v.double().sum(dim=1), max=c).float()
+    del v, cols
+    W = torch.zeros((m, d), device="cuda")
+    for i in range(0, n, step_rows):                                # W = X A' (d x m), stored (m, d)
+        j = min(n, i + step_rows)
+        W += A[i:j].T @ X[i:j]
+    if dist is not None:
+        dist.all_reduce(W)
+    torch.cuda.synchronize()
+    results = {}
+    ws_bytes = sd.lib().sdcab_eval_workspace_bytes
+    ws_bytes.restype = C.c_size_t
+    workspace = torch.empty(ws_bytes(C.c_int64(n), C.c_int64(m), C.c_int64(4)), dtype=torch.uint8, device="cuda")
+    for label, gamma in (("l2_hinge_topk (gamma=0)", 0.0), ("l2_hinge_topk_smooth (gamma=1)", 1.0)):
+        obj = b.make_objective("topk_hinge_alpha", c=c, gamma=gamma, k=k)
+        prob = b.make_problem(X, labels, A=A, W=W, include_primal_regularizer=(rank == 0))
+        sums = torch.zeros(8 + m, dtype=torch.float64, device="cuda")
+
+        def one_eval():
+            sd.eval_sums_(obj, prob, sums, "f32", workspace, workspace.numel())
+            if dist is not None:
+                dist.all_reduce(sums)
+            return sums
+
+        for _ in range(max(1, min(args.warmup, 3))):
+            one_eval()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        steps = max(1, min(args.steps, 5))
+        e0.record()
+        for _ in range(steps):
+            one_eval()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if dist is not None:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        rec = sd.eval_finish(obj, m, sums.cpu().numpy())
+        results[label] = {"seconds_per_eval": ms * 1e-3,
+                          "tflops": 2.0 * d * m * n * world / (ms * 1e-3) / 1e12,
+                          "record": {f: rec[f] for f in ("primal", "dual", "primal_loss", "dual_loss",
+                                                         "primal_regularizer", "relative_gap")},
+                          "top1": float(rec["accuracy"][0])}
+    if rank == 0:
+        first = results["l2_hinge_topk (gamma=0)"]
+        print(json.dumps({
+            "metric": "duality-gap evaluation seconds", "value": first["seconds_per_eval"], "unit": "s",
+            "n_gpus": world, "steps": max(1, min(args.steps, 5)), "warmup": max(1, min(args.warmup, 3)),
+            "ms_per_step": first["seconds_per_eval"] * 1e3, "higher_is_better": False,
+            "scaling": "strong" if args.rows == FULL_ROWS else "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "config 4: gap evaluation, top-k hinge alpha k=5, features d=4096, m=1000, "
+                                   "%d examples per GPU, float32" % n, "examples_per_gpu": n,
+                       "collective": "one all_reduce(sum) of %d doubles" % (8 + m)},
+            "roofline": {"bound": "fp32 fma (CUDA cores; tensor cores not used by this kernel yet)",
+                         "achieved": first["tflops"], "peak": None, "unit": "TFLOP/s", "frac": None,
+                         "traffic": None, "kernel": "gemm_kernel<float,128,128,16,8,8>"},
+            "results": results}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -162,6 +346,10 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=65536, help="rows of the CPU sample")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4],
+                    help="benchmark configuration; 2 (default) is the headline")
+    ap.add_argument("--precision", default="double", choices=["double", "float"],
+                    help="precision of thresholds and accumulators")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
@@ -172,6 +360,10 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
+    if args.config in PROX_CONFIGS:
+        return other_prox_config(args, rank, world, local_rank)
+    if args.config == 4:
+        return gap_config(args, rank, world, local_rank)
 
     import torch
     import libsdca_b200 as sd
@@ -208,7 +400,7 @@ def main():
 
     def step():
         for name, kw in OPS:
-            sd.prox_to(a, out, name, **kw)
+            sd.prox_to(a, out, name, precision=args.precision, **kw)
 
     for _ in range(warmup):
         step()
@@ -220,10 +412,16 @@ def main():
         evs = []
         for _ in range(max(3, min(args.steps, 10))):
             e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-            e0.record(); sd.prox_to(a, out, name, **kw); e1.record()
+            e0.record(); sd.prox_to(a, out, name, precision=args.precision, **kw); e1.record()
             evs.append((e0, e1))
         torch.cuda.synchronize()
         per_op_ms[name] = float(np.mean([x.elapsed_time(y) for x, y in evs]))
+
+    # the same kernels with float thresholds (opts.precision = 'single'), for reference
+    other = "float" if args.precision == "double" else "double"
+    per_op_other = {}
+    for name, kw in OPS:
+        per_op_other[name] = _time_op(torch, lambda: sd.prox_to(a, out, name, precision=other, **kw), 5)
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
@@ -245,7 +443,7 @@ def main():
 
     def e2e_step():
         for name, kw in OPS:
-            o = make_opts(**kw)
+            o = make_opts(precision=args.precision, **kw)
             rc = lib.sdcab_prox_f32(name.encode(), C.c_void_p(pinned_in.data_ptr()), C.c_int64(M),
                                     C.c_int64(rows), C.byref(o), C.c_void_p(pinned_out.data_ptr()))
             if rc != 0:
@@ -277,9 +475,12 @@ def main():
                          "peak_kind": "of " + peak_kind,
                          "per_kernel_ms": per_op_ms,
                          "per_kernel_gbs": {k: rows * BYTES_PER_ROW / (v * 1e-3) / 1e9
-                                            for k, v in per_op_ms.items()}},
+                                            for k, v in per_op_ms.items()},
+                         "thresholds_precision": args.precision,
+                         "per_kernel_gbs_%s_thresholds" % other:
+                             {k: rows * BYTES_PER_ROW / (v * 1e-3) / 1e9 for k, v in per_op_other.items()}},
             "e2e": {"value": 2.0 * rows * world * args.e2e_steps / e2e_s, "unit": "rows/s",
-                    "h2d_bytes_per_step": 2 * rows * M * 4, "d2h_bytes_per_step": 2 * rows * M * 4,
+                    "h2d_bytes_per_step": 2 * rows * M * 4 * world, "d2h_bytes_per_step": 2 * rows * M * 4 * world,
                     "steps": args.e2e_steps, "checksum": checksum},
             "gpu_launches": 2 * args.steps * world,
             "clocks": clocks,
