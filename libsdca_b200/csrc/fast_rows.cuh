@@ -20,9 +20,10 @@ namespace sdcab {
 
 constexpr int kNoFastPath = 1;
 constexpr int kFastThreads = 128;
-#ifndef SDCAB_FAST_MIN_BLOCKS
-#define SDCAB_FAST_MIN_BLOCKS 6
-#endif
+// Resident blocks per SM the register allocation aims for: double thresholds
+// need more live registers, and spilling them costs more than the lost warps.
+template <typename R> struct FastMinBlocks { static constexpr int value = 6; };
+template <> struct FastMinBlocks<double> { static constexpr int value = 5; };
 
 template <typename Data> struct VecOf;
 template <> struct VecOf<float> { typedef float4 type; static constexpr int N = 4; };
@@ -299,6 +300,52 @@ __device__ __forceinline__ Thr<R> sorted_knapsack_eq(const Sorted<R>& c, R hi, R
   }
 }
 
+// Direct solution of  <1,x> = rhs, 0 <= x <= hi = rhs/k  on sorted candidates.
+// With the u largest entries at hi, the others solve an ordinary simplex
+// projection onto the remaining mass rhs - u*hi, whose threshold over sorted
+// data is tau_j = (sum of the first j of them - mass) / j for the largest j with
+// s_j > tau_j; every lane evaluates its own j at once.  u grows from 0 until
+// the pair is consistent (entry u not above hi, entry u-1 above it), which is
+// the unique KKT point that the reference's variable fixing converges to
+// (include/sdca/prox/knapsack_eq.h:25-109); at most k + 1 rounds.
+template <typename R>
+__device__ __forceinline__ bool sorted_capped_simplex(const Sorted<R>& c, R hi, R rhs, int k,
+                                                      int lane, Thr<R>& thr, R& sum_U) {
+  const int n = c.n;
+  const R inf = num<R>::inf();
+  for (int u = 0; u <= k && u < n; ++u) {
+    const R mass = rhs - static_cast<R>(u) * hi;
+    const R Pu = c.pre(u);
+    const int j_mine = lane - u + 1;
+    const bool valid = (lane >= u) && (lane < n);
+    // s_j > tau_j  <=>  j * s_j > (sum - mass): no division until j is known
+    const R excess = c.P - Pu - mass;
+    const R jr = static_cast<R>(valid ? j_mine : 1);
+    const unsigned above = __ballot_sync(kFullMask, valid && c.s * jr > excess);
+    const R s_u = c.at(u);
+    const R s_um1 = (u > 0) ? c.at(u - 1) : inf;
+    if (above == 0u) {
+      // nothing strictly inside: the u capped entries carry all the mass
+      if (u == 0) continue;
+      const R t = s_um1 - hi;
+      if (s_u <= t) {
+        sum_U = Pu;
+        thr = make_thr(t, R(0), hi, u, 0, s_um1, s_um1);
+        return true;
+      }
+      continue;
+    }
+    const int last = 31 - __clz(above);
+    const R t = __shfl_sync(kFullMask, excess, last) / static_cast<R>(last - u + 1);
+    if (s_u - t <= hi && (u == 0 || s_um1 - t > hi)) {
+      sum_U = Pu;
+      thr = make_thr(t, R(0), hi, u, last - u + 1, (u > 0) ? s_um1 : inf, t);
+      return true;
+    }
+  }
+  return false;
+}
+
 enum FastStatus { kFastDone = 0, kFastNeedsFullRow = 1 };
 
 // Top-k simplex (rho = 0) and its biased form.  Returns kFastNeedsFullRow when
@@ -323,10 +370,14 @@ __device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& 
   if (proj == kProjZero) return kFastDone;
   R sum_U;
   if (proj == kProjConstant) {
-    if (K * thr.hi > rhs + eps) thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
+    if (K * thr.hi > rhs + eps) {
+      if (!sorted_capped_simplex<R>(c, H, rhs, k, lane, thr, sum_U))
+        thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
+    }
     return kFastDone;
   }
-  thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
+  if (!sorted_capped_simplex<R>(c, H, rhs, k, lane, thr, sum_U))
+    thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
   bool lt;
   if (thr.nU == 0) {
     lt = thr.t < rho * rhs - eps;
@@ -397,6 +448,133 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
   return kFastNeedsFullRow;
 }
 
+// ---- entropic projections of float rows --------------------------------------
+// For float data the stated accuracy of outputs and thresholds is 1e-5, so the
+// m exponentials of a log-sum-exp are evaluated in float (1e-7 each) and added
+// up in R; everything after the sum (logarithms, the closed forms for t and hi)
+// stays in R.  Double data keeps the general routines.
+
+// max of the row and S = sum_i exp(a_i - max) (the maximum contributes exactly 1)
+template <typename R, int NV>
+__device__ __forceinline__ void row_max_and_expsum(const RegRow<float, NV>& row, float& mx,
+                                                   float& lane_max, R& S) {
+  float lm = -num<float>::inf();
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const float* e = reinterpret_cast<const float*>(&row.v[j]);
+    lm = fmaxf(lm, fmaxf(fmaxf(e[0], e[1]), fmaxf(e[2], e[3])));
+  }
+  lane_max = lm;
+  mx = warp_max_fast(lm);
+  R acc0 = 0, acc1 = 0;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    // padding holds -inf: exp(-inf) = 0
+    const float* e = reinterpret_cast<const float*>(&row.v[j]);
+    const float p0 = exp_(e[0] - mx) + exp_(e[1] - mx);
+    const float p1 = exp_(e[2] - mx) + exp_(e[3] - mx);
+    acc0 += static_cast<R>(p0);
+    acc1 += static_cast<R>(p1);
+  }
+  S = warp_sum(acc0 + acc1);
+}
+
+// Top-k entropy projection (include/sdca/prox/topk_entropy.h:20-76): the
+// reference moves the current maximum into U and recomputes the log-sum-exp of
+// the rest up to k - 1 times; here the k largest entries are sorted into lanes
+// once and lane u evaluates "U = the u largest" from prefix sums of the
+// exponentials, so all sizes of U are tested at the same time.
+template <typename R, int NV>
+__device__ __forceinline__ FastStatus fast_topk_entropy(const RegRow<float, NV>& row, int k,
+                                                        float* slots, int* counter, int lane,
+                                                        Thr<R>& thr) {
+  const int m = row.size();
+  if (k > 30 || m <= 32 || k > m) return kFastNeedsFullRow;
+  const R eps = 16 * num<R>::eps();
+  const R K = static_cast<R>(k);
+  float mxf, lm;
+  R S;
+  row_max_and_expsum<R, NV>(row, mxf, lm, S);
+  const R mx = static_cast<R>(mxf);
+  R z = max_(S - R(1), R(0));
+  R log_z = mx + log1p_(z);
+  if (k <= 1 || mx - eps <= log_z - log_(K)) {
+    const R e = exp_(-mx);
+    const R log_z_1 = finite_(e) ? mx + log1p_(z + e) : R(0);
+    thr = make_thr(log_z_1, R(0), R(1), 0, m, num<R>::inf(), -num<R>::inf());
+    return kFastDone;
+  }
+  // the k + 1 largest entries, sorted, one per lane
+  const float tau = kth_largest_of_lanes(lm, k, lane);
+  const float cut = (tau > -num<float>::inf()) ? nextafterf(tau, -num<float>::inf()) : tau;
+  LaneRow<float> cand;
+  const int total = compact_candidates(row, cut, slots, counter, lane, cand);
+  if (total > 32 || total <= k) return kFastNeedsFullRow;
+  const Sorted<R> c = sort_candidates<R>(cand, total, lane);
+  // prefix sums of exp(s_i - max) over the sorted candidates
+  R pe = (lane < total) ? static_cast<R>(exp_(static_cast<float>(c.s) - mxf)) : R(0);
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const R up = __shfl_up_sync(kFullMask, pe, o);
+    if (lane >= o) pe += up;
+  }
+  // lane u: U = the u largest; the rest has maximum s_u
+  const int u = lane;
+  const R pe_prev = __shfl_up_sync(kFullMask, pe, 1);        // sum of the first u exponentials
+  const R s_prev = __shfl_up_sync(kFullMask, c.s, 1);        // smallest entry of U
+  const R sumU_prev = __shfl_up_sync(kFullMask, c.P, 1);     // sum of U
+  const bool active = (u >= 1) && (u <= k - 1) && (u < total);
+  const R rest = S - pe_prev;                                // relative to the old maximum
+  const R z_u = max_(rest * exp_(mx - c.s) - R(1), R(0));
+  const R log_z_u = c.s + log1p_(z_u);
+  const R tt = log_z_u - log_(K - static_cast<R>(u));
+  const bool ok = active && (c.s - eps <= tt) && (tt <= s_prev + eps);
+  // a rest that is a small fraction of the whole sum has lost too many digits
+  const bool shaky = active && !(rest > R(1e-3) * S);
+  if (__any_sync(kFullMask, shaky)) return kFastNeedsFullRow;
+  const unsigned okmask = __ballot_sync(kFullMask, ok);
+  const int last = min(k - 1, total - 1);
+  const int ustar = okmask ? (__ffs(okmask) - 1) : last;     // the loop ends at k - 1 without a hit
+  const R zs = __shfl_sync(kFullMask, z_u, ustar);
+  const R log_zs = __shfl_sync(kFullMask, log_z_u, ustar);
+  const R cur_max = __shfl_sync(kFullMask, c.s, ustar);
+  const R min_U = __shfl_sync(kFullMask, s_prev, ustar);
+  const R sum_U = __shfl_sync(kFullMask, sumU_prev, ustar);
+  const R k_u = K - static_cast<R>(ustar);
+  const R tmp = ((K - k_u) * log_zs + k_u * log_(k_u) - sum_U) / K;
+  R t, hi;
+  if (tmp > cur_max) {
+    const R a = (1 + zs) * exp_(cur_max - tmp);
+    t = tmp + log1p_(a * K) - log_(k_u);
+    hi = a / (1 + a * K);
+  } else {
+    const R a = exp_(tmp - cur_max) / K;
+    t = cur_max + log1p_(zs + a) - log_(k_u / K);
+    hi = (1 + zs) / ((1 + zs + a) * K);
+  }
+  thr = make_thr(t, R(0), hi, ustar, m - ustar, min_U, -num<R>::inf());
+  return kFastDone;
+}
+
+// Entropic projection (include/sdca/prox/entropy.h:19-53) when no entry reaches
+// the upper bound, which one counting pass establishes; otherwise the general
+// routine takes the row.
+template <typename R, int NV>
+__device__ __forceinline__ FastStatus fast_entropy(const RegRow<float, NV>& row, R hi, R rhs,
+                                                   int lane, Thr<R>& thr) {
+  const int m = row.size();
+  const R eps = 16 * num<R>::eps() * max_(R(1), rhs);
+  float mxf, lm;
+  R S;
+  row_max_and_expsum<R, NV>(row, mxf, lm, S);
+  const R mx = static_cast<R>(mxf);
+  const R t = (mx + log1p_(max_(S - R(1), R(0)))) - log_(rhs);
+  const R tt = t + log_(hi) + eps;
+  if (static_cast<R>(mxf) > tt) return kFastNeedsFullRow;
+  thr = make_thr(t, R(0), hi, 0, m, num<R>::inf(), -num<R>::inf());
+  return kFastDone;
+}
+
 // The general search for one row staged in shared memory; out of line so that
 // the register budget of the kernel is set by the common path.
 template <typename R, typename Data, int PROX>
@@ -406,7 +584,7 @@ __device__ __noinline__ Thr<R> full_row_thresholds(const Data* buf, int m, const
 }
 
 template <typename Data, typename R, int PROX, int NV>
-__global__ void __launch_bounds__(kFastThreads, SDCAB_FAST_MIN_BLOCKS)
+__global__ void __launch_bounds__(kFastThreads, FastMinBlocks<R>::value)
 fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long long n,
                  ProxParams q, int m_pad) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -421,6 +599,9 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
   Data* stage = reinterpret_cast<Data*>(smem_raw) + static_cast<size_t>(warp) * m_pad;
   constexpr bool kTopk = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased ||
                           PROX == kTopkCone || PROX == kTopkConeBiased);
+  // operators with a fast path that can decline a row
+  constexpr bool kStaged = kTopk || (std::is_same<Data, float>::value &&
+                                     (PROX == kTopkEntropy || PROX == kEntropy));
   for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + warp; r < n;
        r += static_cast<long long>(gridDim.x) * warps_per_block) {
     RegRow<Data, NV> row;
@@ -436,7 +617,14 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
       st = fast_topk_cone<R>(row, q.k, PROX == kTopkConeBiased ? static_cast<R>(q.rho) : R(0),
                              slots, counter, lane, thr);
     }
-    if (kTopk) {
+    if (std::is_same<Data, float>::value && PROX == kTopkEntropy) {
+      st = fast_topk_entropy<R, NV>(reinterpret_cast<const RegRow<float, NV>&>(row), q.k,
+                                    reinterpret_cast<float*>(slots), counter, lane, thr);
+    } else if (std::is_same<Data, float>::value && PROX == kEntropy) {
+      st = fast_entropy<R, NV>(reinterpret_cast<const RegRow<float, NV>&>(row),
+                               static_cast<R>(q.hi), static_cast<R>(q.rhs), lane, thr);
+    }
+    if (kStaged) {
       if (st != kFastDone) {
         row.for_each([&](Data x, int i) { stage[i] = x; });
         __syncwarp();
@@ -459,7 +647,8 @@ int launch_fast(const Data* a, Data* out, int m, long long n, const ProxParams& 
   if (rc) return rc;
   auto kernel = fast_rows_kernel<Data, R, PROX, NV>;
   constexpr bool kTopk = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased ||
-                          PROX == kTopkCone || PROX == kTopkConeBiased);
+                          PROX == kTopkCone || PROX == kTopkConeBiased) ||
+                         (std::is_same<Data, float>::value && (PROX == kTopkEntropy || PROX == kEntropy));
   const int m_pad = (m + 15) & ~15;
   const size_t smem = kTopk ? static_cast<size_t>(kFastThreads / 32) * m_pad * sizeof(Data) : 0;
   int per_sm = 0;

@@ -35,44 +35,49 @@ SDCAB_HD T exp_crude(T x) {
 }
 
 // W(exp(x)), float table                (reference: math/lambert.h:77-106)
+//   (-inf, -104] -> 0           (-104, -18] -> exp(x)
+//   (-18, -1]    -> one step from the crude exponential
+//   (-1, 8]      -> two steps from w = x
+//   (8, 2^29]    -> one step from x - log(x) with y = x        above -> x
+// Written without divergent branches: the lanes of a warp usually fall into
+// several intervals, so both seeds are computed and the operands of the one
+// exponential and of the final step are selected; each interval still sees
+// exactly the operations the table prescribes for it.
 SDCAB_HD float lambert_w_exp(float x) {
-  float w;
-  if (x > -1.0f) {
-    if (x <= 8.0f) {
-      w = householder5(x, 1.0f);
-    } else {
-      return (x <= 536870912.0f) ? householder5(x - log_(x), x) : x;
-    }
-  } else {
-    if (x > -18.0f) {
-      w = exp_crude(x);
-    } else {
-      return (x > -104.0f) ? exp_(x) : 0.0f;
-    }
-  }
-  return householder5(w, exp_(x - w));
+  const bool upper = x > -1.0f;                 // (-1, +inf)
+  const bool tail_lo = !(x > -18.0f);           // (-inf, -18]
+  const bool tail_hi = x > 8.0f;                // (8, +inf)
+  const float seed = upper ? householder5(x, 1.0f) : exp_crude(x);
+  const float e = exp_(tail_lo ? x : x - seed);
+  const float w_in = tail_hi ? x - log_(x) : seed;
+  const float y_in = tail_hi ? x : e;
+  const float stepped = householder5(w_in, y_in);
+  if (tail_lo) return (x > -104.0f) ? e : 0.0f;
+  if (tail_hi && !(x <= 536870912.0f)) return x;
+  return stepped;
 }
 
 // W(exp(x)), double table               (reference: math/lambert.h:121-157)
+//   (-inf, -746] -> 0            (-746, -36] -> exp(x)
+//   (-36, -20]   -> one step from the crude exponential
+//   (-20, 0]     -> crude seed, one step with the crude exponential, one step
+//   (0, 4]       -> two steps from w = x
+//   (4, 2^59]    -> step from x - log(x) with y = x, then one step   above -> x
 SDCAB_HD double lambert_w_exp(double x) {
+  const bool pos = x > 0.0;
+  const bool tail_lo = !(x > -36.0);
+  const bool tail_hi = x > 4.0;
   double w;
-  if (x > 0.0) {
-    if (x <= 4.0) {
-      w = householder5(x, 1.0);
-    } else if (x <= 576460752303423488.0) {
-      w = householder5(x - log_(x), x);
-    } else {
-      return x;
-    }
+  if (pos) {
+    w = tail_hi ? householder5(x - log_(x), x) : householder5(x, 1.0);
   } else {
-    if (x > -36.0) {
-      w = exp_crude(x);
-      if (x > -20.0) w = householder5(w, exp_crude(x - w));
-    } else {
-      return (x > -746.0) ? exp_(x) : 0.0;
-    }
+    w = exp_crude(x);
+    if (x > -20.0) w = householder5(w, exp_crude(x - w));
   }
-  return householder5(w, exp_(x - w));
+  const double e = exp_(tail_lo ? x : x - w);
+  if (tail_lo) return (x > -746.0) ? e : 0.0;
+  if (tail_hi && !(x <= 576460752303423488.0)) return x;
+  return householder5(w, e);
 }
 
 // w + log(w)                             (reference: math/lambert.h:210-214)
