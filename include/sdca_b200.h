@@ -47,7 +47,8 @@ typedef enum sdcab_status {
   SDCAB_ERR_NUM_DIM = -11,       /* LIBSDCA:num_dim / num_classes / num_examples */
   SDCAB_ERR_CUDA = -20,
   SDCAB_ERR_NO_DEVICE = -21,
-  SDCAB_ERR_TOO_LARGE = -22
+  SDCAB_ERR_TOO_LARGE = -22,
+  SDCAB_ERR_TIMEOUT = -23        /* a bounded wait inside a kernel ran out */
 } sdcab_status;
 
 const char* sdcab_status_string(int status);
@@ -216,7 +217,8 @@ size_t sdcab_eval_workspace_bytes(int64_t n, int64_t m, int64_t elem_size);
  * SDCAB_EVAL_SUMS(m) doubles:
  *   [0] sum of primal losses (before the objective's coefficient)
  *   [1] sum of dual losses   [2] primal regularizer   [3] dual regularizer
- *   [4] sum of rank losses   [5] number of examples   [6], [7] unused
+ *   [4] sum of rank losses   [5] number of examples
+ *   [6] device error word (0 = none; sdcab_eval_finish then returns SDCAB_ERR_TIMEOUT)   [7] unused
  *   [8 + r] number of examples whose label is outranked by exactly r classes.
  * Rows are independent, so shards of examples are evaluated separately and
  * their sums added (one all-reduce over the ranks) before sdcab_eval_finish.
@@ -273,7 +275,8 @@ int sdcab_eval_f64(const sdcab_objective* obj, const sdcab_problem* host_problem
                    sdcab_eval_record* record, double* accuracy);
 
 /* scores (n x m, example i at scores + m*i) = W'x_i or A K_i, device pointers:
- * the batched form of eval_scores (include/sdca/solver/eval/scores.h:9-47). */
+ * the batched form of eval_scores (include/sdca/solver/eval/scores.h:9-47).
+ * The float form synchronises the stream before it returns. */
 int sdcab_scores_f32_dev(const sdcab_problem* p, float* scores_dev, void* stream);
 int sdcab_scores_f64_dev(const sdcab_problem* p, double* scores_dev, void* stream);
 

@@ -16,11 +16,13 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
 #include "common_host.h"
 #include "eval_host.h"
+#include "gemm_tc.cuh"
 #include "losses.cuh"
 
 namespace sdcab {
@@ -367,6 +369,12 @@ __global__ void regularizer_combine_kernel(const double* __restrict__ partials, 
   }
 }
 
+// sums[6] carries the error word of the tensor-core GEMM (0 = none): a bounded
+// wait inside that kernel ran out; sdcab_eval_finish turns it into a status.
+__global__ void report_gemm_error_kernel(const int* err, double* sums) {
+  if (threadIdx.x == 0) sums[6] = static_cast<double>(*err);
+}
+
 __global__ void set_count_kernel(double* sums, double n) {
   if (threadIdx.x == 0) sums[5] = n;
 }
@@ -377,6 +385,7 @@ struct EvalLayout {
   size_t scores_bytes;   // chunk * m * elem, rounded up
   int max_blocks;
   size_t partials_bytes, hist_bytes, total;
+  size_t err_offset;     // one int: error word of the tensor-core GEMM
 };
 
 static EvalLayout eval_layout(long long n, long long m, long long elem, int sm_count) {
@@ -394,7 +403,8 @@ static EvalLayout eval_layout(long long n, long long m, long long elem, int sm_c
   L.max_blocks = std::max(1, sm_count) * 16;
   L.partials_bytes = (static_cast<size_t>(L.max_blocks) * 4 * sizeof(double) + 255) & ~static_cast<size_t>(255);
   L.hist_bytes = (static_cast<size_t>(m) * sizeof(unsigned long long) + 255) & ~static_cast<size_t>(255);
-  L.total = L.scores_bytes + L.partials_bytes + L.hist_bytes;
+  L.err_offset = L.scores_bytes + L.partials_bytes + L.hist_bytes;
+  L.total = L.err_offset + 256;
   return L;
 }
 
@@ -419,13 +429,39 @@ static int check_problem(const sdcab_objective* obj, const sdcab_problem* p) {
 }
 
 // scores of examples [first, first + count) into `out` (count x m)
+// The float feature GEMM runs on the tensor cores (gemm_tc.cuh) when the caller
+// provides an error word and the operands meet TMA's alignment rules;
+// SDCAB_GEMM=simt in the environment forces the CUDA-core kernel.
+inline bool tensor_core_gemm_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* env = std::getenv("SDCAB_GEMM");
+    enabled = (env && std::strcmp(env, "simt") == 0) ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+inline int scores_tc(const float* X, const float* W, float* out, int M, int N, int K, long long ld,
+                     int* tc_err, cudaStream_t stream) {
+  return tc::launch(X, W, out, M, N, K, ld, ld, N, tc_err, stream);
+}
+inline int scores_tc(const double*, const double*, double*, int, int, int, long long, int*,
+                     cudaStream_t) {
+  return SDCAB_ERR_NOT_IMPLEMENTED;
+}
+inline bool scores_tc_usable(const float* X, const float* W, long long ld) { return tc::usable(X, W, ld, ld); }
+inline bool scores_tc_usable(const double*, const double*, long long) { return false; }
+
 template <typename Data>
 int scores_chunk(const sdcab_problem* p, long long first, long long count, Data* out,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, int* tc_err = nullptr) {
   const Data* X = static_cast<const Data*>(p->x) + first * p->d;
   const int M = static_cast<int>(count), N = static_cast<int>(p->m), K = static_cast<int>(p->d);
   if (p->input_kind == SDCAB_INPUT_FEATURES) {
     // S[i][j] = sum_l X[i][l] W[j][l]   (eval/scores.h:9-26)
+    if (tc_err && tensor_core_gemm_enabled() && K >= 32 &&
+        scores_tc_usable(X, static_cast<const Data*>(p->w), p->d))
+      return scores_tc(X, static_cast<const Data*>(p->w), out, M, N, K, p->d, tc_err, stream);
     return launch_gemm<Data>(X, static_cast<const Data*>(p->w), out, M, N, K, p->d, p->d, p->m,
                              true, stream);
   }
@@ -456,8 +492,10 @@ int eval_sums_dev(const sdcab_objective* obj, const sdcab_problem* p, double* su
   double* partials = reinterpret_cast<double*>(base + L.scores_bytes);
   unsigned long long* hist = reinterpret_cast<unsigned long long*>(base + L.scores_bytes + L.partials_bytes);
 
+  int* tc_err = reinterpret_cast<int*>(base + L.err_offset);
   SDCAB_CUDA_TRY(cudaMemsetAsync(sums, 0, sizeof(double) * SDCAB_EVAL_SUMS(m), stream));
   SDCAB_CUDA_TRY(cudaMemsetAsync(hist, 0, sizeof(unsigned long long) * m, stream));
+  SDCAB_CUDA_TRY(cudaMemsetAsync(tc_err, 0, sizeof(int), stream));
   set_count_kernel<<<1, 32, 0, stream>>>(sums, static_cast<double>(n));
 
   if (p->is_train && p->input_kind == SDCAB_INPUT_FEATURES && p->include_primal_regularizer) {
@@ -491,7 +529,7 @@ int eval_sums_dev(const sdcab_objective* obj, const sdcab_problem* p, double* su
   }
   for (long long first = 0; first < n; first += L.chunk) {
     const long long count = std::min(L.chunk, n - first);
-    rc = scores_chunk<Data>(p, first, count, scores, stream);
+    rc = scores_chunk<Data>(p, first, count, scores, stream, tc_err);
     if (rc) return rc;
     g.n = count; g.first = first;
     const int blocks = static_cast<int>(std::max<long long>(
@@ -503,6 +541,7 @@ int eval_sums_dev(const sdcab_objective* obj, const sdcab_problem* p, double* su
   }
   hist_to_sums_kernel<<<std::max(1, static_cast<int>((m + 255) / 256)), 256, 0, stream>>>(
       hist, static_cast<int>(m), sums);
+  report_gemm_error_kernel<<<1, 32, 0, stream>>>(tc_err, sums);
   SDCAB_CUDA_TRY(cudaGetLastError());
   return SDCAB_OK;
 }
@@ -748,7 +787,17 @@ const char* sdcab_eval_fixed_scratch_error(void) { return sdcab::g_fixed_scratch
 
 int sdcab_scores_f32_dev(const sdcab_problem* p, float* scores, void* stream) {
   if (!p || !scores || !p->x) return SDCAB_ERR_ARG;
-  return sdcab::scores_chunk<float>(p, 0, p->n, scores, static_cast<cudaStream_t>(stream));
+  void* err = nullptr;
+  int rc = sdcab::workspace_reserve(3, 256, &err);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  SDCAB_CUDA_TRY(cudaMemsetAsync(err, 0, sizeof(int), s));
+  rc = sdcab::scores_chunk<float>(p, 0, p->n, scores, s, static_cast<int*>(err));
+  if (rc) return rc;
+  int host_err = 0;
+  SDCAB_CUDA_TRY(cudaMemcpyAsync(&host_err, err, sizeof(int), cudaMemcpyDeviceToHost, s));
+  SDCAB_CUDA_TRY(cudaStreamSynchronize(s));
+  return host_err ? SDCAB_ERR_TIMEOUT : SDCAB_OK;
 }
 int sdcab_scores_f64_dev(const sdcab_problem* p, double* scores, void* stream) {
   if (!p || !scores || !p->x) return SDCAB_ERR_ARG;

@@ -75,6 +75,7 @@ inline ObjectiveParams to_params(const sdcab_objective* o) {
 inline int eval_finish(const sdcab_objective* obj, int64_t m, const double* sums,
                        sdcab_eval_record* rec, double* accuracy) {
   if (!obj || !sums || !rec || m < 1) return SDCAB_ERR_ARG;
+  if (sums[6] != 0.0) return SDCAB_ERR_TIMEOUT;  // a bounded device wait ran out
   const ObjectiveParams q = to_params(obj);
   const double n = sums[5];
   rec->primal_loss = sums[0] * objective_coeff(q);

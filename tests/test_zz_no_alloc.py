@@ -63,7 +63,10 @@ def test_fixed_scratch_matches_ordinary_entry_point(cuda_lib):
             assert rc == 0, lib.sdcab_eval_fixed_scratch_error()
             tol = 1e-5 if dtype == np.float32 else 1e-12
             assert np.all(np.abs(got[:8] - want[:8]) <= tol * np.maximum(1, np.abs(want[:8]))), (oid, attempt)
-            assert np.array_equal(got[8:], want[8:]), (oid, attempt)
+            # rank counts: equal, except that float32 scores from the two GEMM kernels may
+            # order a near-tie differently
+            slack = 0 if dtype == np.float64 else max(4, n // 500)
+            assert np.abs(got[8:] - want[8:]).sum() <= slack, (oid, attempt)
 
 
 def test_fixed_scratch_rejects_what_does_not_fit(cuda_lib):
