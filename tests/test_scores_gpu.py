@@ -42,13 +42,14 @@ def test_scores_match_float64_product(cuda_lib, dtype):
         X = rng.standard_normal((n, d)).astype(dtype)
         W = rng.standard_normal((m, d)).astype(dtype)
         A = rng.standard_normal((d, m)).astype(dtype)
-        # error bound of a float dot product of length d, relative to sum |x||w|
+        # error of a length-d dot product in the data type, relative to sum |x||w|:
+        # a few ulps plus the usual sqrt(d) growth
         eps = np.finfo(dtype).eps
         for got, ref, mag in ((scores(cuda_lib, X, W=W), X.astype(np.float64) @ W.astype(np.float64).T,
                                np.abs(X).astype(np.float64) @ np.abs(W).astype(np.float64).T),
                               (scores(cuda_lib, X, A=A), X.astype(np.float64) @ A.astype(np.float64),
                                np.abs(X).astype(np.float64) @ np.abs(A).astype(np.float64))):
-            bound = 4 * eps * np.sqrt(d) * mag / np.sqrt(d) + 8 * eps * mag / 8
+            bound = (16 + 2 * np.sqrt(d)) * eps * mag
             assert (np.abs(got - ref) <= bound + 1e-30).all(), (n, d, m, np.abs(got - ref).max())
 
 
