@@ -308,18 +308,35 @@ eval_loss_kernel(LossArgs g, const Data* __restrict__ scores, const Data* __rest
     if (local_hist[i]) atomicAdd(&hist[i], static_cast<unsigned long long>(local_hist[i]));
 }
 
-// sums[0..3] += block partials in block order (one block, fixed order)
-__global__ void combine_partials_kernel(const double* __restrict__ partials, int blocks,
-                                        double* __restrict__ sums) {
+// sums[0..4] += block partials.  One block of 256 threads: thread t adds the
+// partials of blocks t, t + 256, ... in order, then a fixed tree combines the
+// 256 values, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256)
+combine_partials_kernel(const double* __restrict__ partials, int blocks,
+                        double* __restrict__ sums) {
+  __shared__ double sh[4][256];
   const int t = threadIdx.x;
-  if (t < 4) {
-    double s = 0;
-    for (int b = 0; b < blocks; ++b) s += partials[static_cast<size_t>(b) * 4 + t];
+  double s[4] = {0, 0, 0, 0};
+  for (int b = t; b < blocks; b += 256) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) s[q] += partials[static_cast<size_t>(b) * 4 + q];
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) sh[q][t] = s[q];
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (t < o) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) sh[q][t] += sh[q][t + o];
+    }
+    __syncthreads();
+  }
+  if (t == 0) {
     // [0] primal loss, [1] dual loss, [2]+[3] regularisers, [4] rank loss
-    if (t == 0) sums[0] += s;
-    if (t == 1) sums[1] += s;
-    if (t == 2) { sums[2] += s; sums[3] += s; }
-    if (t == 3) sums[4] += s;
+    sums[0] += sh[0][0];
+    sums[1] += sh[1][0];
+    sums[2] += sh[2][0]; sums[3] += sh[2][0];
+    sums[4] += sh[3][0];
   }
 }
 
@@ -358,13 +375,22 @@ dot_partials_kernel(const Data* __restrict__ w, const Data* __restrict__ w0, lon
 }
 
 // eval/regularizer.h:22-63 with objective_base.h:59-89
-__global__ void regularizer_combine_kernel(const double* __restrict__ partials, int blocks,
-                                           int has_w0, double* __restrict__ sums) {
-  if (threadIdx.x == 0) {
-    double ww = 0, w0w = 0;
-    for (int b = 0; b < blocks; ++b) { ww += partials[2 * b]; w0w += partials[2 * b + 1]; }
-    const double regul = ww / 2;
-    sums[2] += has_w0 ? regul - w0w : regul;
+__global__ void __launch_bounds__(256)
+regularizer_combine_kernel(const double* __restrict__ partials, int blocks, int has_w0,
+                           double* __restrict__ sums) {
+  __shared__ double sh[2][256];
+  const int t = threadIdx.x;
+  double ww = 0, w0w = 0;
+  for (int b = t; b < blocks; b += 256) { ww += partials[2 * b]; w0w += partials[2 * b + 1]; }
+  sh[0][t] = ww; sh[1][t] = w0w;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (t < o) { sh[0][t] += sh[0][t + o]; sh[1][t] += sh[1][t + o]; }
+    __syncthreads();
+  }
+  if (t == 0) {
+    const double regul = sh[0][0] / 2;
+    sums[2] += has_w0 ? regul - sh[1][0] : regul;
     sums[3] += regul;
   }
 }
@@ -503,7 +529,7 @@ int eval_sums_dev(const sdcab_objective* obj, const sdcab_problem* p, double* su
     const int blocks = static_cast<int>(std::min<long long>(L.max_blocks / 2, (count + 255) / 256));
     dot_partials_kernel<Data><<<blocks, 256, 0, stream>>>(
         static_cast<const Data*>(p->w), static_cast<const Data*>(p->w0), count, partials);
-    regularizer_combine_kernel<<<1, 32, 0, stream>>>(partials, blocks, p->w0 ? 1 : 0, sums);
+    regularizer_combine_kernel<<<1, 256, 0, stream>>>(partials, blocks, p->w0 ? 1 : 0, sums);
   }
 
   LossArgs g;
@@ -537,7 +563,7 @@ int eval_sums_dev(const sdcab_objective* obj, const sdcab_problem* p, double* su
     const Data* A = static_cast<const Data*>(p->a);
     if (fl) kf<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
     else kd<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
-    combine_partials_kernel<<<1, 32, 0, stream>>>(partials, blocks, sums);
+    combine_partials_kernel<<<1, 256, 0, stream>>>(partials, blocks, sums);
   }
   hist_to_sums_kernel<<<std::max(1, static_cast<int>((m + 255) / 256)), 256, 0, stream>>>(
       hist, static_cast<int>(m), sums);
@@ -694,7 +720,7 @@ int eval_sums_fixed_scratch(const sdcab_objective* obj, const sdcab_problem* p, 
     const int blocks = static_cast<int>(std::min<long long>(max_blocks / 2, (count + 255) / 256));
     dot_partials_kernel<Data><<<blocks, 256, 0, stream>>>(
         static_cast<const Data*>(p->w), static_cast<const Data*>(p->w0), count, partials);
-    regularizer_combine_kernel<<<1, 32, 0, stream>>>(partials, blocks, p->w0 ? 1 : 0, sums);
+    regularizer_combine_kernel<<<1, 256, 0, stream>>>(partials, blocks, p->w0 ? 1 : 0, sums);
   }
   LossArgs g;
   g.obj = to_params(obj);
@@ -727,7 +753,7 @@ int eval_sums_fixed_scratch(const sdcab_objective* obj, const sdcab_problem* p, 
     const Data* A = static_cast<const Data*>(p->a);
     if (fl) kf<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
     else kd<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
-    combine_partials_kernel<<<1, 32, 0, stream>>>(partials, blocks, sums);
+    combine_partials_kernel<<<1, 256, 0, stream>>>(partials, blocks, sums);
   }
   hist_to_sums_kernel<<<std::max(1, static_cast<int>((m + 255) / 256)), 256, 0, stream>>>(
       hist, static_cast<int>(m), sums);
