@@ -280,6 +280,74 @@ int sdcab_eval_f64(const sdcab_objective* obj, const sdcab_problem* host_problem
 int sdcab_scores_f32_dev(const sdcab_problem* p, float* scores_dev, void* stream);
 int sdcab_scores_f64_dev(const sdcab_problem* p, double* scores_dev, void* stream);
 
+/* ---------------------------------------------------------------- fit ---- */
+
+/* solver_status of the reference (include/sdca/solver/solverdef.h:11-20). */
+enum {
+  SDCAB_FIT_NONE = 0,
+  SDCAB_FIT_SOLVING = 1,
+  SDCAB_FIT_SOLVED = 2,
+  SDCAB_FIT_NO_PROGRESS = 3,
+  SDCAB_FIT_MAX_EPOCH = 4,
+  SDCAB_FIT_MAX_CPU_TIME = 5,
+  SDCAB_FIT_MAX_WALL_TIME = 6,
+  SDCAB_FIT_FAILED = 7
+};
+
+/* stopping_criteria of the reference (include/sdca/solver/solverdef.h:50-57)
+ * without the time limits. */
+typedef struct sdcab_fit_criteria {
+  double epsilon;         /* relative duality gap to reach                          */
+  int64_t max_epoch;
+  int64_t eval_epoch;     /* evaluate every eval_epoch epochs; 0: only at the end   */
+  int32_t eval_on_start;
+  int32_t reserved;
+} sdcab_fit_criteria;
+
+typedef struct sdcab_fit_result {
+  int32_t status;         /* SDCAB_FIT_*                                            */
+  int32_t reserved;
+  int64_t epoch;          /* epochs run                                             */
+  int64_t num_evals;      /* records written to `evals`                             */
+  double solve_seconds;   /* device time of the update steps                        */
+  double eval_seconds;    /* device time of the evaluations                         */
+} sdcab_fit_result;
+
+/* The example order of the first num_epochs epochs of the reference's solver
+ * for n training examples: a default-seeded std::minstd_rand driving
+ * std::shuffle (as libstdc++ implements it) on one index vector that is kept
+ * from epoch to epoch (include/sdca/solver.h:59,77-79,96-100).  perm (host)
+ * receives num_epochs * n indices. */
+int sdcab_epoch_permutations(int64_t n, int64_t num_epochs, int64_t* perm);
+
+/*
+ * SDCA fit on the current device: solver::solve of the reference
+ * (include/sdca/solver.h:39-117) with update_variables
+ * (include/sdca/solver/update.h:52-107) as the step and the evaluation above
+ * after every eval_epoch epochs.  `train` holds device pointers: the kernel
+ * matrix (n x n, input_kind SDCAB_INPUT_KERNEL, d == n) or the features
+ * (d x n) in x, labels, and the variables the fit updates in place -- a
+ * (m x n dual variables, read as the starting point) and, for features, w
+ * (d x m primal variables, kept equal to X A').  The objective must be one of
+ * the hinge family (SDCAB_OBJ_L2_HINGE_TOPK[_SMOOTH], SDCAB_OBJ_L2_TOPK_HINGE[_SMOOTH];
+ * Crammer-Singer is SDCAB_OBJ_L2_TOPK_HINGE with k = 1); others return
+ * SDCAB_ERR_NOT_IMPLEMENTED.  The steps of one epoch are sequential by
+ * definition; each step spreads its score product over the whole GPU.
+ *   permutations: optional host array, max_epoch * n example indices (the
+ *                 order of every epoch); NULL uses sdcab_epoch_permutations.
+ *   evals:        host array of evals_cap records, one per evaluation in order
+ *                 (later ones are dropped when it is full); may be NULL.
+ * The call synchronises the stream at every evaluation.
+ */
+int sdcab_fit_f32_dev(const sdcab_objective* obj, const sdcab_problem* train,
+                      const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                      sdcab_eval_record* evals, int64_t evals_cap,
+                      sdcab_fit_result* result, void* stream);
+int sdcab_fit_f64_dev(const sdcab_objective* obj, const sdcab_problem* train,
+                      const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                      sdcab_eval_record* evals, int64_t evals_cap,
+                      sdcab_fit_result* result, void* stream);
+
 /* ------------------------------------------------------------- memory ---- */
 
 /* Page-locked host memory for callers that want the host-buffer entry points

@@ -24,4 +24,6 @@ from .binding import (  # noqa: F401
     eval_finish,
     make_objective,
     make_problem,
+    fit_,
+    epoch_permutations,
 )

@@ -293,3 +293,62 @@ def eval_finish(objective, m, sums_host):
                                    sums_host.ctypes.data_as(C.c_void_p), C.byref(rec),
                                    acc.ctypes.data_as(C.c_void_p)), "sdcab_eval_finish")
     return record_to_dict(rec, acc)
+
+
+# ---- fit -----------------------------------------------------------------------
+
+class FitCriteria(C.Structure):
+    _fields_ = [("epsilon", C.c_double), ("max_epoch", C.c_int64), ("eval_epoch", C.c_int64),
+                ("eval_on_start", C.c_int32), ("reserved", C.c_int32)]
+
+
+class FitResult(C.Structure):
+    _fields_ = [("status", C.c_int32), ("reserved", C.c_int32), ("epoch", C.c_int64),
+                ("num_evals", C.c_int64), ("solve_seconds", C.c_double),
+                ("eval_seconds", C.c_double)]
+
+
+FIT_STATUS = ("none", "solving", "solved", "no_progress", "max_epoch", "max_cpu_time",
+              "max_wall_time", "failed")
+
+
+def fit_result_to_dict(res, evals):
+    count = min(res.num_evals, len(evals))
+    return dict(status=FIT_STATUS[res.status], status_code=res.status, epoch=res.epoch,
+                num_evals=res.num_evals, solve_seconds=res.solve_seconds,
+                eval_seconds=res.eval_seconds,
+                history=[{f: getattr(evals[i], f) for f in RECORD_FIELDS} for i in range(count)])
+
+
+def epoch_permutations(n, num_epochs):
+    """Example order of the reference's solver for its first ``num_epochs`` epochs."""
+    perm = np.zeros((num_epochs, n), dtype=np.int64)
+    _check(lib().sdcab_epoch_permutations(C.c_int64(n), C.c_int64(num_epochs),
+                                          perm.ctypes.data_as(C.c_void_p)),
+           "sdcab_epoch_permutations")
+    return perm
+
+
+def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
+         precision="double", epsilon=1e-3, max_epoch=1000, eval_epoch=10, eval_on_start=False,
+         permutations=None):
+    """SDCA fit on torch CUDA tensors, in place on ``A`` (n x m) and ``W`` (m x d).
+
+    Mirrors ``matsdca_fit``'s stopping options (src/matlab/mex_solve.cpp:505-528 of the
+    reference); returns status, epochs and the evaluation records."""
+    obj = objective if isinstance(objective, Objective) else make_objective(objective, c, gamma, k, precision)
+    prob = make_problem(X, labels, A, W, None, None, kernel, True)
+    crit = FitCriteria(epsilon, max_epoch, eval_epoch, 1 if eval_on_start else 0, 0)
+    cap = int(max_epoch) + 4
+    evals = (EvalRecord * cap)()
+    res = FitResult()
+    perm = None
+    if permutations is not None:
+        perm = np.ascontiguousarray(permutations, dtype=np.int64)
+        if perm.size < max_epoch * X.shape[0]:
+            raise SdcabError(-1, "fit_: permutations must hold max_epoch * n indices")
+    fn = getattr(lib(), "sdcab_fit_%s_dev" % _suffix(str(X.dtype)))
+    _check(fn(C.byref(obj), C.byref(prob), C.byref(crit),
+              perm.ctypes.data_as(C.c_void_p) if perm is not None else None, evals,
+              C.c_int64(cap), C.byref(res), _torch_stream()), "sdcab_fit_dev")
+    return fit_result_to_dict(res, evals)

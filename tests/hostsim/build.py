@@ -58,6 +58,34 @@ class HostSim:
         assert rc == 0, rc
         return b.record_to_dict(rec, acc)
 
+    def fit(self, objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
+            precision="double", epsilon=1e-3, max_epoch=100, eval_epoch=1, eval_on_start=False,
+            permutations=None):
+        """Runs the fit in place on A (and W); returns status, epoch and the records."""
+        from libsdca_b200 import binding as b
+        obj = b.make_objective(objective, c, gamma, k, precision,
+                               from_name=self.lib.sdcab_hostsim_objective_from_name)
+        prob = b.make_problem(X, labels, A, W, None, None, kernel, True)
+        crit = b.FitCriteria(epsilon, max_epoch, eval_epoch, 1 if eval_on_start else 0, 0)
+        cap = max_epoch + 4
+        evals = (b.EvalRecord * cap)()
+        res = b.FitResult()
+        perm = None
+        if permutations is not None:
+            perm = np.ascontiguousarray(permutations, dtype=np.int64)
+        rc = self.lib.sdcab_hostsim_fit(
+            C.byref(obj), C.byref(prob), 0 if X.dtype == np.float32 else 1, C.byref(crit),
+            perm.ctypes.data_as(C.c_void_p) if perm is not None else None, evals, C.c_int64(cap),
+            C.byref(res))
+        assert rc == 0, rc
+        return b.fit_result_to_dict(res, evals)
+
+    def epoch_permutations(self, n, epochs):
+        perm = np.zeros((epochs, n), dtype=np.int64)
+        self.lib.sdcab_hostsim_epoch_permutations(C.c_int64(n), C.c_int64(epochs),
+                                                  perm.ctypes.data_as(C.c_void_p))
+        return perm
+
 
 def load():
     return HostSim()

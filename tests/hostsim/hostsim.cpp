@@ -149,3 +149,108 @@ extern "C" int sdcab_hostsim_objective_from_name(const char* name, double c, dou
                                                  int64_t k, sdcab_objective* out) {
   return sdcab::objective_from_name(name, c, gamma, k, out);
 }
+
+// ---- fit: the device code's update step with one lane, driven by the host-side
+// epoch order and stopping rule the library uses ---------------------------------
+#include "../../libsdca_b200/csrc/fit_host.h"
+#include "../../libsdca_b200/csrc/update_core.cuh"
+
+namespace {
+
+template <typename Data, typename R>
+int run_fit(const sdcab_objective* obj, const sdcab_problem* p, const sdcab_fit_criteria* crit,
+            const int64_t* permutations, sdcab_eval_record* evals, int64_t cap,
+            sdcab_fit_result* res) {
+  using namespace sdcab;
+  const ObjectiveParams q = to_params(obj);
+  const int m = static_cast<int>(p->m);
+  const long long n = p->n, d = p->d;
+  const Data* X = static_cast<const Data*>(p->x);
+  Data* A = static_cast<Data*>(const_cast<void*>(p->a));
+  Data* W = static_cast<Data*>(const_cast<void*>(p->w));
+  const bool kernel = (p->input_kind == SDCAB_INPUT_KERNEL);
+  std::vector<Data> s(m), v(m), old(m);
+  std::vector<double> sums(SDCAB_EVAL_SUMS(m));
+  std::vector<sdcab_eval_record> hist;
+  sdcab_problem ep = *p;
+  ep.is_train = 1; ep.a_row_offset = 0; ep.include_primal_regularizer = 1;
+  auto evaluate = [&]() {
+    run_eval<Data, R>(obj, &ep, sums.data());
+    sdcab_eval_record rec;
+    eval_finish(obj, m, sums.data(), &rec, nullptr);
+    hist.push_back(rec);
+    if (evals && (int64_t)hist.size() <= cap) evals[hist.size() - 1] = rec;
+  };
+  const double eps_floor = std::max(double(num<Data>::eps()), double(num<R>::eps()));
+  auto check = [&](int st, int64_t epoch) {
+    return check_stopping(st, hist.empty() ? nullptr : &hist.back(),
+                          hist.size() > 1 ? &hist[hist.size() - 2] : nullptr, crit->epsilon,
+                          epoch, crit->max_epoch, eps_floor);
+  };
+  int64_t epoch = 0;
+  int status = crit->max_epoch > 0 ? SDCAB_FIT_SOLVING : SDCAB_FIT_MAX_EPOCH;
+  bool evaluated = false;
+  if (crit->eval_on_start) { evaluate(); status = check(status, epoch); }
+  MinstdRand gen;
+  std::vector<int64_t> order(n);
+  for (long long i = 0; i < n; ++i) order[i] = i;
+  while (status == SDCAB_FIT_SOLVING) {
+    evaluated = false;
+    const int64_t* ord;
+    if (permutations) ord = permutations + epoch * n;
+    else { shuffle_like_libstdcxx(order, gen); ord = order.data(); }
+    for (long long step = 0; step < n; ++step) {
+      const long long i = ord[step];
+      Data norm2;
+      if (kernel) {
+        norm2 = X[n * i + i];
+      } else {
+        double t = 0;
+        for (long long r = 0; r < d; ++r) t = std::fma(double(X[d * i + r]), double(X[d * i + r]), t);
+        norm2 = Data(t);
+      }
+      if (!(norm2 > 0)) continue;
+      for (int j = 0; j < m; ++j) {
+        double acc = 0;
+        if (kernel) for (long long l = 0; l < n; ++l) acc = std::fma(double(A[l * m + j]), double(X[n * i + l]), acc);
+        else for (long long r = 0; r < d; ++r) acc = std::fma(double(W[d * j + r]), double(X[d * i + r]), acc);
+        s[j] = Data(acc);
+      }
+      Data* a = A + i * m;
+      for (int j = 0; j < m; ++j) old[j] = a[j];
+      update_dual_variables_multiclass<R, Data>(q, norm2, s.data(), a, v.data(), m, (int)p->labels[i]);
+      if (!kernel) {
+        Data asum = 0;
+        for (int j = 0; j < m; ++j) { old[j] -= a[j]; asum += abs_(old[j]); }
+        if (asum > num<Data>::eps())
+          for (int j = 0; j < m; ++j)
+            for (long long r = 0; r < d; ++r) W[d * j + r] = W[d * j + r] - X[d * i + r] * old[j];
+      }
+    }
+    ++epoch;
+    if (crit->eval_epoch > 0 && epoch % crit->eval_epoch == 0) { evaluate(); evaluated = true; }
+    status = check(status, epoch);
+  }
+  if (!evaluated && !(crit->eval_on_start && epoch == 0)) evaluate();
+  res->status = status; res->epoch = epoch; res->num_evals = (int64_t)hist.size();
+  res->solve_seconds = 0; res->eval_seconds = 0;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int sdcab_hostsim_fit(const sdcab_objective* obj, const sdcab_problem* p, int dtype,
+                                 const sdcab_fit_criteria* crit, const int64_t* permutations,
+                                 sdcab_eval_record* evals, int64_t cap, sdcab_fit_result* res) {
+  if (!sdcab::objective_has_update(obj->id)) return SDCAB_ERR_NOT_IMPLEMENTED;
+  const bool f = (obj->precision == SDCAB_PRECISION_FLOAT);
+  if (dtype == 0) return f ? run_fit<float, float>(obj, p, crit, permutations, evals, cap, res)
+                           : run_fit<float, double>(obj, p, crit, permutations, evals, cap, res);
+  return f ? run_fit<double, float>(obj, p, crit, permutations, evals, cap, res)
+           : run_fit<double, double>(obj, p, crit, permutations, evals, cap, res);
+}
+
+extern "C" int sdcab_hostsim_epoch_permutations(int64_t n, int64_t epochs, int64_t* perm) {
+  sdcab::epoch_permutations(n, epochs, perm);
+  return 0;
+}

@@ -1,0 +1,103 @@
+"""Parity of the device fit (one launch per SDCA step, evaluation per epoch;
+through the C ABI) with the reference's solver::solve on the same problems:
+status, epoch count, final dual / primal variables and the evaluation records."""
+import numpy as np
+import pytest
+
+from libsdca_b200.synth import kernel_problem
+from tests.test_oracle_restatement import random_problem
+from tests.util import stable_seed
+
+pytestmark = pytest.mark.gpu
+
+HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth")
+REF_STATUS = ("none", "solving", "solved", "no_progress", "max_epoch", "max_cpu_time",
+              "max_wall_time", "failed")
+
+
+def dev(x):
+    import torch
+    return None if x is None else torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def run_both(ref, mod, objective, data, labels, m, kernel, dtype, permutations=None, **kw):
+    from oracle.refapi import OBJECTIVES as IDS
+    n, d = data.shape
+    fit_kw = dict(epsilon=kw.pop("epsilon", 1e-3), max_epoch=kw.pop("max_epoch", 30),
+                  eval_epoch=kw.pop("eval_epoch", 1), eval_on_start=kw.pop("eval_on_start", False))
+    A_ref = np.zeros((n, m), dtype=dtype); W_ref = np.zeros((m, d), dtype=dtype)
+    r = ref.fit(objective, data, A_ref, labels, W=None if kernel else W_ref, kernel=kernel,
+                **fit_kw, **kw)
+    A = dev(np.zeros((n, m), dtype=dtype)); W = None if kernel else dev(np.zeros((m, d), dtype=dtype))
+    g = mod.fit_(IDS[objective], dev(data), dev(labels), A, W=W, kernel=kernel,
+                 permutations=permutations, **fit_kw, **kw)
+    return r, g, A_ref, W_ref, A.cpu().numpy(), None if kernel else W.cpu().numpy()
+
+
+def compare(r, g, A_ref, W_ref, A, W, tol, what):
+    assert g["status"] == REF_STATUS[r["status"]], (what, g["status"], r["status"])
+    assert g["epoch"] == r["epoch"], what
+    assert g["num_evals"] == len(r["history"]), what
+    # final variables: |difference| against the largest variable
+    assert np.abs(A - A_ref).max() <= tol * max(1.0, np.abs(A_ref).max()), (what, np.abs(A - A_ref).max())
+    if W is not None:
+        assert np.abs(W - W_ref).max() <= tol * max(1.0, np.abs(W_ref).max()) * W.shape[1], what
+    for e, (rec, ref_rec) in enumerate(zip(g["history"], r["history"])):
+        for i, f in enumerate(("primal", "dual")):
+            assert abs(rec[f] - ref_rec[i]) <= 10 * tol * max(1.0, abs(ref_rec[i])), (what, e, f)
+
+
+@pytest.mark.parametrize("objective", HINGE)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_kernel_fit_matches_reference(ref, cuda_lib, objective, dtype):
+    tol = 1e-9 if dtype == np.float64 else 2e-4
+    for n, dim, m, k in ((120, 8, 6, 1), (700, 16, 37, 3), (1500, 32, 150, 5)):
+        K, labels = kernel_problem(n=n, dim=dim, m=m, seed=stable_seed("gpu-fit", objective, n) % 1000,
+                                   dtype=dtype)
+        out = run_both(ref, cuda_lib, objective, K, labels, m, True, dtype, c=1.0, gamma=0.5, k=k,
+                       max_epoch=15)
+        compare(*out, tol, (objective, n, m, k))
+
+
+@pytest.mark.parametrize("objective", HINGE)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_feature_fit_matches_reference(ref, cuda_lib, objective, dtype):
+    rng = np.random.default_rng(stable_seed("gpu-fit-features", objective, str(dtype)))
+    tol = 1e-9 if dtype == np.float64 else 2e-4
+    for n, d, m, k in ((90, 7, 5, 2), (600, 50, 40, 1), (400, 300, 20, 4)):
+        X, labels, _ = random_problem(rng, n, d, m, dtype, False)
+        out = run_both(ref, cuda_lib, objective, X, labels, m, False, dtype, c=0.7, gamma=1.0, k=k,
+                       max_epoch=10, eval_epoch=2)
+        compare(*out, tol, (objective, n, d, m, k))
+
+
+def test_crammer_singer_medium(ref, cuda_lib):
+    """The shape of the full-size problem at a size the CPU solver finishes quickly:
+    RBF kernel of Gaussian blobs, msvm (top-k hinge beta, k = 1), gap checked every epoch."""
+    K, labels = kernel_problem(n=4000, dim=128, m=100, seed=11)
+    out = run_both(ref, cuda_lib, "l2_topk_hinge", K, labels, 100, True, np.float64, c=1.0, k=1,
+                   max_epoch=50)
+    compare(*out, 1e-9, "crammer-singer n=4000")
+    assert out[1]["status"] == "solved"
+
+
+def test_stopping_paths_and_given_order(ref, cuda_lib):
+    K, labels = kernel_problem(n=200, dim=4, m=4, seed=3)
+    args = (ref, cuda_lib, "l2_topk_hinge", K, labels, 4, True, np.float64)
+    compare(*run_both(*args, eval_on_start=True, max_epoch=2, epsilon=1e-9), 1e-9, "on start")
+    compare(*run_both(*args, eval_epoch=0, max_epoch=4), 1e-9, "no evaluation until the end")
+    compare(*run_both(*args, max_epoch=0), 1e-9, "no epochs")
+    # an order passed in by the caller is followed as given
+    perm = cuda_lib.epoch_permutations(200, 6)
+    assert np.array_equal(perm, ref.epoch_permutations(200, 6))
+    compare(*run_both(*args, max_epoch=6, epsilon=0.0, permutations=perm), 1e-9, "given order")
+
+
+def test_rejects_what_it_cannot_fit(cuda_lib):
+    from libsdca_b200.binding import SdcabError
+    K, labels = kernel_problem(n=50, dim=4, m=4, seed=3)
+    A = dev(np.zeros((50, 4)))
+    with pytest.raises(SdcabError):
+        cuda_lib.fit_(0, dev(K), dev(labels), A, kernel=True)   # softmax: no device step yet
+    with pytest.raises(SdcabError):
+        cuda_lib.fit_(4, dev(K[:, :40].copy()), dev(labels), A, kernel=True)  # kernel not square

@@ -1,0 +1,74 @@
+"""The SDCA step of the CUDA sources (update_core.cuh), the epoch order and the
+stopping rule (fit_host.h), compiled for the host with one lane, against the
+reference's solver on the same problems."""
+import numpy as np
+import pytest
+
+from libsdca_b200.synth import kernel_problem
+from tests.test_oracle_restatement import random_problem
+from tests.util import stable_seed
+
+HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth")
+REF_STATUS = ("none", "solving", "solved", "no_progress", "max_epoch", "max_cpu_time",
+              "max_wall_time", "failed")
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 10, 101, 1000, 46340, 46341, 50000])
+def test_epoch_order_matches_std_shuffle(ref, hostsim, n):
+    epochs = 3
+    assert np.array_equal(hostsim.epoch_permutations(n, epochs), ref.epoch_permutations(n, epochs))
+
+
+def check_fit(ref, hostsim, objective, data, labels, kernel, dtype, tol, **kw):
+    from oracle.refapi import OBJECTIVES as IDS
+    n = data.shape[0]
+    m = int(labels.max()) + 1 if kw.get("m") is None else kw.pop("m")
+    d = data.shape[1]
+    fit_kw = dict(epsilon=kw.pop("epsilon", 1e-3), max_epoch=kw.pop("max_epoch", 30),
+                  eval_epoch=kw.pop("eval_epoch", 1), eval_on_start=kw.pop("eval_on_start", False))
+    A_ref = np.zeros((n, m), dtype=dtype); W_ref = np.zeros((m, d), dtype=dtype)
+    A = np.zeros((n, m), dtype=dtype); W = np.zeros((m, d), dtype=dtype)
+    r = ref.fit(objective, data, A_ref, labels, W=None if kernel else W_ref, kernel=kernel,
+                **fit_kw, **kw)
+    h = hostsim.fit(IDS[objective], data, labels, A, W=None if kernel else W, kernel=kernel,
+                    **fit_kw, **kw)
+    assert h["status"] == REF_STATUS[r["status"]], (h["status"], r["status"])
+    assert h["epoch"] == r["epoch"]
+    assert h["num_evals"] == len(r["history"])
+    scale = max(1.0, np.abs(A_ref).max())
+    assert np.abs(A - A_ref).max() <= tol * scale, np.abs(A - A_ref).max()
+    if not kernel:
+        assert np.abs(W - W_ref).max() <= tol * max(1.0, np.abs(W_ref).max()) * d
+    last, rlast = h["history"][-1], r["history"][-1]
+    for i, f in enumerate(("primal", "dual")):
+        assert abs(last[f] - rlast[i]) <= 10 * tol * max(1.0, abs(rlast[i])), (f, last[f], rlast[i])
+
+
+@pytest.mark.parametrize("objective", HINGE)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_kernel_fit_matches_reference(ref, hostsim, objective, dtype):
+    K, labels = kernel_problem(n=120, dim=8, m=6, seed=stable_seed("fit", objective) % 1000, dtype=dtype)
+    tol = 1e-9 if dtype == np.float64 else 2e-4
+    for k in (1, 2):
+        check_fit(ref, hostsim, objective, K, labels, True, dtype, tol, m=6, c=1.0, gamma=0.5, k=k)
+
+
+@pytest.mark.parametrize("objective", HINGE)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_feature_fit_matches_reference(ref, hostsim, objective, dtype):
+    rng = np.random.default_rng(stable_seed("fit-features", objective, str(dtype)))
+    X, labels, _ = random_problem(rng, 90, 7, 5, dtype, False)
+    tol = 1e-9 if dtype == np.float64 else 2e-4
+    check_fit(ref, hostsim, objective, X, labels, False, dtype, tol, m=5, c=0.7, gamma=1.0, k=2,
+              max_epoch=12, eval_epoch=3)
+
+
+def test_stopping_paths(ref, hostsim):
+    K, labels = kernel_problem(n=60, dim=4, m=4, seed=3)
+    # evaluation before the first epoch, epoch limit reached, and no evaluation until the end
+    check_fit(ref, hostsim, "l2_topk_hinge", K, labels, True, np.float64, 1e-9, m=4,
+              eval_on_start=True, max_epoch=2, epsilon=1e-9)
+    check_fit(ref, hostsim, "l2_topk_hinge", K, labels, True, np.float64, 1e-9, m=4,
+              eval_epoch=0, max_epoch=4)
+    check_fit(ref, hostsim, "l2_topk_hinge", K, labels, True, np.float64, 1e-9, m=4,
+              max_epoch=0)
