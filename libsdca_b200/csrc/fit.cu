@@ -2,12 +2,17 @@
 // (include/sdca/solver.h:39-117) with update_variables
 // (include/sdca/solver/update.h:52-107) as the step.
 //
-// The steps of an epoch form a sequential chain -- step s reads the dual
-// variables step s-1 wrote -- so the unit of parallelism is the inside of one
-// step: its score product A K_i (or W'x_i) is spread over every SM, and the
-// block that finishes last adds the per-block partial sums in a fixed order and
-// runs the objective's update on one warp.  One launch per step, no block ever
-// waits for another; the launches of an epoch are replayed from a CUDA graph.
+// The steps of an epoch form a sequential chain -- step s reads the variables
+// step s-1 wrote -- but a step changes the dual variables of one example only,
+// so the scores of the next 64 examples can be formed together, from the
+// variables as they are now, by one product on the whole GPU (64 columns of K
+// against A, or 64 examples against W); the chain itself then runs inside a
+// single thread block that corrects the remaining score rows after every step
+// by the one-example change (a 64 x 64 block of K, or of the examples' Gram
+// matrix, is all it needs).  That turns N matrix-vector products per epoch into
+// N / 64 matrix products and keeps the sequential part on chip.  For features
+// the primal variables receive the block's rank-one changes afterwards, in
+// step order.
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
@@ -16,6 +21,7 @@
 #include "common_host.h"
 #include "eval_host.h"
 #include "fit_host.h"
+#include "gemm_simt.cuh"
 #include "update_core.cuh"
 
 namespace sdcab {
@@ -23,239 +29,428 @@ namespace {
 
 constexpr int kFitThreads = 512;
 constexpr int kFitWarps = kFitThreads / 32;
-constexpr int kStepsPerGraph = 500;
+constexpr int kBlockSteps = 64;   // steps whose score products are formed together
 
-struct FitState {
-  long long step;        // position in the epoch's example order
-  unsigned int ticket;   // blocks that have delivered their partial sums
-  unsigned int pad;
+// ---- the chain ---------------------------------------------------------------
+// One thread block walks through the `count` steps of a block of examples
+// i_0, i_1, ...  It starts from S[b] = scores of example i_b under the variables
+// the block began with; after step b changed a_{i_b} by delta, the scores of
+// every later example of the block move by delta * G[b][b''], with
+// G[b][b''] = K[i_b, i_b''] (kernel input) or -<x_{i_b}, x_{i_b''}> with
+// delta = a_old - a_new (features, update.h:77-84), so S[b''] += delta * G[b][b'']
+// keeps the rows current.  Rows are corrected in step order, which fixes the
+// order of the floating-point sums.
+struct ChainArgs {
+  ObjectiveParams o;
+  const int64_t* order;    // the block's examples: order[0 .. count)
+  const int64_t* labels;
+  double* S;               // count x m, scores at the start of the block (updated in place
+                           // when they do not fit on chip)
+  const double* G;         // kBlockSteps x kBlockSteps (row b = example i_b)
+  void* A;                 // dual variables, n x m
+  void* D;                 // features: count x m, a_old - a_new of every step (0 if skipped)
+  int m, count, kernel_input, s_on_chip;
 };
 
-template <typename T> __device__ __forceinline__ T ld_cg(const T* p) { return __ldcg(p); }
+#ifdef SDCAB_FIT_PROFILE
+// Cycle counts of the chain's phases (a build for measurements only): thread 0
+// adds up in shared memory and the totals go to global memory at the end.
+__device__ unsigned long long g_chain_clk[24];
+__shared__ unsigned long long s_chain_clk[24];
+#define CHAIN_CLK(slot, t0) do { if (threadIdx.x == 0) s_chain_clk[slot] += clock64() - (t0); } while (0)
+#define STAGE_CLK(slot) do { if (threadIdx.x == 0) { const long long now__ = clock64(); s_chain_clk[slot] += now__ - t_stage; t_stage = now__; } } while (0)
+#define STAGE_BEGIN() long long t_stage = clock64()
+#else
+#define CHAIN_CLK(slot, t0) do { } while (0)
+#define STAGE_CLK(slot) do { } while (0)
+#define STAGE_BEGIN() do { } while (0)
+#endif
 
-// ---- kernel input ------------------------------------------------------------
-// scores_j = sum_n A[j + m n] K[n, i]: every warp takes examples n = gw, gw + GW,
-// ... and keeps NACC classes per lane; the block adds its warps' sums and stores
-// m partial sums; the last block to arrive finishes the step.
-template <typename Data, typename R, int NACC>
-__global__ void __launch_bounds__(kFitThreads, 1)
-fit_step_kernel_input(ObjectiveParams o, const Data* __restrict__ K, Data* A,
-                      const int64_t* __restrict__ labels, const int64_t* __restrict__ order,
-                      FitState* st, double* partials, int m, long long n) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  double* red = reinterpret_cast<double*>(smem_raw);              // kFitWarps x tile
-  __shared__ bool s_last;
-  constexpr int kTile = 32 * NACC;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const long long i = order[st->step];
-  const Data* Ki = K + n * i;
-  const Data norm2 = Ki[i];
-  const bool active = norm2 > Data(0);   // update.h:97: nothing to do otherwise
+constexpr int kSmallRow = 256;   // rows up to this length take the block-wide update
 
-  if (active) {
-    const long long gw = static_cast<long long>(blockIdx.x) * kFitWarps + warp;
-    const long long GW = static_cast<long long>(gridDim.x) * kFitWarps;
-    for (int j0 = 0; j0 < m; j0 += kTile) {
-      double acc[NACC];
-#pragma unroll
-      for (int v = 0; v < NACC; ++v) acc[v] = 0.0;
-      long long e = gw;
-      // four examples in flight per warp
-      for (; e + 3 * GW < n; e += 4 * GW) {
-        Data a[4][NACC];
-        Data kv[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const long long ee = e + u * GW;
-          kv[u] = Ki[ee];
-          const Data* row = A + ee * m + j0;
-#pragma unroll
-          for (int v = 0; v < NACC; ++v) {
-            const int j = lane + 32 * v;
-            a[u][v] = (j0 + j < m) ? ld_cg(row + j) : Data(0);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-#pragma unroll
-          for (int v = 0; v < NACC; ++v)
-            acc[v] = fma(static_cast<double>(a[u][v]), static_cast<double>(kv[u]), acc[v]);
-      }
-      for (; e < n; e += GW) {
-        const Data kv = Ki[e];
-        const Data* row = A + e * m + j0;
-#pragma unroll
-        for (int v = 0; v < NACC; ++v) {
-          const int j = lane + 32 * v;
-          const Data a = (j0 + j < m) ? ld_cg(row + j) : Data(0);
-          acc[v] = fma(static_cast<double>(a), static_cast<double>(kv), acc[v]);
-        }
-      }
-#pragma unroll
-      for (int v = 0; v < NACC; ++v) red[warp * kTile + lane + 32 * v] = acc[v];
-      __syncthreads();
-      for (int j = tid; j < kTile && j0 + j < m; j += kFitThreads) {
-        double s = 0.0;
-#pragma unroll
-        for (int w = 0; w < kFitWarps; ++w) s += red[w * kTile + j];
-        partials[static_cast<long long>(blockIdx.x) * m + j0 + j] = s;
-      }
-      __syncthreads();
-    }
-  }
+// Per-step constants of the update, worked out for all steps of a block at once.
+template <typename R, typename Data>
+struct StepConsts {
+  Data norm2, alpha, beta;
+  R rho, rho_inv;
+};
 
-  // hand in this block's part; the last one continues
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const unsigned int t = atomicAdd(&st->ticket, 1u);
-    s_last = (t == gridDim.x - 1);
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-
-  if (active) {
-    Data* scores = reinterpret_cast<Data*>(smem_raw);
-    Data* a_s = scores + m;
-    Data* v_s = a_s + m;
-    Data* a_g = A + i * m;
-    const int G = gridDim.x;
-    for (int j = tid; j < m; j += kFitThreads) {
-      double s = 0.0;
-      int g = 0;
-      for (; g + 8 <= G; g += 8) {
-        double p[8];
+// f(t) = sum_i clip(v_i - t, 0, hi) over a row held in registers (NV entries per
+// lane, -inf where the lane has none), with the sizes of the sets it is made of:
+// u entries at hi, q entries above 0.
+template <typename R, int NV>
+struct ClipSum {
+  R f;
+  int u, q;
+};
+template <typename R, int NV>
+__device__ __forceinline__ ClipSum<R, NV> clip_sum(const R (&v)[NV], R t, R hi) {
+  R s = 0;
+  int cnt = 0;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) p[u] = ld_cg(partials + static_cast<long long>(g + u) * m + j);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) s += p[u];
-      }
-      for (; g < G; ++g) s += ld_cg(partials + static_cast<long long>(g) * m + j);
-      scores[j] = static_cast<Data>(s);
-      a_s[j] = a_g[j];
-    }
-    __syncthreads();
-    if (warp == 0) {
-      const int y = static_cast<int>(labels[i]);
-      update_dual_variables_multiclass<R, Data>(o, norm2, scores, a_s, v_s, m, y);
-      for (int j = lane; j < m; j += 32) a_g[j] = a_s[j];
-    }
+  for (int e = 0; e < NV; ++e) {
+    const R d = v[e] - t;
+    s += min_(max_(d, R(0)), hi);
+    cnt += (d > R(0) ? 1 : 0) + (d >= hi ? 0x10000 : 0);
   }
-  if (tid == 0) {
-    st->ticket = 0;
-    st->step += 1;
-  }
+  ClipSum<R, NV> out;
+  out.f = warp_sum(s);
+  cnt = __reduce_add_sync(0xffffffffu, cnt);
+  out.u = cnt >> 16; out.q = cnt & 0xffff;
+  return out;
 }
 
-// ---- feature input -------------------------------------------------------------
-// scores_j = <W_j, x_i> with W d x m, one warp per class.  The rank-one change of
-// W that step s owes (update.h:77-84) is applied by step s+1 while it reads the
-// columns anyway: W_j -= x_prev * delta_j, then the dot product with x_i.  A
-// last launch with `flush` set applies the change the final step left behind.
-struct PendingUpdate {
-  long long example;     // -1: nothing pending
-  long long pad;
-};
+// The update of the top-k hinge (beta) objectives for one example by one warp with
+// the row in registers: update_dual_variables of
+// include/sdca/solver/objective/l2_topk_hinge.h:45-69,136-163, i.e.
+// x = clip(v - t, 0, hi) solving  min 0.5 (|x|^2 + rho <1,x>^2) - <v,x>, <1,x> <= rhs
+// (include/sdca/prox/knapsack_le_biased.h:96-127).  The reference first tries
+// <1,x> = rhs by variable fixing, accepts it if t >= rho rhs, and otherwise
+// searches sorted data for the sets at hi / strictly inside.  f is decreasing, so
+// one evaluation at t = rho rhs tells the two cases apart: f >= rhs there means the
+// equality case with its root to the right, anything else the root of
+// t = rho f(t) to the left.  Either root is found by Newton steps on the
+// piecewise-linear function -- a step is the closed form for the current sets, so
+// the search ends as soon as a step stays on its piece -- kept inside a bracket,
+// and t finally comes from the reference's closed form for the sets found.
+// Lane l holds classes l, l + 32, ...; a_new receives their new variables.
+// Returns false if the search did not settle (the caller then takes the general
+// routine).
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>& sc, R hi, R rhs,
+                                                       const double* Sb, const Data* a_cur, int m,
+                                                       int y, Data (&a_new)[NV]) {
+  const int lane = threadIdx.x & 31;
+  const R neg_inf = -num<R>::inf(), pos_inf = num<R>::inf();
+  // the vector to project (objective/l2_topk_hinge.h:55-59)
+  const Data vy = add_rn_(mul_rn_(sc.beta, a_cur[y]), mul_rn_(sc.alpha, static_cast<Data>(Sb[y])));
+  const Data shift = sc.alpha - vy;
+  Data vd[NV];
+  R v[NV];
+#pragma unroll
+  for (int e = 0; e < NV; ++e) {
+    const int j = lane + 32 * e;
+    const bool mine = j < m && j != y;
+    vd[e] = mine ? add_rn_(mul_rn_(sc.beta, a_cur[j]), mul_rn_(sc.alpha, static_cast<Data>(Sb[j]))) + shift
+                 : Data(0);
+    v[e] = mine ? static_cast<R>(vd[e]) : neg_inf;
+  }
+  const R rho = sc.rho, t0 = rho * rhs;
+  ClipSum<R, NV> c = clip_sum<R, NV>(v, t0, hi);
+  const bool equality = (c.f >= rhs);
+  // phi(t) = rhs - f(t) (equality) or t - rho f(t) (biased): increasing, root wanted
+  R t = t0, tl, tr;
+  if (equality) { tl = t0; tr = pos_inf; } else { tl = neg_inf; tr = t0; }
+  bool settled = false;
+  for (int it = 0; it < 48 && !settled; ++it) {
+    const int inside = c.q - c.u;
+    const R phi = equality ? rhs - c.f : t - rho * c.f;
+    if (phi == R(0)) { settled = true; break; }
+    if (phi < R(0)) tl = max_(tl, t); else tr = min_(tr, t);
+    R tn = t;
+    bool newton = true;
+    if (equality && inside == 0 && phi > R(0)) {
+      newton = false;   // overshot into a flat stretch: halve the bracket instead
+    } else if (equality && inside == 0) {
+      // flat piece with f > rhs: the next piece starts where the first entries leave
+      // the upper bound; solve on that piece
+      R nb = pos_inf;
+#pragma unroll
+      for (int e = 0; e < NV; ++e) {
+        const R b = v[e] - hi;
+        if (b >= t) nb = min_(nb, b);
+      }
+      nb = -warp_max(-nb);
+      if (!(nb < pos_inf)) return false;
+      int leaving = 0;
+#pragma unroll
+      for (int e = 0; e < NV; ++e) leaving += (v[e] - hi == nb) ? 1 : 0;
+      leaving = __reduce_add_sync(0xffffffffu, leaving);
+      tn = nb + (c.f - rhs) / static_cast<R>(leaving);
+    } else {
+      const R slope = equality ? static_cast<R>(inside) : R(1) + rho * static_cast<R>(inside);
+      tn = t - phi / slope;
+      if (tn == t) { settled = true; break; }   // the root of this piece, to the last bit
+    }
+    if (!newton || !(tn > tl && tn < tr)) {
+      if (!(tl > neg_inf) || !(tr < pos_inf)) return false;
+      tn = tl + (tr - tl) / 2;
+      newton = false;
+      if (!(tn > tl && tn < tr)) return false;
+    }
+    const ClipSum<R, NV> cn = clip_sum<R, NV>(v, tn, hi);
+    // a Newton step that finds the sets it started from has solved its piece exactly
+    settled = newton && (cn.u == c.u && cn.q == c.q) && (!equality || inside > 0);
+    t = tn; c = cn;
+  }
+  if (!settled) return false;
+  // the reference's closed forms for the sets found (knapsack_le_biased.h:52;
+  // knapsack_eq.h for the equality case): entries at hi, entries strictly inside
+  R sum_m = 0;
+#pragma unroll
+  for (int e = 0; e < NV; ++e) {
+    const R d = v[e] - t;
+    if (d > R(0) && !(d >= hi)) sum_m += v[e];
+  }
+  sum_m = warp_sum(sum_m);
+  const int inside = c.q - c.u;
+  if (equality) {
+    if (inside > 0) t = (hi * static_cast<R>(c.u) + sum_m - rhs) / static_cast<R>(inside);
+  } else {
+    t = (hi * static_cast<R>(c.u) + sum_m) / (sc.rho_inv + static_cast<R>(inside));
+  }
+  // new variables (objective/l2_topk_hinge.h:64-68)
+  const Data td = static_cast<Data>(t), hid = static_cast<Data>(hi);
+  R total = 0;
+#pragma unroll
+  for (int e = 0; e < NV; ++e) {
+    const int j = lane + 32 * e;
+    const Data pj = (j < m && j != y) ? clip_(static_cast<Data>(vd[e] - td), Data(0), hid) : Data(0);
+    total += static_cast<R>(pj);
+    a_new[e] = -pj;
+  }
+  total = warp_sum(total);
+  if ((y & 31) == lane) {
+    const Data ay = static_cast<Data>(min_(rhs, total));
+#pragma unroll
+    for (int e = 0; e < NV; ++e) if (e == (y >> 5)) a_new[e] = ay;
+  }
+  return true;
+}
+
+// One step by warp 0 with the row in registers; writes the new variables, the
+// change `delta` and (features) decides whether the primal variables move.
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ bool warp_step_topk_hinge(const StepConsts<R, Data>& sc, R hi, R rhs,
+                                                     const double* Sb, const Data* a_cur, int m, int y,
+                                                     Data* a_row, double* delta, int kernel_input,
+                                                     int* skip) {
+  const int lane = threadIdx.x & 31;
+  Data a_new[NV];
+  if (!warp_update_topk_hinge<R, Data, NV>(sc, hi, rhs, Sb, a_cur, m, y, a_new)) return false;
+  Data asum = 0;
+#pragma unroll
+  for (int e = 0; e < NV; ++e) {
+    const int j = lane + 32 * e;
+    if (j < m) {
+      const Data a_old = a_cur[j];
+      a_row[j] = a_new[e];
+      if (kernel_input) {
+        delta[j] = static_cast<double>(a_new[e]) - static_cast<double>(a_old);
+      } else {
+        const Data dlt = a_old - a_new[e];   // var_copy of update.h:74-77
+        asum += abs_(dlt);
+        delta[j] = static_cast<double>(dlt);
+      }
+    }
+  }
+  if (!kernel_input) {
+    asum = warp_sum(asum);
+    if (!(asum > num<Data>::eps()) && lane == 0) *skip = 1;   // update.h:78
+  }
+  return true;
+}
 
 template <typename Data, typename R>
-__global__ void __launch_bounds__(kFitThreads, 1)
-fit_step_feature_input(ObjectiveParams o, const Data* __restrict__ X, Data* W, Data* A,
-                       const Data* __restrict__ norms, const int64_t* __restrict__ labels,
-                       const int64_t* __restrict__ order, FitState* st, PendingUpdate* pend,
-                       Data* delta /* m */, Data* scores_g /* m */, int m, long long d, long long n,
-                       int flush) {
+__global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ bool s_last;
+  const int m = p.m, count = p.count;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const long long prev = pend->example;
-  const long long i = flush ? -1 : order[st->step];
-  const Data norm2 = flush ? Data(0) : norms[i];
-  const bool active = norm2 > Data(0);
-  const Data* xp = prev >= 0 ? X + d * prev : nullptr;
-  const Data* xi = active ? X + d * i : nullptr;
+  double* G = reinterpret_cast<double*>(smem_raw);                  // 64 x 64
+  double* delta = G + kBlockSteps * kBlockSteps;                    // m
+  double* S = delta + m;                                            // count x m when on chip
+  Data* scores = reinterpret_cast<Data*>(p.s_on_chip ? S + static_cast<size_t>(kBlockSteps) * m : S);
+  Data* a_s = scores + m;
+  Data* v_s = a_s + m;
+  Data* a_next = v_s + m;                                           // 2 x m, rows fetched ahead
+  __shared__ long long s_idx[kBlockSteps];
+  __shared__ int s_lab[kBlockSteps];
+  __shared__ int s_skip;
+  __shared__ StepConsts<R, Data> s_consts[kBlockSteps];
+  const R hi_small = static_cast<R>(p.o.c) / static_cast<R>(p.o.k), rhs_small = static_cast<R>(p.o.c);
+  const bool small_rows = (p.o.id == kObjL2TopkHinge || p.o.id == kObjL2TopkHingeSmooth) &&
+                          m <= kSmallRow;
+  Data* A = static_cast<Data*>(p.A);
+  Data* D = static_cast<Data*>(p.D);
 
-  if (prev >= 0 || active) {
-    const int gw = blockIdx.x * kFitWarps + warp;
-    const int GW = gridDim.x * kFitWarps;
-    for (int j = gw; j < m; j += GW) {
-      Data* Wj = W + d * j;
-      const Data dj = prev >= 0 ? ld_cg(delta + j) : Data(0);
-      double s = 0.0;
-      if (prev >= 0 && dj != Data(0)) {
-        for (long long r = lane; r < d; r += 32) {
-          // W_j <- W_j - x_prev * delta_j, product and difference rounded separately
-          const Data w = sub_rn_(Wj[r], mul_rn_(xp[r], dj));
-          Wj[r] = w;
-          if (active) s = fma(static_cast<double>(w), static_cast<double>(xi[r]), s);
-        }
-      } else if (active) {
-        for (long long r = lane; r < d; r += 32)
-          s = fma(static_cast<double>(Wj[r]), static_cast<double>(xi[r]), s);
-      }
-      if (active) {
-        s = warp_sum(s);
-        if (lane == 0) scores_g[j] = static_cast<Data>(s);
-      }
+#ifdef SDCAB_FIT_PROFILE
+  if (tid < 24) s_chain_clk[tid] = 0;
+  __syncthreads();
+  long long t_begin = clock64();
+#endif
+  for (int t = tid; t < kBlockSteps * kBlockSteps; t += kFitThreads) G[t] = p.G[t];
+  if (tid < count) {
+    const long long i = p.order[tid];
+    s_idx[tid] = i;
+    s_lab[tid] = static_cast<int>(p.labels[i]);
+  }
+  if (p.s_on_chip) {
+    for (int t = tid; t < count * m; t += kFitThreads) S[t] = p.S[t];
+  } else {
+    S = p.S;
+  }
+  __syncthreads();
+  for (int j = tid; j < m; j += kFitThreads) a_next[j] = A[s_idx[0] * m + j];
+  if (tid < count) {
+    // constants of step tid (objective/l2_topk_hinge.h:53-54, 144-150; l2_hinge_topk.h alike)
+    StepConsts<R, Data> sc;
+    sc.norm2 = static_cast<Data>(p.kernel_input ? G[tid * kBlockSteps + tid] : -G[tid * kBlockSteps + tid]);
+    const bool smooth = (p.o.id == kObjL2HingeTopkSmooth || p.o.id == kObjL2TopkHingeSmooth);
+    const R c = static_cast<R>(p.o.c);
+    sc.rho = smooth ? static_cast<R>(sc.norm2) / (static_cast<R>(sc.norm2) + static_cast<R>(p.o.gamma) / c) : R(1);
+    sc.rho_inv = R(1) / sc.rho;
+    sc.alpha = smooth ? static_cast<Data>(sc.rho) / sc.norm2 : Data(1) / sc.norm2;
+    sc.beta = smooth ? -static_cast<Data>(sc.rho) : Data(-1);
+    s_consts[tid] = sc;
+  }
+  __syncthreads();
+
+  CHAIN_CLK(0, t_begin);
+  for (int b = 0; b < count; ++b) {
+#ifdef SDCAB_FIT_PROFILE
+    long long t_step = clock64();
+#endif
+    const long long i = s_idx[b];
+    const Data norm2 = s_consts[b].norm2;
+    const bool active = norm2 > Data(0);    // update.h:63,97
+    Data* a_cur = a_next + (b & 1) * m;
+    bool done = false;
+    if (warp == 0 && small_rows && active) {
+      CHAIN_CLK(1, t_step);
+      s_skip = 0;
+      __syncwarp();
+      const double* Sb = S + static_cast<size_t>(b) * m;
+      done = (m <= 128)
+          ? warp_step_topk_hinge<R, Data, 4>(s_consts[b], hi_small, rhs_small, Sb, a_cur, m, s_lab[b],
+                                             A + i * m, delta, p.kernel_input, &s_skip)
+          : warp_step_topk_hinge<R, Data, 8>(s_consts[b], hi_small, rhs_small, Sb, a_cur, m, s_lab[b],
+                                             A + i * m, delta, p.kernel_input, &s_skip);
+      CHAIN_CLK(2, t_step);
     }
-  }
-
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const unsigned int t = atomicAdd(&st->ticket, 1u);
-    s_last = (t == gridDim.x - 1);
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-
-  long long next_pending = -1;
-  if (active) {
-    Data* scores = reinterpret_cast<Data*>(smem_raw);
-    Data* a_s = scores + m;
-    Data* v_s = a_s + m;
-    Data* old = v_s + m;
-    Data* a_g = A + i * m;
-    for (int j = tid; j < m; j += kFitThreads) {
-      scores[j] = ld_cg(scores_g + j);
-      const Data a = a_g[j];
-      a_s[j] = a; old[j] = a;
+    if (warp == 0 && done) {
+      // nothing left to do for this step
+    } else if (warp == 0) {
+      if (lane == 0) s_skip = active ? 0 : 1;
+      if (active) {
+        const double* Sb = S + static_cast<size_t>(b) * m;
+        for (int j = lane; j < m; j += 32) { scores[j] = static_cast<Data>(Sb[j]); a_s[j] = a_cur[j]; }
+        __syncwarp();
+        CHAIN_CLK(1, t_step);
+        update_dual_variables_multiclass<R, Data>(p.o, norm2, scores, a_s, v_s, m, s_lab[b]);
+        CHAIN_CLK(2, t_step);
+        Data asum = 0;
+        for (int j = lane; j < m; j += 32) {
+          const Data a_new = a_s[j], a_old = a_cur[j];
+          A[i * m + j] = a_new;
+          if (p.kernel_input) {
+            delta[j] = static_cast<double>(a_new) - static_cast<double>(a_old);
+          } else {
+            const Data dlt = a_old - a_new;   // var_copy of update.h:74-77
+            asum += abs_(dlt);
+            delta[j] = static_cast<double>(dlt);
+          }
+        }
+        if (!p.kernel_input) {
+          asum = warp_sum(asum);
+          if (!(asum > num<Data>::eps()) && lane == 0) s_skip = 1;   // update.h:78
+        }
+      }
+    } else if (warp == 1 && b + 1 < count) {
+      Data* nxt = a_next + ((b + 1) & 1) * m;
+      const Data* src = A + s_idx[b + 1] * m;
+      for (int j = lane; j < m; j += 32) nxt[j] = src[j];
     }
     __syncthreads();
-    if (warp == 0) {
-      const int y = static_cast<int>(labels[i]);
-      update_dual_variables_multiclass<R, Data>(o, norm2, scores, a_s, v_s, m, y);
-      // delta = old - new; the primal variables move only if it is not negligible
-      Data asum = 0;
-      for (int j = lane; j < m; j += 32) {
-        const Data dlt = old[j] - a_s[j];
-        a_g[j] = a_s[j];
-        delta[j] = dlt;
-        asum += abs_(dlt);
-      }
-      asum = warp_sum(asum);
-      if (asum > num<Data>::eps()) next_pending = i;
+    CHAIN_CLK(3, t_step);
+    const bool skip = s_skip != 0;
+    if (!p.kernel_input) {
+      Data* Db = D + static_cast<size_t>(b) * m;
+      for (int j = tid; j < m; j += kFitThreads) Db[j] = skip ? Data(0) : static_cast<Data>(delta[j]);
     }
+    if (!skip) {
+      // later rows of S move by delta * G[b][row]; four rows in flight per thread
+      const double* Gb = G + b * kBlockSteps;
+      constexpr int kRowGroups = kFitThreads >> 7;
+      for (int j = tid & 127; j < m; j += 128) {
+        const double dj = delta[j];
+        int bb = b + 1 + (tid >> 7);
+        for (; bb + 3 * kRowGroups < count; bb += 4 * kRowGroups) {
+          double sv[4], gv[4];
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            gv[r] = Gb[bb + r * kRowGroups];
+            sv[r] = S[static_cast<size_t>(bb + r * kRowGroups) * m + j];
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) S[static_cast<size_t>(bb + r * kRowGroups) * m + j] = fma(dj, gv[r], sv[r]);
+        }
+        for (; bb < count; bb += kRowGroups) {
+          double* Sr = S + static_cast<size_t>(bb) * m;
+          Sr[j] = fma(dj, Gb[bb], Sr[j]);
+        }
+      }
+    }
+    __syncthreads();
+    CHAIN_CLK(4, t_step);
   }
-  if (tid == 0) {
-    pend->example = next_pending;
-    st->ticket = 0;
-    if (!flush) st->step += 1;
-  }
+#ifdef SDCAB_FIT_PROFILE
+  if (tid < 24) g_chain_clk[tid] += s_chain_clk[tid];
+#endif
 }
 
-// ||x_i||^2 for every example (solver_scratch::init, data/scratch.h)
+// S[b][j] = sum over the slices of the split product, in slice order; G from the
+// kernel matrix (kernel input) or from the sliced Gram product, negated (features).
 template <typename Data>
-__global__ void column_norms_kernel(const Data* __restrict__ X, Data* norms, long long d, long long n) {
-  const long long i = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (i >= n) return;
-  const int lane = threadIdx.x & 31;
-  const Data* x = X + d * i;
-  double s = 0.0;
-  for (long long r = lane; r < d; r += 32) s = fma(static_cast<double>(x[r]), static_cast<double>(x[r]), s);
-  s = warp_sum(s);
-  if (lane == 0) norms[i] = static_cast<Data>(s);
+__global__ void fit_pack_kernel(const Data* __restrict__ s_parts, int slices, long long slice_stride,
+                                const Data* __restrict__ g_parts, int g_slices, long long g_stride,
+                                const Data* __restrict__ K, long long n,
+                                const int64_t* __restrict__ order, int count, int m,
+                                double* __restrict__ S, double* __restrict__ G) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long s_elems = static_cast<long long>(count) * m;
+  if (t < s_elems) {
+    double acc = 0.0;
+    for (int z = 0; z < slices; ++z) acc += static_cast<double>(s_parts[z * slice_stride + t]);
+    S[t] = acc;
+    return;
+  }
+  const long long u = t - s_elems;
+  if (u >= kBlockSteps * kBlockSteps) return;
+  const int b = static_cast<int>(u / kBlockSteps), bb = static_cast<int>(u % kBlockSteps);
+  double g = 0.0;
+  if (b < count && bb < count) {
+    if (K) {
+      g = static_cast<double>(K[order[b] + n * order[bb]]);
+    } else {
+      for (int z = 0; z < g_slices; ++z) g += static_cast<double>(g_parts[z * g_stride + b * count + bb]);
+      g = -g;
+    }
+  }
+  G[u] = g;
+}
+
+// W_j <- W_j - x_{i_b} * D[b][j] for the steps of one block in step order, every
+// product and difference rounded on its own like the reference's ger (update.h:83).
+template <typename Data>
+__global__ void __launch_bounds__(256)
+fit_primal_update_kernel(Data* W, const Data* __restrict__ X, const Data* __restrict__ D,
+                         const int64_t* __restrict__ order, int count, int m, long long d) {
+  __shared__ Data s_d[kBlockSteps];
+  __shared__ long long s_i[kBlockSteps];
+  const int j = blockIdx.y;
+  if (threadIdx.x < count) {
+    s_d[threadIdx.x] = D[static_cast<size_t>(threadIdx.x) * m + j];
+    s_i[threadIdx.x] = order[threadIdx.x];
+  }
+  __syncthreads();
+  const long long r = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (r >= d) return;
+  Data w = W[d * j + r];
+  for (int b = 0; b < count; ++b) {
+    const Data dj = s_d[b];
+    if (dj != Data(0)) w = sub_rn_(w, mul_rn_(X[d * s_i[b] + r], dj));
+  }
+  W[d * j + r] = w;
 }
 
 template <typename Data> int eval_sums_call(const sdcab_objective*, const sdcab_problem*, double*, void*);
@@ -267,83 +462,137 @@ template <> int eval_sums_call<double>(const sdcab_objective* o, const sdcab_pro
 }
 
 struct DeviceBuffers {
-  void* p[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  void* p[12] = {nullptr};
   int count = 0;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
-  cudaGraph_t graph = nullptr;
-  cudaGraphExec_t exec = nullptr;
   ~DeviceBuffers() {
-    if (exec) cudaGraphExecDestroy(exec);
-    if (graph) cudaGraphDestroy(graph);
     for (int i = 0; i < count; ++i) cudaFree(p[i]);
     for (int i = 0; i < 4; ++i) if (ev[i]) cudaEventDestroy(ev[i]);
     if (stream) cudaStreamDestroy(stream);
   }
-  int alloc(void** out, size_t bytes) {
-    SDCAB_CUDA_TRY(cudaMalloc(out, bytes));
-    p[count++] = *out;
+  template <typename T>
+  int alloc(T** out, size_t elems) {
+    void* ptr = nullptr;
+    SDCAB_CUDA_TRY(cudaMalloc(&ptr, std::max<size_t>(elems, 1) * sizeof(T)));
+    p[count++] = ptr;
+    *out = static_cast<T*>(ptr);
     return SDCAB_OK;
   }
 };
 
+// The launches of one block of steps.
 template <typename Data, typename R>
-struct StepLauncher {
+struct BlockRunner {
   ObjectiveParams o;
   const sdcab_problem* t;
-  int grid;
-  size_t smem;
-  FitState* st;
-  int64_t* order;
-  double* partials;
-  PendingUpdate* pend;
-  Data *delta, *scores_g, *norms;
+  int sm_count = 0;
+  size_t chain_smem = 0;
+  int s_on_chip = 0;
+  int slices = 1, g_slices = 1;
+  int64_t* order = nullptr;     // the epoch's order on the device
+  Data* s_parts = nullptr;      // slices x 64 x m
+  Data* g_parts = nullptr;      // features: g_slices x 64 x 64
+  double* S = nullptr;          // 64 x m
+  double* G = nullptr;          // 64 x 64
+  Data* D = nullptr;            // features: 64 x m
 
-  int launch(cudaStream_t s, int flush) const {
+  static int pick_slices(int tiles, long long k, int bk, int sm_count) {
+    long long want = (2LL * sm_count + tiles - 1) / tiles;
+    const long long most = std::max<long long>(1, k / (4LL * bk));
+    return static_cast<int>(std::max<long long>(1, std::min(want, most)));
+  }
+
+  int prepare(const DeviceInfo& info, DeviceBuffers& buf) {
+    typedef SmallGemmTile<Data> GT;
+    const long long m = t->m;
+    sm_count = info.sm_count;
+    const int tiles = static_cast<int>((m + GT::BN - 1) / GT::BN);
+    slices = pick_slices(tiles, t->d, GT::BK, sm_count);
+    g_slices = pick_slices(1, t->d, GT::BK, sm_count);
+    const size_t fixed = (kBlockSteps * kBlockSteps + m) * sizeof(double) + 5 * m * sizeof(Data);
+    const size_t with_s = fixed + static_cast<size_t>(kBlockSteps) * m * sizeof(double);
+    s_on_chip = (with_s + 2048 <= info.smem_optin) ? 1 : 0;
+    chain_smem = s_on_chip ? with_s : fixed;
+    if (chain_smem + 2048 > info.smem_optin) return SDCAB_ERR_TOO_LARGE;
+    SDCAB_CUDA_TRY(cudaFuncSetAttribute(fit_chain_kernel<Data, R>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(chain_smem)));
+    int rc = buf.alloc(&order, static_cast<size_t>(t->n)); if (rc) return rc;
+    rc = buf.alloc(&s_parts, static_cast<size_t>(slices) * kBlockSteps * m); if (rc) return rc;
+    rc = buf.alloc(&S, static_cast<size_t>(kBlockSteps) * m); if (rc) return rc;
+    rc = buf.alloc(&G, static_cast<size_t>(kBlockSteps) * kBlockSteps); if (rc) return rc;
+    if (t->input_kind != SDCAB_INPUT_KERNEL) {
+      rc = buf.alloc(&g_parts, static_cast<size_t>(g_slices) * kBlockSteps * kBlockSteps); if (rc) return rc;
+      rc = buf.alloc(&D, static_cast<size_t>(kBlockSteps) * m); if (rc) return rc;
+    }
+    return SDCAB_OK;
+  }
+
+  // steps [first, first + count) of the epoch whose order is on the device
+  int run(long long first, int count, cudaStream_t s) const {
+    typedef SmallGemmTile<Data> GT;
     const int m = static_cast<int>(t->m);
+    const bool kernel_input = (t->input_kind == SDCAB_INPUT_KERNEL);
+    const Data* X = static_cast<const Data*>(t->x);
     Data* A = static_cast<Data*>(const_cast<void*>(t->a));
-    if (t->input_kind == SDCAB_INPUT_KERNEL) {
-      const Data* K = static_cast<const Data*>(t->x);
-      if (m <= 32)
-        fit_step_kernel_input<Data, R, 1><<<grid, kFitThreads, smem, s>>>(o, K, A, t->labels, order, st, partials, m, t->n);
-      else if (m <= 64)
-        fit_step_kernel_input<Data, R, 2><<<grid, kFitThreads, smem, s>>>(o, K, A, t->labels, order, st, partials, m, t->n);
-      else if (m <= 128)
-        fit_step_kernel_input<Data, R, 4><<<grid, kFitThreads, smem, s>>>(o, K, A, t->labels, order, st, partials, m, t->n);
-      else
-        fit_step_kernel_input<Data, R, 8><<<grid, kFitThreads, smem, s>>>(o, K, A, t->labels, order, st, partials, m, t->n);
+    Data* W = static_cast<Data*>(const_cast<void*>(t->w));
+    const int64_t* ord = order + first;
+    GemmExtras x;
+    x.a_gather = ord;
+    x.slices = slices;
+    x.c_slice_stride = static_cast<long long>(count) * m;
+    int rc;
+    if (kernel_input) {
+      // S = K[:, block]' A : rows = columns of K (contiguous), A is n x m
+      rc = launch_gemm_tile<Data, GT>(X, A, s_parts, count, m, static_cast<int>(t->n), t->n, m, m,
+                                      false, s, x);
     } else {
-      fit_step_feature_input<Data, R><<<grid, kFitThreads, smem, s>>>(
-          o, static_cast<const Data*>(t->x), static_cast<Data*>(const_cast<void*>(t->w)), A, norms,
-          t->labels, order, st, pend, delta, scores_g, m, t->d, t->n, flush);
+      // S = X[:, block]' W, both with the feature index contiguous
+      rc = launch_gemm_tile<Data, GT>(X, W, s_parts, count, m, static_cast<int>(t->d), t->d, t->d, m,
+                                      true, s, x);
+      if (rc) return rc;
+      GemmExtras g;
+      g.a_gather = ord; g.b_gather = ord; g.slices = g_slices;
+      g.c_slice_stride = static_cast<long long>(count) * count;
+      rc = launch_gemm_tile<Data, GT>(X, X, g_parts, count, count, static_cast<int>(t->d), t->d, t->d,
+                                      count, true, s, g);
     }
+    if (rc) return rc;
+    const long long pack_threads = static_cast<long long>(count) * m + kBlockSteps * kBlockSteps;
+    fit_pack_kernel<Data><<<static_cast<unsigned>((pack_threads + 255) / 256), 256, 0, s>>>(
+        s_parts, slices, x.c_slice_stride, g_parts, g_slices, static_cast<long long>(count) * count,
+        kernel_input ? X : nullptr, t->n, ord, count, m, S, G);
     SDCAB_CUDA_TRY(cudaGetLastError());
-    return SDCAB_OK;
-  }
-
-  template <typename F>
-  static int set_smem(F* kernel, size_t bytes) {
-    SDCAB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(bytes)));
-    return SDCAB_OK;
-  }
-  int prepare() const {
-    if (t->input_kind == SDCAB_INPUT_KERNEL) {
-      int rc = set_smem(fit_step_kernel_input<Data, R, 1>, smem); if (rc) return rc;
-      rc = set_smem(fit_step_kernel_input<Data, R, 2>, smem); if (rc) return rc;
-      rc = set_smem(fit_step_kernel_input<Data, R, 4>, smem); if (rc) return rc;
-      return set_smem(fit_step_kernel_input<Data, R, 8>, smem);
+    ChainArgs c;
+    c.o = o; c.order = ord; c.labels = t->labels; c.S = S; c.G = G; c.A = A; c.D = D;
+    c.m = m; c.count = count; c.kernel_input = kernel_input ? 1 : 0; c.s_on_chip = s_on_chip;
+    fit_chain_kernel<Data, R><<<1, kFitThreads, chain_smem, s>>>(c);
+    SDCAB_CUDA_TRY(cudaGetLastError());
+    if (!kernel_input) {
+      dim3 grid(static_cast<unsigned>((t->d + 255) / 256), static_cast<unsigned>(m));
+      fit_primal_update_kernel<Data><<<grid, 256, 0, s>>>(W, X, D, ord, count, m, t->d);
+      SDCAB_CUDA_TRY(cudaGetLastError());
     }
-    return set_smem(fit_step_feature_input<Data, R>, smem);
+    return SDCAB_OK;
   }
 };
+
+bool is_permutation(const int64_t* p, long long n, std::vector<unsigned char>& seen) {
+  seen.assign(static_cast<size_t>(n), 0);
+  for (long long i = 0; i < n; ++i) {
+    const int64_t v = p[i];
+    if (v < 0 || v >= n || seen[static_cast<size_t>(v)]) return false;
+    seen[static_cast<size_t>(v)] = 1;
+  }
+  return true;
+}
 
 template <typename Data, typename R>
 int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_fit_criteria* crit,
             const int64_t* permutations, sdcab_eval_record* evals, int64_t evals_cap,
             sdcab_fit_result* result, cudaStream_t user_stream) {
-  const long long n = train->n, m = train->m, d = train->d;
-  const bool kernel_input = (train->input_kind == SDCAB_INPUT_KERNEL);
+  const long long n = train->n, m = train->m;
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc) return rc;
@@ -356,43 +605,13 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
   SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[0], user_stream));
   SDCAB_CUDA_TRY(cudaStreamWaitEvent(s, buf.ev[0], 0));
 
-  StepLauncher<Data, R> L;
-  L.o = to_params(obj);
-  L.t = train;
-  L.grid = info.sm_count;
-  if (!kernel_input) L.grid = static_cast<int>(std::min<long long>(info.sm_count, (m + kFitWarps - 1) / kFitWarps));
-  const size_t smem_update = static_cast<size_t>(4 * m) * sizeof(Data);
-  const size_t smem_reduce = kernel_input ? static_cast<size_t>(kFitWarps) * 256 * sizeof(double) : 0;
-  L.smem = std::max(smem_update, smem_reduce);
-  if (L.smem > info.smem_optin) return SDCAB_ERR_TOO_LARGE;
-  L.pend = nullptr; L.delta = nullptr; L.scores_g = nullptr; L.norms = nullptr; L.partials = nullptr;
-
-  void* ptr = nullptr;
-  rc = buf.alloc(&ptr, sizeof(FitState)); if (rc) return rc;
-  L.st = static_cast<FitState*>(ptr);
-  rc = buf.alloc(&ptr, static_cast<size_t>(n) * sizeof(long long)); if (rc) return rc;
-  L.order = static_cast<int64_t*>(ptr);
+  BlockRunner<Data, R> runner;
+  runner.o = to_params(obj);
+  runner.t = train;
+  rc = runner.prepare(info, buf);
+  if (rc) return rc;
   double* sums_dev = nullptr;
-  rc = buf.alloc(&ptr, SDCAB_EVAL_SUMS(m) * sizeof(double)); if (rc) return rc;
-  sums_dev = static_cast<double*>(ptr);
-  if (kernel_input) {
-    rc = buf.alloc(&ptr, static_cast<size_t>(L.grid) * m * sizeof(double)); if (rc) return rc;
-    L.partials = static_cast<double*>(ptr);
-  } else {
-    rc = buf.alloc(&ptr, sizeof(PendingUpdate)); if (rc) return rc;
-    L.pend = static_cast<PendingUpdate*>(ptr);
-    rc = buf.alloc(&ptr, static_cast<size_t>(2 * m + n) * sizeof(Data)); if (rc) return rc;
-    L.delta = static_cast<Data*>(ptr);
-    L.scores_g = L.delta + m;
-    L.norms = L.scores_g + m;
-    const PendingUpdate none = {-1, 0};
-    SDCAB_CUDA_TRY(cudaMemcpyAsync(L.pend, &none, sizeof(none), cudaMemcpyHostToDevice, s));
-    const int wpb = 8;
-    column_norms_kernel<Data><<<static_cast<unsigned>((n + wpb - 1) / wpb), wpb * 32, 0, s>>>(
-        static_cast<const Data*>(train->x), L.norms, d, n);
-    SDCAB_CUDA_TRY(cudaGetLastError());
-  }
-  rc = L.prepare();
+  rc = buf.alloc(&sums_dev, static_cast<size_t>(SDCAB_EVAL_SUMS(m)));
   if (rc) return rc;
 
   sdcab_problem ep = *train;
@@ -437,41 +656,27 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
 
   MinstdRand gen;
   std::vector<int64_t> order_host(static_cast<size_t>(n));
+  std::vector<unsigned char> seen;
   for (long long i = 0; i < n; ++i) order_host[static_cast<size_t>(i)] = i;
-  const FitState zero_state = {0, 0, 0};
-  SDCAB_CUDA_TRY(cudaMemcpyAsync(L.st, &zero_state, sizeof(zero_state), cudaMemcpyHostToDevice, s));
 
-  const long long per_graph = std::min<long long>(kStepsPerGraph, n);
   while (status == SDCAB_FIT_SOLVING) {
     // begin_epoch (solver.h:94-100)
     evaluated = false;
     const int64_t* order_src;
     if (permutations) {
       order_src = permutations + epoch * n;
+      if (!is_permutation(order_src, n, seen)) return SDCAB_ERR_ARG_RANGE;
     } else {
       shuffle_like_libstdcxx(order_host, gen);
       order_src = order_host.data();
     }
-    SDCAB_CUDA_TRY(cudaMemcpyAsync(L.order, order_src, static_cast<size_t>(n) * sizeof(long long),
+    SDCAB_CUDA_TRY(cudaMemcpyAsync(runner.order, order_src, static_cast<size_t>(n) * sizeof(int64_t),
                                    cudaMemcpyHostToDevice, s));
-    SDCAB_CUDA_TRY(cudaMemsetAsync(&L.st->step, 0, sizeof(long long), s));
     SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[0], s));
-    if (!buf.exec) {
-      // per_graph consecutive steps recorded once; every step reads its example
-      // from the order array through the device-side step counter, so the same
-      // recording serves every stretch of every epoch
-      SDCAB_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-      int lrc = SDCAB_OK;
-      for (long long k = 0; k < per_graph && lrc == SDCAB_OK; ++k) lrc = L.launch(s, 0);
-      cudaError_t cerr = cudaStreamEndCapture(s, &buf.graph);
-      if (lrc) return lrc;
-      SDCAB_CUDA_TRY(cerr);
-      SDCAB_CUDA_TRY(cudaGraphInstantiate(&buf.exec, buf.graph, 0));
+    for (long long first = 0; first < n; first += kBlockSteps) {
+      rc = runner.run(first, static_cast<int>(std::min<long long>(kBlockSteps, n - first)), s);
+      if (rc) return rc;
     }
-    long long done = 0;
-    for (; done + per_graph <= n; done += per_graph) SDCAB_CUDA_TRY(cudaGraphLaunch(buf.exec, s));
-    for (; done < n; ++done) { rc = L.launch(s, 0); if (rc) return rc; }
-    if (!kernel_input) { rc = L.launch(s, 1); if (rc) return rc; }
     SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[1], s));
     SDCAB_CUDA_TRY(cudaStreamSynchronize(s));
     float ms = 0;
@@ -537,6 +742,17 @@ int fit_entry(const sdcab_objective* obj, const sdcab_problem* t, const sdcab_fi
 
 }  // namespace
 }  // namespace sdcab
+
+#ifdef SDCAB_FIT_PROFILE
+extern "C" int sdcab_debug_chain_clocks(unsigned long long* out, int reset) {
+  cudaMemcpyFromSymbol(out, sdcab::g_chain_clk, sizeof(unsigned long long) * 24);
+  if (reset) {
+    unsigned long long z[24] = {0};
+    cudaMemcpyToSymbol(sdcab::g_chain_clk, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
 
 extern "C" {
 

@@ -1,0 +1,244 @@
+// Register-blocked SIMT GEMM for the score products, in the data type (float or
+// double): the evaluation's batched scores and the fit's per-block scores.
+#pragma once
+
+#include <cstdint>
+
+#include "common_host.h"
+
+namespace sdcab {
+
+// ------------------------------------------------------------------ GEMM ----
+// C (M x N, row major) = A (M x K, row major) * op(B), with
+//   B_KMAJOR:  B is N x K row major  (C = A B')   -- scores = X' W
+//   otherwise: B is K x N row major  (C = A B)    -- scores = K' A'
+// Thread block tile BM x BN x BK, TM x TN outputs per thread, register
+// prefetch of the next tile while the current one is consumed from shared
+// memory.  Arithmetic is plain FMA in the data type, accumulating over the
+// contraction index in increasing order, like a reference BLAS gemv.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> { typedef float4 type; };
+template <> struct Vec16<double> { typedef double2 type; };
+
+// Loads this thread's share of a rows x BK tile whose contraction index is
+// contiguous in memory (16-byte vectors where alignment allows, zero fill past
+// the edges).
+template <typename T, int BK, int NT, int PER>
+__device__ __forceinline__ void load_kmajor_tile(const T* __restrict__ base, long long ld,
+                                                 int rows_total, int K, int r0, int k0,
+                                                 int vec_ok, int tid, T (&dst)[PER][16 / sizeof(T)],
+                                                 const int64_t* __restrict__ gather = nullptr) {
+  constexpr int V = 16 / sizeof(T);
+  typedef typename Vec16<T>::type Vec;
+#pragma unroll
+  for (int it = 0; it < PER; ++it) {
+    const int idx = tid + it * NT;
+    const int r = idx / (BK / V), kv = (idx % (BK / V)) * V;
+    const int gk = k0 + kv;
+    const bool row_ok = r0 + r < rows_total;
+    // row r of the operand is row gather[r] of the matrix when a gather list is given
+    const long long gr = row_ok ? (gather ? static_cast<long long>(gather[r0 + r]) : r0 + r) : 0;
+    if (row_ok && vec_ok && gk + V <= K) {
+      const Vec v = *reinterpret_cast<const Vec*>(base + gr * ld + gk);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int c = 0; c < V; ++c) dst[it][c] = e[c];
+    } else {
+#pragma unroll
+      for (int c = 0; c < V; ++c)
+        dst[it][c] = (row_ok && gk + c < K) ? base[gr * ld + gk + c] : T(0);
+    }
+  }
+}
+
+template <typename T, int BM, int BN, int BK, int TM, int TN, bool B_KMAJOR>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int M, int N,
+            int K, long long lda, long long ldb, long long ldc, int a_vec, int b_vec, int c_vec,
+            const int64_t* __restrict__ a_gather, const int64_t* __restrict__ b_gather,
+            int k_per_slice, long long c_slice_stride) {
+  constexpr int NT = (BM / TM) * (BN / TN);
+  constexpr int V = 16 / sizeof(T);
+  constexpr int PAD = V;
+  typedef typename Vec16<T>::type Vec;
+  __shared__ __align__(16) T As[2][BK][BM + PAD];
+  __shared__ __align__(16) T Bs[2][BK][BN + PAD];
+  const int tid = threadIdx.x;
+  const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+  const int row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+  // slice blockIdx.z of the contraction index: a partial product of its own
+  {
+    const long long kb = static_cast<long long>(blockIdx.z) * k_per_slice;
+    A += kb;
+    B += B_KMAJOR ? kb : kb * ldb;
+    C += static_cast<long long>(blockIdx.z) * c_slice_stride;
+    K = (K - kb < k_per_slice) ? static_cast<int>(K - kb) : k_per_slice;
+    if (K < 0) K = 0;
+  }
+
+  constexpr int A_PER = (BM * BK / V) / NT;
+  constexpr int B_PER = (BN * BK / V) / NT;
+  static_assert(A_PER >= 1 && B_PER >= 1, "tile too small for the thread count");
+  T ra[A_PER][V], rb[B_PER][V];
+
+  auto load_b_nmajor = [&](int k0) {
+#pragma unroll
+    for (int it = 0; it < B_PER; ++it) {
+      const int idx = tid + it * NT;
+      const int kk = idx / (BN / V), nv = (idx % (BN / V)) * V;
+      const int gk = k0 + kk, gn = col0 + nv;
+      if (gk < K && b_vec && gn + V <= N) {
+        const Vec v = *reinterpret_cast<const Vec*>(B + static_cast<long long>(gk) * ldb + gn);
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int c = 0; c < V; ++c) rb[it][c] = e[c];
+      } else {
+#pragma unroll
+        for (int c = 0; c < V; ++c)
+          rb[it][c] = (gk < K && gn + c < N) ? B[static_cast<long long>(gk) * ldb + gn + c] : T(0);
+      }
+    }
+  };
+  auto store_tiles = [&](int buf) {
+#pragma unroll
+    for (int it = 0; it < A_PER; ++it) {
+      const int idx = tid + it * NT;
+      const int r = idx / (BK / V), kv = (idx % (BK / V)) * V;
+#pragma unroll
+      for (int c = 0; c < V; ++c) As[buf][kv + c][r] = ra[it][c];
+    }
+#pragma unroll
+    for (int it = 0; it < B_PER; ++it) {
+      const int idx = tid + it * NT;
+      if (B_KMAJOR) {
+        const int r = idx / (BK / V), kv = (idx % (BK / V)) * V;
+#pragma unroll
+        for (int c = 0; c < V; ++c) Bs[buf][kv + c][r] = rb[it][c];
+      } else {
+        const int kk = idx / (BN / V), nv = (idx % (BN / V)) * V;
+#pragma unroll
+        for (int c = 0; c < V; ++c) Bs[buf][kk][nv + c] = rb[it][c];
+      }
+    }
+  };
+  auto load_tiles = [&](int k0) {
+    load_kmajor_tile<T, BK, NT, A_PER>(A, lda, M, K, row0, k0, a_vec, tid, ra, a_gather);
+    if (B_KMAJOR) load_kmajor_tile<T, BK, NT, B_PER>(B, ldb, N, K, col0, k0, b_vec, tid, rb, b_gather);
+    else load_b_nmajor(k0);
+  };
+
+  T acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = T(0);
+
+  constexpr int HM = TM / 2, HN = TN / 2;  // each thread owns two strips per dimension
+  load_tiles(0);
+  store_tiles(0);
+  __syncthreads();
+  const int ktiles = (K + BK - 1) / BK;
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < ktiles) load_tiles((kt + 1) * BK);
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      T a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < HM; ++i) {
+        a[i] = As[buf][kk][ty * HM + i];
+        a[HM + i] = As[buf][kk][BM / 2 + ty * HM + i];
+      }
+#pragma unroll
+      for (int j = 0; j < HN; ++j) {
+        b[j] = Bs[buf][kk][tx * HN + j];
+        b[HN + j] = Bs[buf][kk][BN / 2 + tx * HN + j];
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+    }
+    if (kt + 1 < ktiles) {
+      store_tiles(buf ^ 1);
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = row0 + ((i < HM) ? ty * HM + i : BM / 2 + ty * HM + (i - HM));
+    if (r >= M) continue;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c0 = col0 + (h ? BN / 2 : 0) + tx * HN;
+      T* dst = C + static_cast<long long>(r) * ldc + c0;
+      if (c_vec && HN == V && c0 + HN <= N) {
+        Vec v;
+        T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+        for (int j = 0; j < HN; ++j) e[j] = acc[i][h * HN + j];
+        *reinterpret_cast<Vec*>(dst) = v;
+      } else {
+#pragma unroll
+        for (int j = 0; j < HN; ++j)
+          if (c0 + j < N) dst[j] = acc[i][h * HN + j];
+      }
+    }
+  }
+}
+
+// Tile shapes: the large one for the evaluation's batched scores, the small one
+// for the fit, whose products have at most 64 rows.
+template <typename T> struct GemmTile;
+template <> struct GemmTile<float> { static constexpr int BM = 128, BN = 128, BK = 16, TM = 8, TN = 8; };
+template <> struct GemmTile<double> { static constexpr int BM = 64, BN = 64, BK = 8, TM = 4, TN = 4; };
+template <typename T> struct SmallGemmTile;
+template <> struct SmallGemmTile<float> { static constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4; };
+template <> struct SmallGemmTile<double> { static constexpr int BM = 64, BN = 64, BK = 8, TM = 4, TN = 4; };
+
+// Optional extras of a launch: row gather lists for the operands whose
+// contraction index is contiguous, and a split of the contraction index into
+// `slices` partial products stored c_slice_stride elements apart.
+struct GemmExtras {
+  const int64_t* a_gather = nullptr;
+  const int64_t* b_gather = nullptr;
+  int slices = 1;
+  long long c_slice_stride = 0;
+};
+
+template <typename T, typename G>
+int launch_gemm_tile(const T* A, const T* B, T* C, int M, int N, int K, long long lda,
+                     long long ldb, long long ldc, bool b_kmajor, cudaStream_t stream,
+                     const GemmExtras& x) {
+  constexpr int V = 16 / sizeof(T);
+  auto aligned = [&](const void* p, long long ld) {
+    return ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && ld % V == 0) ? 1 : 0;
+  };
+  // slices start at multiples of the tile depth, which keeps 16-byte loads aligned
+  int k_per_slice = (K + x.slices - 1) / x.slices;
+  k_per_slice = (k_per_slice + G::BK - 1) / G::BK * G::BK;
+  if (k_per_slice <= 0) k_per_slice = G::BK;
+  const int a_vec = aligned(A, lda), c_vec = aligned(C, ldc) && (x.c_slice_stride % V == 0);
+  const int b_vec = aligned(B, ldb);
+  dim3 grid((N + G::BN - 1) / G::BN, (M + G::BM - 1) / G::BM, x.slices);
+  const int threads = (G::BM / G::TM) * (G::BN / G::TN);
+  if (b_kmajor)
+    gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, true><<<grid, threads, 0, stream>>>(
+        A, B, C, M, N, K, lda, ldb, ldc, a_vec, b_vec, c_vec, x.a_gather, x.b_gather, k_per_slice,
+        x.c_slice_stride);
+  else
+    gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, false><<<grid, threads, 0, stream>>>(
+        A, B, C, M, N, K, lda, ldb, ldc, a_vec, b_vec, c_vec, x.a_gather, nullptr, k_per_slice,
+        x.c_slice_stride);
+  SDCAB_CUDA_TRY(cudaGetLastError());
+  return SDCAB_OK;
+}
+
+template <typename T>
+int launch_gemm(const T* A, const T* B, T* C, int M, int N, int K, long long lda, long long ldb,
+                long long ldc, bool b_kmajor, cudaStream_t stream) {
+  return launch_gemm_tile<T, GemmTile<T>>(A, B, C, M, N, K, lda, ldb, ldc, b_kmajor, stream,
+                                          GemmExtras());
+}
+
+}  // namespace sdcab
