@@ -27,7 +27,7 @@
 namespace sdcab {
 namespace {
 
-constexpr int kFitThreads = 512;
+constexpr int kFitThreads = 288;   // warp 0 steps, 256 threads keep the score rows current
 constexpr int kFitWarps = kFitThreads / 32;
 constexpr int kBlockSteps = 64;   // steps whose score products are formed together
 
@@ -49,6 +49,7 @@ struct ChainArgs {
   const double* G;         // kBlockSteps x kBlockSteps (row b = example i_b)
   void* A;                 // dual variables, n x m
   void* D;                 // features: count x m, a_old - a_new of every step (0 if skipped)
+  double* t_keep;          // n: every example's threshold from its last step
   int m, count, kernel_input, s_on_chip;
 };
 
@@ -75,26 +76,67 @@ struct StepConsts {
   R rho, rho_inv;
 };
 
+// Warp sums of doubles through the integer reduction unit: every lane's term is
+// scaled by a power of two to a 57-bit fixed-point number, the three 21-bit limbs
+// are added by redux.sync, and the total is scaled back.  The sum is exact for
+// the fixed-point terms, so it does not depend on the order of the lanes; the
+// terms themselves are rounded at 2^-56 of `bound`, the same size as the
+// rounding of a floating-point sum.  Takes a fifth of the shuffle butterfly's
+// latency, which is what the step's chain of dependent reductions is made of.
+struct FixedScale {
+  double to_fixed, from_fixed;
+};
+// bound: a power of two not below any lane's |term|
+__device__ __forceinline__ FixedScale fixed_scale(int bound_exponent) {
+  FixedScale f;
+  f.to_fixed = __hiloint2double((1023 + 56 - bound_exponent) << 20, 0);
+  f.from_fixed = __hiloint2double((1023 - 56 + bound_exponent) << 20, 0);
+  return f;
+}
+__device__ __forceinline__ double warp_sum_fixed(double v, const FixedScale& f) {
+  const long long x = __double2ll_rn(v * f.to_fixed);
+  const int l0 = static_cast<int>(x & 0x1fffff), l1 = static_cast<int>((x >> 21) & 0x1fffff),
+            l2 = static_cast<int>(x >> 42);
+  const long long s0 = __reduce_add_sync(0xffffffffu, l0), s1 = __reduce_add_sync(0xffffffffu, l1),
+                  s2 = __reduce_add_sync(0xffffffffu, l2);
+  return static_cast<double>(s0 + (s1 << 21) + (s2 << 42)) * f.from_fixed;
+}
+__device__ __forceinline__ float warp_sum_fixed(float v, const FixedScale& f) {
+  return static_cast<float>(warp_sum_fixed(static_cast<double>(v), f));
+}
+// smallest e with |x| <= 2^e for every lane's x (finite)
+__device__ __forceinline__ int warp_bound_exponent(double x) {
+  const unsigned bits = __float_as_uint(__double2float_ru(fabs(x)));
+  const unsigned top = __reduce_max_sync(0xffffffffu, bits);
+  return static_cast<int>(top >> 23) - 127 + 1;
+}
+
 // f(t) = sum_i clip(v_i - t, 0, hi) over a row held in registers (NV entries per
-// lane, -inf where the lane has none), with the sizes of the sets it is made of:
-// u entries at hi, q entries above 0.
-template <typename R, int NV>
+// lane, -inf where the lane has none), with the sizes of the sets it is made of
+// (u entries at hi, q entries above 0).
+template <typename R>
 struct ClipSum {
   R f;
   int u, q;
 };
 template <typename R, int NV>
-__device__ __forceinline__ ClipSum<R, NV> clip_sum(const R (&v)[NV], R t, R hi) {
-  R s = 0;
+__device__ __forceinline__ ClipSum<R> clip_sum(const R (&v)[NV], R t, R hi, const FixedScale& fs) {
+  R x[NV];
   int cnt = 0;
 #pragma unroll
   for (int e = 0; e < NV; ++e) {
     const R d = v[e] - t;
-    s += min_(max_(d, R(0)), hi);
+    x[e] = min_(max_(d, R(0)), hi);
     cnt += (d > R(0) ? 1 : 0) + (d >= hi ? 0x10000 : 0);
   }
-  ClipSum<R, NV> out;
-  out.f = warp_sum(s);
+  // pairwise, to keep the chain of dependent additions short
+#pragma unroll
+  for (int h = NV / 2; h > 0; h >>= 1) {
+#pragma unroll
+    for (int e = 0; e < h; ++e) x[e] += x[e + h];
+  }
+  ClipSum<R> out;
+  out.f = warp_sum_fixed(x[0], fs);
   cnt = __reduce_add_sync(0xffffffffu, cnt);
   out.u = cnt >> 16; out.q = cnt & 0xffff;
   return out;
@@ -116,32 +158,62 @@ __device__ __forceinline__ ClipSum<R, NV> clip_sum(const R (&v)[NV], R t, R hi) 
 // Lane l holds classes l, l + 32, ...; a_new receives their new variables.
 // Returns false if the search did not settle (the caller then takes the general
 // routine).
+// What a step reads: the score row as the block's product left it, the change
+// of the previous step that this row has not received yet (pending_g = 0 if
+// none), the example's variables, and where the search for t starts.
+template <typename R, typename Data>
+struct StepInput {
+  const double* Sb;        // scores of the example at the start of the block (+ earlier corrections)
+  const double* pending;   // change of the previous step's variables (m entries)
+  double pending_g;        // its factor for this row
+  const Data* a_cur;       // current variables of the example
+  int m, y;
+  R t_start;
+};
+
 template <typename R, typename Data, int NV>
 __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>& sc, R hi, R rhs,
-                                                       const double* Sb, const Data* a_cur, int m,
-                                                       int y, Data (&a_new)[NV]) {
+                                                       const StepInput<R, Data>& in,
+                                                       Data (&a_old)[NV], Data (&a_new)[NV],
+                                                       R& t_out) {
   const int lane = threadIdx.x & 31;
+  const int m = in.m, y = in.y;
   const R neg_inf = -num<R>::inf(), pos_inf = num<R>::inf();
+  STAGE_BEGIN();
   // the vector to project (objective/l2_topk_hinge.h:55-59)
-  const Data vy = add_rn_(mul_rn_(sc.beta, a_cur[y]), mul_rn_(sc.alpha, static_cast<Data>(Sb[y])));
+  const Data score_y = static_cast<Data>(fma(in.pending[y], in.pending_g, in.Sb[y]));
+  const Data vy = add_rn_(mul_rn_(sc.beta, in.a_cur[y]), mul_rn_(sc.alpha, score_y));
   const Data shift = sc.alpha - vy;
   Data vd[NV];
   R v[NV];
+  double biggest = static_cast<double>(hi);
 #pragma unroll
   for (int e = 0; e < NV; ++e) {
     const int j = lane + 32 * e;
     const bool mine = j < m && j != y;
-    vd[e] = mine ? add_rn_(mul_rn_(sc.beta, a_cur[j]), mul_rn_(sc.alpha, static_cast<Data>(Sb[j]))) + shift
-                 : Data(0);
+    a_old[e] = j < m ? in.a_cur[j] : Data(0);
+    const Data score = j < m ? static_cast<Data>(fma(in.pending[j], in.pending_g, in.Sb[j])) : Data(0);
+    vd[e] = mine ? add_rn_(mul_rn_(sc.beta, a_old[e]), mul_rn_(sc.alpha, score)) + shift : Data(0);
     v[e] = mine ? static_cast<R>(vd[e]) : neg_inf;
+    biggest = fmax(biggest, fabs(static_cast<double>(vd[e])));
   }
-  const R rho = sc.rho, t0 = rho * rhs;
-  ClipSum<R, NV> c = clip_sum<R, NV>(v, t0, hi);
-  const bool equality = (c.f >= rhs);
+  // a lane's partial sums stay below NV * max(hi, |v|)
+  const FixedScale fs = fixed_scale(warp_bound_exponent(biggest) + (NV == 8 ? 3 : 2));
+  // Every solution has t >= 0.  The search starts from the threshold this example
+  // had in the previous epoch (0 in the first), which late in a fit is nearly the
+  // answer; t = rho rhs is only looked at when the steps get that far.
+  const R rho = sc.rho, t_split = rho * rhs;
+  R t = (in.t_start >= R(0) && in.t_start < t_split) ? in.t_start : R(0);
+  R tl = neg_inf, tr = pos_inf;
+  STAGE_CLK(8);
+  ClipSum<R> c = clip_sum<R, NV>(v, t, hi, fs);
+  STAGE_CLK(9);
+  bool equality = false;
   // phi(t) = rhs - f(t) (equality) or t - rho f(t) (biased): increasing, root wanted
-  R t = t0, tl, tr;
-  if (equality) { tl = t0; tr = pos_inf; } else { tl = neg_inf; tr = t0; }
   bool settled = false;
+#ifdef SDCAB_FIT_PROFILE
+  int evals = 1;
+#endif
   for (int it = 0; it < 48 && !settled; ++it) {
     const int inside = c.q - c.u;
     const R phi = equality ? rhs - c.f : t - rho * c.f;
@@ -172,83 +244,142 @@ __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>
       tn = t - phi / slope;
       if (tn == t) { settled = true; break; }   // the root of this piece, to the last bit
     }
-    if (!newton || !(tn > tl && tn < tr)) {
+    bool probe = false;
+    if (!equality && newton && tn >= t_split && t < t_split) {
+      tn = t_split;      // which case it is shows at t = rho rhs
+      probe = true;
+      newton = false;
+    } else if (!newton || !(tn > tl && tn < tr)) {
       if (!(tl > neg_inf) || !(tr < pos_inf)) return false;
       tn = tl + (tr - tl) / 2;
       newton = false;
       if (!(tn > tl && tn < tr)) return false;
     }
-    const ClipSum<R, NV> cn = clip_sum<R, NV>(v, tn, hi);
+#ifdef SDCAB_FIT_PROFILE
+    ++evals;
+#endif
+    const ClipSum<R> cn = clip_sum<R, NV>(v, tn, hi, fs);
     // a Newton step that finds the sets it started from has solved its piece exactly
     settled = newton && (cn.u == c.u && cn.q == c.q) && (!equality || inside > 0);
     t = tn; c = cn;
+    if (probe && c.f >= rhs) {
+      // the sum reaches rhs: the equality case, its root to the right of here
+      equality = true;
+      tl = t; tr = pos_inf;
+    }
   }
+#ifdef SDCAB_FIT_PROFILE
+  if (threadIdx.x == 0) { s_chain_clk[15] += evals; s_chain_clk[16] += equality ? 1 : 0; s_chain_clk[17] += settled ? 0 : 1; }
+#endif
+  STAGE_CLK(10);
   if (!settled) return false;
   // the reference's closed forms for the sets found (knapsack_le_biased.h:52;
   // knapsack_eq.h for the equality case): entries at hi, entries strictly inside
-  R sum_m = 0;
-#pragma unroll
-  for (int e = 0; e < NV; ++e) {
-    const R d = v[e] - t;
-    if (d > R(0) && !(d >= hi)) sum_m += v[e];
-  }
-  sum_m = warp_sum(sum_m);
   const int inside = c.q - c.u;
+  // the entries strictly inside add up to f + inside t - hi u  (f is their clipped sum)
+  const R sum_inside = c.f + static_cast<R>(inside) * t - hi * static_cast<R>(c.u);
   if (equality) {
-    if (inside > 0) t = (hi * static_cast<R>(c.u) + sum_m - rhs) / static_cast<R>(inside);
+    if (inside > 0) t = (hi * static_cast<R>(c.u) + sum_inside - rhs) / static_cast<R>(inside);
   } else {
-    t = (hi * static_cast<R>(c.u) + sum_m) / (sc.rho_inv + static_cast<R>(inside));
+    t = (hi * static_cast<R>(c.u) + sum_inside) / (sc.rho_inv + static_cast<R>(inside));
   }
+  STAGE_CLK(11);
   // new variables (objective/l2_topk_hinge.h:64-68)
   const Data td = static_cast<Data>(t), hid = static_cast<Data>(hi);
-  R total = 0;
+  R part[NV];
 #pragma unroll
   for (int e = 0; e < NV; ++e) {
     const int j = lane + 32 * e;
     const Data pj = (j < m && j != y) ? clip_(static_cast<Data>(vd[e] - td), Data(0), hid) : Data(0);
-    total += static_cast<R>(pj);
+    part[e] = static_cast<R>(pj);
     a_new[e] = -pj;
   }
-  total = warp_sum(total);
+#pragma unroll
+  for (int h = NV / 2; h > 0; h >>= 1) {
+#pragma unroll
+    for (int e = 0; e < h; ++e) part[e] += part[e + h];
+  }
+  const R total = warp_sum_fixed(part[0], fs);
   if ((y & 31) == lane) {
     const Data ay = static_cast<Data>(min_(rhs, total));
 #pragma unroll
     for (int e = 0; e < NV; ++e) if (e == (y >> 5)) a_new[e] = ay;
   }
+  t_out = t;
+  STAGE_CLK(12);
   return true;
 }
 
-// One step by warp 0 with the row in registers; writes the new variables, the
-// change `delta` and (features) decides whether the primal variables move.
+// The general routine, out of line so that the chain's registers are set by the
+// common path.
+template <typename R, typename Data>
+__device__ __noinline__ void general_update(const ObjectiveParams* o, Data norm2, const Data* scores,
+                                            Data* a, Data* v, int m, int y) {
+  update_dual_variables_multiclass<R, Data>(*o, norm2, scores, a, v, m, y);
+}
+
+// Where a step writes: the example's row of A, its change for the rows of S that
+// follow, (features) the change for the primal variables, the threshold for the
+// next epoch, and whether anything changed at all.
+template <typename Data>
+struct StepOutput {
+  Data* a_row;
+  double* delta;
+  Data* d_row;       // features only
+  double* t_keep;
+  int* skip;
+  int kernel_input;
+};
+
+// One step by warp 0 with the row in registers.
 template <typename R, typename Data, int NV>
 __device__ __forceinline__ bool warp_step_topk_hinge(const StepConsts<R, Data>& sc, R hi, R rhs,
-                                                     const double* Sb, const Data* a_cur, int m, int y,
-                                                     Data* a_row, double* delta, int kernel_input,
-                                                     int* skip) {
+                                                     const StepInput<R, Data>& in,
+                                                     const StepOutput<Data>& out) {
   const int lane = threadIdx.x & 31;
-  Data a_new[NV];
-  if (!warp_update_topk_hinge<R, Data, NV>(sc, hi, rhs, Sb, a_cur, m, y, a_new)) return false;
-  Data asum = 0;
+  Data a_old[NV], a_new[NV];
+  R t;
+  if (!warp_update_topk_hinge<R, Data, NV>(sc, hi, rhs, in, a_old, a_new, t)) return false;
+  if (lane == 0) *out.t_keep = static_cast<double>(t);
+  if (out.kernel_input) {
+#pragma unroll
+    for (int e = 0; e < NV; ++e) {
+      const int j = lane + 32 * e;
+      if (j < in.m) {
+        out.a_row[j] = a_new[e];
+        out.delta[j] = static_cast<double>(a_new[e]) - static_cast<double>(a_old[e]);
+      }
+    }
+    return true;
+  }
+  Data dlt[NV], asum = 0;
+#pragma unroll
+  for (int e = 0; e < NV; ++e) {
+    dlt[e] = a_old[e] - a_new[e];   // var_copy of update.h:74-77 (0 past the row's end)
+    asum += abs_(dlt[e]);
+  }
+  asum = warp_sum(asum);
+  const bool moved = asum > num<Data>::eps();   // update.h:78
+  if (!moved && lane == 0) *out.skip = 1;
 #pragma unroll
   for (int e = 0; e < NV; ++e) {
     const int j = lane + 32 * e;
-    if (j < m) {
-      const Data a_old = a_cur[j];
-      a_row[j] = a_new[e];
-      if (kernel_input) {
-        delta[j] = static_cast<double>(a_new[e]) - static_cast<double>(a_old);
-      } else {
-        const Data dlt = a_old - a_new[e];   // var_copy of update.h:74-77
-        asum += abs_(dlt);
-        delta[j] = static_cast<double>(dlt);
-      }
+    if (j < in.m) {
+      out.a_row[j] = a_new[e];
+      out.delta[j] = static_cast<double>(dlt[e]);
+      out.d_row[j] = moved ? dlt[e] : Data(0);
     }
   }
-  if (!kernel_input) {
-    asum = warp_sum(asum);
-    if (!(asum > num<Data>::eps()) && lane == 0) *skip = 1;   // update.h:78
-  }
   return true;
+}
+
+// Rows of 129 .. 256 classes: the same step out of line, so that the registers of
+// the chain are set by the short-row case.
+template <typename R, typename Data>
+__device__ __noinline__ bool warp_step_topk_hinge_long(const StepConsts<R, Data>* sc, R hi, R rhs,
+                                                       const StepInput<R, Data>* in,
+                                                       const StepOutput<Data>* out) {
+  return warp_step_topk_hinge<R, Data, 8>(*sc, hi, rhs, *in, *out);
 }
 
 template <typename Data, typename R>
@@ -257,15 +388,16 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
   const int m = p.m, count = p.count;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   double* G = reinterpret_cast<double*>(smem_raw);                  // 64 x 64
-  double* delta = G + kBlockSteps * kBlockSteps;                    // m
-  double* S = delta + m;                                            // count x m when on chip
+  double* delta = G + kBlockSteps * kBlockSteps;                    // 2 x m: this step's / the previous one's
+  double* S = delta + 2 * m;                                        // count x m when on chip
   Data* scores = reinterpret_cast<Data*>(p.s_on_chip ? S + static_cast<size_t>(kBlockSteps) * m : S);
   Data* a_s = scores + m;
   Data* v_s = a_s + m;
   Data* a_next = v_s + m;                                           // 2 x m, rows fetched ahead
   __shared__ long long s_idx[kBlockSteps];
   __shared__ int s_lab[kBlockSteps];
-  __shared__ int s_skip;
+  __shared__ double s_t[kBlockSteps];
+  __shared__ int s_skip[2];
   __shared__ StepConsts<R, Data> s_consts[kBlockSteps];
   const R hi_small = static_cast<R>(p.o.c) / static_cast<R>(p.o.k), rhs_small = static_cast<R>(p.o.c);
   const bool small_rows = (p.o.id == kObjL2TopkHinge || p.o.id == kObjL2TopkHingeSmooth) &&
@@ -279,11 +411,14 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
   long long t_begin = clock64();
 #endif
   for (int t = tid; t < kBlockSteps * kBlockSteps; t += kFitThreads) G[t] = p.G[t];
+  for (int t = tid; t < 2 * m; t += kFitThreads) delta[t] = 0.0;
   if (tid < count) {
     const long long i = p.order[tid];
     s_idx[tid] = i;
     s_lab[tid] = static_cast<int>(p.labels[i]);
+    s_t[tid] = p.t_keep[i];
   }
+  if (tid < 2) s_skip[tid] = 1;
   if (p.s_on_chip) {
     for (int t = tid; t < count * m; t += kFitThreads) S[t] = p.S[t];
   } else {
@@ -306,87 +441,100 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
   __syncthreads();
 
   CHAIN_CLK(0, t_begin);
+  // Step b is worked by warp 0.  Meanwhile the other warps bring the rows after b
+  // up to date with the change of step b - 1; row b itself receives that change
+  // from warp 0 as it reads the row, so nobody waits for anybody inside a step.
   for (int b = 0; b < count; ++b) {
 #ifdef SDCAB_FIT_PROFILE
     long long t_step = clock64();
 #endif
-    const long long i = s_idx[b];
-    const Data norm2 = s_consts[b].norm2;
-    const bool active = norm2 > Data(0);    // update.h:63,97
-    Data* a_cur = a_next + (b & 1) * m;
-    bool done = false;
-    if (warp == 0 && small_rows && active) {
-      CHAIN_CLK(1, t_step);
-      s_skip = 0;
+    const int cur = b & 1, prev = cur ^ 1;
+    const bool pending = (b > 0) && (s_skip[prev] == 0);
+    const double* d_prev = delta + prev * m;
+    if (warp == 0) {
+      const long long i = s_idx[b];
+      const Data norm2 = s_consts[b].norm2;
+      const bool active = norm2 > Data(0);    // update.h:63,97
+      const Data* a_cur = a_next + cur * m;
+      double* d_cur = delta + cur * m;
+      Data* d_row = p.kernel_input ? nullptr : D + static_cast<size_t>(b) * m;
+      if (lane == 0) s_skip[cur] = active ? 0 : 1;
       __syncwarp();
-      const double* Sb = S + static_cast<size_t>(b) * m;
-      done = (m <= 128)
-          ? warp_step_topk_hinge<R, Data, 4>(s_consts[b], hi_small, rhs_small, Sb, a_cur, m, s_lab[b],
-                                             A + i * m, delta, p.kernel_input, &s_skip)
-          : warp_step_topk_hinge<R, Data, 8>(s_consts[b], hi_small, rhs_small, Sb, a_cur, m, s_lab[b],
-                                             A + i * m, delta, p.kernel_input, &s_skip);
-      CHAIN_CLK(2, t_step);
-    }
-    if (warp == 0 && done) {
-      // nothing left to do for this step
-    } else if (warp == 0) {
-      if (lane == 0) s_skip = active ? 0 : 1;
-      if (active) {
-        const double* Sb = S + static_cast<size_t>(b) * m;
-        for (int j = lane; j < m; j += 32) { scores[j] = static_cast<Data>(Sb[j]); a_s[j] = a_cur[j]; }
-        __syncwarp();
+      bool done = !active;
+      if (!active && d_row) {
+        for (int j = lane; j < m; j += 32) d_row[j] = Data(0);
+      }
+      if (active && small_rows) {
+        StepInput<R, Data> in;
+        in.Sb = S + static_cast<size_t>(b) * m; in.pending = d_prev;
+        in.pending_g = pending ? G[(b - 1) * kBlockSteps + b] : 0.0;
+        in.a_cur = a_cur; in.m = m; in.y = s_lab[b]; in.t_start = static_cast<R>(s_t[b]);
+        StepOutput<Data> out;
+        out.a_row = A + i * m; out.delta = d_cur; out.d_row = d_row; out.t_keep = p.t_keep + i;
+        out.skip = &s_skip[cur]; out.kernel_input = p.kernel_input;
         CHAIN_CLK(1, t_step);
-        update_dual_variables_multiclass<R, Data>(p.o, norm2, scores, a_s, v_s, m, s_lab[b]);
+        done = (m <= 128) ? warp_step_topk_hinge<R, Data, 4>(s_consts[b], hi_small, rhs_small, in, out)
+                          : warp_step_topk_hinge_long<R, Data>(&s_consts[b], hi_small, rhs_small, &in, &out);
         CHAIN_CLK(2, t_step);
+      }
+      if (!done) {
+        // the general routine on the row in shared memory
+        const double* Sb = S + static_cast<size_t>(b) * m;
+        const double g = pending ? G[(b - 1) * kBlockSteps + b] : 0.0;
+        for (int j = lane; j < m; j += 32) {
+          scores[j] = static_cast<Data>(fma(d_prev[j], g, Sb[j]));
+          a_s[j] = a_cur[j];
+        }
+        __syncwarp();
+        general_update<R, Data>(&p.o, norm2, scores, a_s, v_s, m, s_lab[b]);
         Data asum = 0;
         for (int j = lane; j < m; j += 32) {
           const Data a_new = a_s[j], a_old = a_cur[j];
           A[i * m + j] = a_new;
           if (p.kernel_input) {
-            delta[j] = static_cast<double>(a_new) - static_cast<double>(a_old);
+            d_cur[j] = static_cast<double>(a_new) - static_cast<double>(a_old);
           } else {
             const Data dlt = a_old - a_new;   // var_copy of update.h:74-77
             asum += abs_(dlt);
-            delta[j] = static_cast<double>(dlt);
+            d_cur[j] = static_cast<double>(dlt);
           }
         }
         if (!p.kernel_input) {
           asum = warp_sum(asum);
-          if (!(asum > num<Data>::eps()) && lane == 0) s_skip = 1;   // update.h:78
+          const bool moved = asum > num<Data>::eps();   // update.h:78
+          if (!moved && lane == 0) s_skip[cur] = 1;
+          for (int j = lane; j < m; j += 32) d_row[j] = moved ? static_cast<Data>(d_cur[j]) : Data(0);
         }
       }
-    } else if (warp == 1 && b + 1 < count) {
-      Data* nxt = a_next + ((b + 1) & 1) * m;
-      const Data* src = A + s_idx[b + 1] * m;
-      for (int j = lane; j < m; j += 32) nxt[j] = src[j];
-    }
-    __syncthreads();
-    CHAIN_CLK(3, t_step);
-    const bool skip = s_skip != 0;
-    if (!p.kernel_input) {
-      Data* Db = D + static_cast<size_t>(b) * m;
-      for (int j = tid; j < m; j += kFitThreads) Db[j] = skip ? Data(0) : static_cast<Data>(delta[j]);
-    }
-    if (!skip) {
-      // later rows of S move by delta * G[b][row]; four rows in flight per thread
-      const double* Gb = G + b * kBlockSteps;
-      constexpr int kRowGroups = kFitThreads >> 7;
-      for (int j = tid & 127; j < m; j += 128) {
-        const double dj = delta[j];
-        int bb = b + 1 + (tid >> 7);
-        for (; bb + 3 * kRowGroups < count; bb += 4 * kRowGroups) {
-          double sv[4], gv[4];
+    } else {
+      const int h = tid - 32;
+      if (h < 32 && b + 1 < count) {
+        Data* nxt = a_next + prev * m;     // the buffer of step b + 1
+        const Data* src = A + s_idx[b + 1] * m;
+        for (int j = h; j < m; j += 32) nxt[j] = src[j];
+      }
+      if (pending) {
+        // rows b + 1 .. move by the change of step b - 1 times G[b - 1][row]
+        const double* Gp = G + (b - 1) * kBlockSteps;
+        constexpr int kRowGroups = (kFitThreads - 32) >> 7, kFlight = 8;
+        for (int j = h & 127; j < m; j += 128) {
+          const double dj = d_prev[j];
+          for (int first = b + 1 + (h >> 7); first < count; first += kFlight * kRowGroups) {
+            double sv[kFlight], gv[kFlight];
 #pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            gv[r] = Gb[bb + r * kRowGroups];
-            sv[r] = S[static_cast<size_t>(bb + r * kRowGroups) * m + j];
+            for (int r = 0; r < kFlight; ++r) {
+              const int bb = first + r * kRowGroups;
+              if (bb < count) {
+                gv[r] = Gp[bb];
+                sv[r] = S[static_cast<size_t>(bb) * m + j];
+              }
+            }
+#pragma unroll
+            for (int r = 0; r < kFlight; ++r) {
+              const int bb = first + r * kRowGroups;
+              if (bb < count) S[static_cast<size_t>(bb) * m + j] = fma(dj, gv[r], sv[r]);
+            }
           }
-#pragma unroll
-          for (int r = 0; r < 4; ++r) S[static_cast<size_t>(bb + r * kRowGroups) * m + j] = fma(dj, gv[r], sv[r]);
-        }
-        for (; bb < count; bb += kRowGroups) {
-          double* Sr = S + static_cast<size_t>(bb) * m;
-          Sr[j] = fma(dj, Gb[bb], Sr[j]);
         }
       }
     }
@@ -496,6 +644,7 @@ struct BlockRunner {
   double* S = nullptr;          // 64 x m
   double* G = nullptr;          // 64 x 64
   Data* D = nullptr;            // features: 64 x m
+  double* t_keep = nullptr;     // n
 
   static int pick_slices(int tiles, long long k, int bk, int sm_count) {
     long long want = (2LL * sm_count + tiles - 1) / tiles;
@@ -510,7 +659,7 @@ struct BlockRunner {
     const int tiles = static_cast<int>((m + GT::BN - 1) / GT::BN);
     slices = pick_slices(tiles, t->d, GT::BK, sm_count);
     g_slices = pick_slices(1, t->d, GT::BK, sm_count);
-    const size_t fixed = (kBlockSteps * kBlockSteps + m) * sizeof(double) + 5 * m * sizeof(Data);
+    const size_t fixed = (kBlockSteps * kBlockSteps + 2 * m) * sizeof(double) + 5 * m * sizeof(Data);
     const size_t with_s = fixed + static_cast<size_t>(kBlockSteps) * m * sizeof(double);
     s_on_chip = (with_s + 2048 <= info.smem_optin) ? 1 : 0;
     chain_smem = s_on_chip ? with_s : fixed;
@@ -522,6 +671,8 @@ struct BlockRunner {
     rc = buf.alloc(&s_parts, static_cast<size_t>(slices) * kBlockSteps * m); if (rc) return rc;
     rc = buf.alloc(&S, static_cast<size_t>(kBlockSteps) * m); if (rc) return rc;
     rc = buf.alloc(&G, static_cast<size_t>(kBlockSteps) * kBlockSteps); if (rc) return rc;
+    rc = buf.alloc(&t_keep, static_cast<size_t>(t->n)); if (rc) return rc;
+    SDCAB_CUDA_TRY(cudaMemset(t_keep, 0, static_cast<size_t>(t->n) * sizeof(double)));
     if (t->input_kind != SDCAB_INPUT_KERNEL) {
       rc = buf.alloc(&g_parts, static_cast<size_t>(g_slices) * kBlockSteps * kBlockSteps); if (rc) return rc;
       rc = buf.alloc(&D, static_cast<size_t>(kBlockSteps) * m); if (rc) return rc;
@@ -565,7 +716,7 @@ struct BlockRunner {
         kernel_input ? X : nullptr, t->n, ord, count, m, S, G);
     SDCAB_CUDA_TRY(cudaGetLastError());
     ChainArgs c;
-    c.o = o; c.order = ord; c.labels = t->labels; c.S = S; c.G = G; c.A = A; c.D = D;
+    c.o = o; c.order = ord; c.labels = t->labels; c.S = S; c.G = G; c.A = A; c.D = D; c.t_keep = t_keep;
     c.m = m; c.count = count; c.kernel_input = kernel_input ? 1 : 0; c.s_on_chip = s_on_chip;
     fit_chain_kernel<Data, R><<<1, kFitThreads, chain_smem, s>>>(c);
     SDCAB_CUDA_TRY(cudaGetLastError());
