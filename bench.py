@@ -239,6 +239,26 @@ def other_prox_config(args, rank, world, local_rank):
         "cpu_baseline": cpu, "gpu_launches": len(per_op) * max(args.steps, 10)}))
 
 
+def gap_roofline(tflops):
+    """The score GEMM runs on tcgen05 as 3xTF32: three tensor-core products per
+    useful multiply-add, TF32 at half the bf16 rate, so the useful-flop ceiling is
+    a sixth of the measured bf16 GEMM throughput."""
+    peak = None
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp = json.load(f)
+        bf16 = mp.get("bf16_tflops") or mp.get("bf16_tflops_sustained")   # a kernel timed alone
+        peak = float(bf16) / 6.0 if bf16 else None
+    except (OSError, ValueError):
+        pass
+    kind = "of measured" if peak else "of fallback"
+    if peak is None:
+        peak = 1590.0 / 6.0
+    return {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s (useful fp32 flop; 3xTF32)",
+            "frac": tflops / peak, "traffic": None, "peak_kind": kind,
+            "kernel": "gemm_tf32x3_kernel (tcgen05, TMA) + eval_loss_kernel"}
+
+
 def gap_config(args, rank, world, local_rank):
     """Config 4: duality-gap evaluation, top-k hinge alpha (k = 5), feature input,
     d = 4096, m = 1000, float32; examples sharded over the ranks, one all-reduce
@@ -328,12 +348,109 @@ def gap_config(args, rank, world, local_rank):
             "config": {"workload": "config 4: gap evaluation, top-k hinge alpha k=5, features d=4096, m=1000, "
                                    "%d examples per GPU, float32" % n, "examples_per_gpu": n,
                        "collective": "one all_reduce(sum) of %d doubles" % (8 + m)},
-            "roofline": {"bound": "fp32 fma (CUDA cores; tensor cores not used by this kernel yet)",
-                         "achieved": first["tflops"], "peak": None, "unit": "TFLOP/s", "frac": None,
-                         "traffic": None, "kernel": "gemm_kernel<float,128,128,16,8,8>"},
+            "roofline": gap_roofline(first["tflops"]),
             "results": results}))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def rbf_problem(torch, n, seed=6, dim=128, m=100, sigma=1.5):
+    """Config 5's data on the device: Gaussian blobs and their RBF Gram matrix,
+    gamma = 1 / dim, float64 (the same construction as synth.kernel_problem)."""
+    g = torch.Generator(device="cuda"); g.manual_seed(seed)
+    means = torch.randn(m, dim, generator=g, device="cuda", dtype=torch.float64)
+    labels = torch.randint(0, m, (n,), generator=g, device="cuda")
+    P = means[labels] + sigma * torch.randn(n, dim, generator=g, device="cuda", dtype=torch.float64)
+    sq = (P * P).sum(1)
+    K = P @ P.T
+    K.mul_(-2).add_(sq[:, None]).add_(sq[None, :]).clamp_(min=0).div_(-dim).exp_()
+    return K, labels
+
+
+def fit_config(args, rank, world, local_rank):
+    """Config 5: Crammer-Singer SDCA fit, kernel input, N = 50000 (or --rows),
+    m = 100, float64, epsilon = 1e-3, gap evaluated every epoch.  The steps of an
+    epoch are sequential, so ranks do not share the work: every rank runs the
+    same fit (replicas only) and rank 0 reports."""
+    import torch
+    import libsdca_b200 as sd
+    torch.cuda.set_device(local_rank)
+    n = args.rows if args.rows != FULL_ROWS else 50000
+    m = 100
+    K, labels = rbf_problem(torch, n)
+    A = torch.zeros(n, m, device="cuda", dtype=torch.float64)
+    # warm-up on a small problem (module load, workspace growth)
+    Kw, lw = rbf_problem(torch, 2048, seed=7)
+    sd.fit_(4, Kw, lw, torch.zeros(2048, m, device="cuda", dtype=torch.float64), kernel=True,
+            c=1.0, k=1, max_epoch=3, eval_epoch=1)
+    del Kw, lw
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    t0 = time.perf_counter()
+    r = sd.fit_(4, K, labels, A, kernel=True, c=1.0, k=1, max_epoch=args.max_epoch, eval_epoch=1,
+                epsilon=1e-3)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    clocks = sampler.finish() if sampler else None
+    if rank != 0:
+        return
+    epochs = max(1, r["epoch"])
+    last = r["history"][-1]
+    out = {
+        "metric": "SDCA fit seconds per epoch (Crammer-Singer, kernel input, gap evaluated every epoch)",
+        "value": (r["solve_seconds"] + r["eval_seconds"]) / epochs, "unit": "s", "n_gpus": world,
+        "steps": epochs, "warmup": 1, "ms_per_step": 1e3 * (r["solve_seconds"] + r["eval_seconds"]) / epochs,
+        "higher_is_better": False, "scaling": "replicas only", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": "config 5: msvm (l2_topk_hinge, k=1, c=1) fit on an RBF Gram matrix, "
+                               "N=%d, m=100, float64, epsilon=1e-3, eval_epoch=1" % n, "examples": n},
+        "fit": {"status": r["status"], "epochs": r["epoch"], "solve_seconds": r["solve_seconds"],
+                "eval_seconds": r["eval_seconds"], "seconds_per_epoch_updates": r["solve_seconds"] / epochs,
+                "seconds_per_evaluation": r["eval_seconds"] / max(1, r["num_evals"]),
+                "wall_seconds": wall, "primal": last["primal"], "dual": last["dual"],
+                "relative_gap": last["relative_gap"]},
+        "roofline": {"bound": "latency (a chain of N dependent steps per epoch)",
+                     "achieved": 1e6 * r["solve_seconds"] / epochs / n, "peak": None,
+                     "unit": "us/step", "frac": None, "traffic": None,
+                     "kernel": "fit_chain_kernel + gemm_kernel<double,64,64,8,4,4>"},
+        "gpu_launches": int(3 * ((n + 63) // 64) * r["epoch"] + 6 * r["num_evals"]),
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        out["cpu_baseline"] = fit_cpu_baseline(args.cpu_fit_examples, sd, torch)
+    print(json.dumps(out))
+
+
+def fit_cpu_baseline(n_small, sd, torch):
+    """The reference's solver on a bounded problem of the same family (the full size
+    would take it hours: an epoch reads A once per example, N^2 m multiply-adds), and
+    the same problem through the device fit for the comparison of the results."""
+    from libsdca_b200 import synth
+    from oracle import refapi
+    if not refapi.have_reference():
+        return {"value": None, "unit": "s/epoch", "cores": 1, "kind": "port",
+                "sample": "the compiled reference is not present and the oracle restatement has no solver"}
+    ref = refapi.reference()
+    K, labels = synth.kernel_problem(n=n_small, seed=6)
+    A_ref = np.zeros((n_small, 100))
+    t0 = time.perf_counter()
+    r = ref.fit("l2_topk_hinge", K, A_ref, labels, kernel=True, c=1.0, k=1, epsilon=1e-3,
+                max_epoch=200, eval_epoch=1)
+    dt = time.perf_counter() - t0
+    A = torch.zeros(n_small, 100, device="cuda", dtype=torch.float64)
+    g = sd.fit_(4, torch.from_numpy(K).cuda(), torch.from_numpy(labels).cuda(), A, kernel=True, c=1.0,
+                k=1, epsilon=1e-3, max_epoch=200, eval_epoch=1)
+    return {"value": dt / max(1, r["epoch"]), "unit": "s/epoch", "cores": 1, "kind": "reference",
+            "sample": "the reference's solver::solve (sequential BLAS) on N=%d of the same generator, "
+                      "%d epochs to epsilon=1e-3; its epoch cost grows with N^2" % (n_small, r["epoch"]),
+            "seconds": dt, "epochs": r["epoch"],
+            "device_same_problem": {"epochs": g["epoch"], "status": g["status"],
+                                    "seconds": g["solve_seconds"] + g["eval_seconds"],
+                                    "max_abs_diff_A": float(np.abs(A.cpu().numpy() - A_ref).max()),
+                                    "primal_diff": abs(g["history"][-1]["primal"] - r["history"][-1][0]),
+                                    "dual_diff": abs(g["history"][-1]["dual"] - r["history"][-1][1])}}
 
 
 def main():
@@ -346,7 +463,10 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=65536, help="rows of the CPU sample")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4],
+    ap.add_argument("--max-epoch", type=int, default=100, help="config 5: epoch limit")
+    ap.add_argument("--cpu-fit-examples", type=int, default=4000,
+                    help="config 5: size of the problem the reference's solver is timed on")
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="benchmark configuration; 2 (default) is the headline")
     ap.add_argument("--precision", default="double", choices=["double", "float"],
                     help="precision of thresholds and accumulators")
@@ -364,6 +484,8 @@ def main():
         return other_prox_config(args, rank, world, local_rank)
     if args.config == 4:
         return gap_config(args, rank, world, local_rank)
+    if args.config == 5:
+        return fit_config(args, rank, world, local_rank)
 
     import torch
     import libsdca_b200 as sd
