@@ -214,6 +214,26 @@ __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>
 #ifdef SDCAB_FIT_PROFILE
   int evals = 1;
 #endif
+  // The common course first, as a loop without side exits: t = rho f(t), Newton
+  // steps that stay inside the bracket and left of rho rhs.  Anything else drops
+  // into the general loop below with the state reached so far.
+  for (int it = 0; it < 16; ++it) {
+    const R phi = t - rho * c.f;
+    const R slope = R(1) + rho * static_cast<R>(c.q - c.u);
+    const R tn = t - phi / slope;
+    const bool at_root = (phi == R(0)) || (tn == t);
+    const R tl_n = phi < R(0) ? max_(tl, t) : tl, tr_n = phi < R(0) ? tr : min_(tr, t);
+    const bool plain = tn > tl_n && tn < tr_n && tn < t_split;
+    if (__any_sync(0xffffffffu, at_root || !plain)) break;
+    tl = tl_n; tr = tr_n;
+#ifdef SDCAB_FIT_PROFILE
+    ++evals;
+#endif
+    const ClipSum<R> cn = clip_sum<R, NV>(v, tn, hi, fs);
+    const bool same = (cn.u == c.u && cn.q == c.q);
+    t = tn; c = cn;
+    if (__any_sync(0xffffffffu, same)) { settled = true; break; }
+  }
   for (int it = 0; it < 48 && !settled; ++it) {
     const int inside = c.q - c.u;
     const R phi = equality ? rhs - c.f : t - rho * c.f;
@@ -546,35 +566,41 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
 #endif
 }
 
-// S[b][j] = sum over the slices of the split product, in slice order; G from the
-// kernel matrix (kernel input) or from the sliced Gram product, negated (features).
+// S[b][j] = sum over the slices of the split product; G from the kernel matrix
+// (kernel input) or from the sliced Gram product, negated (features).
 template <typename Data>
-__global__ void fit_pack_kernel(const Data* __restrict__ s_parts, int slices, long long slice_stride,
-                                const Data* __restrict__ g_parts, int g_slices, long long g_stride,
-                                const Data* __restrict__ K, long long n,
-                                const int64_t* __restrict__ order, int count, int m,
-                                double* __restrict__ S, double* __restrict__ G) {
-  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(256)
+fit_pack_kernel(const Data* __restrict__ s_parts, int slices, long long slice_stride,
+                const Data* __restrict__ g_parts, int g_slices, long long g_stride,
+                const Data* __restrict__ K, long long n, const int64_t* __restrict__ order,
+                int count, int m, double* __restrict__ S, double* __restrict__ G) {
+  // 64 outputs per block, the slices of each dealt to four threads (slice z to
+  // thread z mod 4); the four partial sums are added in a fixed order
+  __shared__ double part[4][64];
+  const int lane64 = threadIdx.x & 63, group = threadIdx.x >> 6;
+  const long long t = static_cast<long long>(blockIdx.x) * 64 + lane64;
   const long long s_elems = static_cast<long long>(count) * m;
-  if (t < s_elems) {
-    double acc = 0.0;
-    for (int z = 0; z < slices; ++z) acc += static_cast<double>(s_parts[z * slice_stride + t]);
-    S[t] = acc;
-    return;
-  }
   const long long u = t - s_elems;
-  if (u >= kBlockSteps * kBlockSteps) return;
-  const int b = static_cast<int>(u / kBlockSteps), bb = static_cast<int>(u % kBlockSteps);
-  double g = 0.0;
-  if (b < count && bb < count) {
-    if (K) {
-      g = static_cast<double>(K[order[b] + n * order[bb]]);
-    } else {
-      for (int z = 0; z < g_slices; ++z) g += static_cast<double>(g_parts[z * g_stride + b * count + bb]);
-      g = -g;
+  double acc = 0.0;
+  if (t < s_elems) {
+    for (int z = group; z < slices; z += 4) acc += static_cast<double>(s_parts[z * slice_stride + t]);
+  } else if (u < kBlockSteps * kBlockSteps) {
+    const int b = static_cast<int>(u / kBlockSteps), bb = static_cast<int>(u % kBlockSteps);
+    if (b < count && bb < count) {
+      if (K) {
+        if (group == 0) acc = static_cast<double>(K[order[b] + n * order[bb]]);
+      } else {
+        for (int z = group; z < g_slices; z += 4)
+          acc -= static_cast<double>(g_parts[z * g_stride + b * count + bb]);
+      }
     }
   }
-  G[u] = g;
+  part[group][lane64] = acc;
+  __syncthreads();
+  if (group != 0) return;
+  const double total = (part[0][lane64] + part[1][lane64]) + (part[2][lane64] + part[3][lane64]);
+  if (t < s_elems) S[t] = total;
+  else if (u < kBlockSteps * kBlockSteps) G[u] = total;
 }
 
 // W_j <- W_j - x_{i_b} * D[b][j] for the steps of one block in step order, every
@@ -711,7 +737,7 @@ struct BlockRunner {
     }
     if (rc) return rc;
     const long long pack_threads = static_cast<long long>(count) * m + kBlockSteps * kBlockSteps;
-    fit_pack_kernel<Data><<<static_cast<unsigned>((pack_threads + 255) / 256), 256, 0, s>>>(
+    fit_pack_kernel<Data><<<static_cast<unsigned>((pack_threads + 63) / 64), 256, 0, s>>>(
         s_parts, slices, x.c_slice_stride, g_parts, g_slices, static_cast<long long>(count) * count,
         kernel_input ? X : nullptr, t->n, ord, count, m, S, G);
     SDCAB_CUDA_TRY(cudaGetLastError());

@@ -93,6 +93,30 @@ def test_stopping_paths_and_given_order(ref, cuda_lib):
     compare(*run_both(*args, max_epoch=6, epsilon=0.0, permutations=perm), 1e-9, "given order")
 
 
+def test_float_thresholds_reach_the_same_solution(cuda_lib):
+    """opts.precision = 'single' of the reference's front end: thresholds and sums of
+    the step in float.  The reference's compiled solver here is double only, so the
+    check is against the double run: same objective values to float accuracy."""
+    K, labels = kernel_problem(n=900, dim=16, m=30, seed=5)
+    runs = {}
+    for precision in ("double", "float"):
+        A = dev(np.zeros((900, 30)))
+        runs[precision] = cuda_lib.fit_(4, dev(K), dev(labels), A, kernel=True, c=1.0, k=1,
+                                        precision=precision, max_epoch=40, eval_epoch=1)
+        assert runs[precision]["status"] == "solved"
+    d, f = runs["double"]["history"][-1], runs["float"]["history"][-1]
+    assert abs(d["dual"] - f["dual"]) <= 2e-3 * abs(d["dual"])
+    assert abs(d["primal"] - f["primal"]) <= 2e-3 * abs(d["primal"])
+
+
+def test_many_classes_take_the_general_step(ref, cuda_lib):
+    """More than 256 classes: the step runs the general threshold routines."""
+    K, labels = kernel_problem(n=400, dim=16, m=300, seed=9)
+    out = run_both(ref, cuda_lib, "l2_topk_hinge", K, labels, 300, True, np.float64, c=1.0, k=2,
+                   max_epoch=4)
+    compare(*out, 1e-9, "m=300")
+
+
 def test_rejects_what_it_cannot_fit(cuda_lib):
     from libsdca_b200.binding import SdcabError
     K, labels = kernel_problem(n=50, dim=4, m=4, seed=3)
