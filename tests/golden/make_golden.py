@@ -1,7 +1,8 @@
 """Generates tests/golden/*.npz from the reference's own headers.
 
 Run where the reference tree is available (it builds oracle/_ref first):
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py          # everything
+    python tests/golden/make_golden.py fit      # only fit_golden.npz
 The vectors are small seeded inputs together with the outputs, thresholds and
 evaluation records the reference produced for them; the tests load them without
 needing the reference.
@@ -20,9 +21,48 @@ from tests.util import PROX_SINGLE, random_opts, regime  # noqa: E402
 from tests.test_oracle_restatement import OBJECTIVES, random_problem  # noqa: E402
 
 
+HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth")
+
+
+def make_fit(ref):
+    """Small fits by the reference's solver: inputs, final variables, the records
+    of every evaluation, status and epoch count, and the order of the epochs."""
+    rng = np.random.default_rng(20240919)
+    out = {}
+    idx = 0
+    for objective in HINGE:
+        for dtype in (np.float32, np.float64):
+            for kernel in (False, True):
+                n, d, m = 48, 6, 5
+                X, labels, _ = random_problem(rng, n, d, m, dtype, False)
+                data = (X.astype(np.float64) @ X.astype(np.float64).T).astype(dtype) if kernel else X
+                A = np.zeros((n, m), dtype=dtype); W = np.zeros((m, d), dtype=dtype)
+                kw = dict(c=0.8, gamma=0.6, k=2)
+                r = ref.fit(objective, data, A, labels, W=None if kernel else W, kernel=kernel,
+                            epsilon=1e-3, max_epoch=25, eval_epoch=2, **kw)
+                key = "fit%03d" % idx
+                idx += 1
+                out[key + "_objective"] = np.array(objective)
+                out[key + "_kernel"] = np.array(kernel)
+                out[key + "_data"] = data
+                out[key + "_labels"] = labels
+                out[key + "_params"] = np.array([kw["c"], kw["gamma"], kw["k"], 1e-3, 25, 2])
+                out[key + "_A"] = A
+                out[key + "_W"] = W
+                out[key + "_history"] = r["history"]
+                out[key + "_status"] = np.array([r["status"], r["epoch"]])
+    out["order_n50000_first64"] = ref.epoch_permutations(50000, 2)[:, :64]
+    out["order_n1000"] = ref.epoch_permutations(1000, 3)
+    np.savez_compressed(os.path.join(HERE, "fit_golden.npz"), **out)
+    print("wrote", len(out), "fit arrays")
+
+
 def main():
     build_oracle.build_reference()
     ref = refapi.reference()
+    if sys.argv[1:] == ["fit"]:
+        make_fit(ref)
+        return
     rng = np.random.default_rng(20240607)
     out = {}
     idx = 0
@@ -80,6 +120,7 @@ def main():
                 ev[key + "_accuracy"] = rec["accuracy"]
     np.savez_compressed(os.path.join(HERE, "eval_golden.npz"), **ev)
     print("wrote", len(out), "prox arrays and", len(ev), "eval arrays")
+    make_fit(ref)
 
 
 if __name__ == "__main__":

@@ -29,3 +29,21 @@ def eval_cases():
                    c=float(z[key + "_params"][0]), gamma=float(z[key + "_params"][1]),
                    k=int(z[key + "_params"][2]), record=z[key + "_record"],
                    accuracy=z[key + "_accuracy"])
+
+
+def fit_cases():
+    z = np.load(os.path.join(HERE, "golden", "fit_golden.npz"))
+    keys = sorted({k.split("_")[0] for k in z.files if k.startswith("fit")})
+    for key in keys:
+        prm = z[key + "_params"]
+        yield dict(objective=str(z[key + "_objective"]), kernel=bool(z[key + "_kernel"]),
+                   data=z[key + "_data"], labels=z[key + "_labels"], c=float(prm[0]),
+                   gamma=float(prm[1]), k=int(prm[2]), epsilon=float(prm[3]), max_epoch=int(prm[4]),
+                   eval_epoch=int(prm[5]), A=z[key + "_A"], W=z[key + "_W"],
+                   history=z[key + "_history"], status=int(z[key + "_status"][0]),
+                   epoch=int(z[key + "_status"][1]))
+
+
+def epoch_orders():
+    z = np.load(os.path.join(HERE, "golden", "fit_golden.npz"))
+    return z["order_n50000_first64"], z["order_n1000"]

@@ -59,3 +59,18 @@ def test_argument_errors_need_no_gpu(lib):
     assert f(b"topk_entropy_biased", buf, C.c_int64(4), C.c_int64(2), C.byref(o), None) == -2
     o.alpha = 1.0; o.precision = 7
     assert f(b"knapsack", buf, C.c_int64(4), C.c_int64(2), C.byref(o), None) == -8
+
+
+def test_epoch_order_needs_no_gpu(lib):
+    """sdcab_epoch_permutations is host code: the committed orders of the reference's
+    solver (std::minstd_rand + std::shuffle) come out of the product library."""
+    import numpy as np
+    from tests.golden_util import epoch_orders
+    big, small = epoch_orders()
+    perm = np.zeros((3, 1000), dtype=np.int64)
+    assert lib.sdcab_epoch_permutations(C.c_int64(1000), C.c_int64(3), perm.ctypes.data_as(C.c_void_p)) == 0
+    assert np.array_equal(perm, small)
+    perm = np.zeros((2, 50000), dtype=np.int64)
+    assert lib.sdcab_epoch_permutations(C.c_int64(50000), C.c_int64(2), perm.ctypes.data_as(C.c_void_p)) == 0
+    assert np.array_equal(perm[:, :64], big)
+    assert lib.sdcab_epoch_permutations(C.c_int64(-1), C.c_int64(1), None) != 0

@@ -125,3 +125,19 @@ def test_rejects_what_it_cannot_fit(cuda_lib):
         cuda_lib.fit_(0, dev(K), dev(labels), A, kernel=True)   # softmax: no device step yet
     with pytest.raises(SdcabError):
         cuda_lib.fit_(4, dev(K[:, :40].copy()), dev(labels), A, kernel=True)  # kernel not square
+
+
+def test_golden_fits(cuda_lib):
+    """The committed fits of the reference's solver, without the reference at hand."""
+    from oracle.refapi import OBJECTIVES as IDS
+    from tests.golden_util import epoch_orders, fit_cases
+    from tests.test_hostsim_fit import golden_check
+    for c in fit_cases():
+        A = dev(np.zeros_like(c["A"])); W = None if c["kernel"] else dev(np.zeros_like(c["W"]))
+        r = cuda_lib.fit_(IDS[c["objective"]], dev(c["data"]), dev(c["labels"]), A, W=W,
+                          kernel=c["kernel"], c=c["c"], gamma=c["gamma"], k=c["k"],
+                          epsilon=c["epsilon"], max_epoch=c["max_epoch"], eval_epoch=c["eval_epoch"])
+        golden_check(c, r, A.cpu().numpy(), None if c["kernel"] else W.cpu().numpy())
+    big, small = epoch_orders()
+    assert np.array_equal(cuda_lib.epoch_permutations(50000, 2)[:, :64], big)
+    assert np.array_equal(cuda_lib.epoch_permutations(1000, 3), small)

@@ -72,3 +72,40 @@ def test_stopping_paths(ref, hostsim):
               eval_epoch=0, max_epoch=4)
     check_fit(ref, hostsim, "l2_topk_hinge", K, labels, True, np.float64, 1e-9, m=4,
               max_epoch=0)
+
+
+def golden_check(case, result, A, W):
+    from oracle.refapi import OBJECTIVES  # noqa: F401  (names only)
+    f64 = case["data"].dtype == np.float64
+    tol = 1e-9 if f64 else 2e-4
+    assert result["status_code"] == case["status"]
+    assert result["epoch"] == case["epoch"]
+    assert result["num_evals"] == len(case["history"])
+    assert np.abs(A - case["A"]).max() <= tol * max(1.0, np.abs(case["A"]).max())
+    if not case["kernel"]:
+        d = case["data"].shape[1]
+        assert np.abs(W - case["W"]).max() <= tol * max(1.0, np.abs(case["W"]).max()) * d
+    for rec, ref_rec in zip(result["history"], case["history"]):
+        for i, f in enumerate(("primal", "dual")):
+            assert abs(rec[f] - ref_rec[i]) <= 10 * tol * max(1.0, abs(ref_rec[i]))
+
+
+def test_golden_fits(hostsim):
+    from oracle.refapi import OBJECTIVES as IDS
+    from tests.golden_util import fit_cases
+    count = 0
+    for c in fit_cases():
+        A = np.zeros_like(c["A"]); W = np.zeros_like(c["W"])
+        r = hostsim.fit(IDS[c["objective"]], c["data"], c["labels"], A, W=None if c["kernel"] else W,
+                        kernel=c["kernel"], c=c["c"], gamma=c["gamma"], k=c["k"], epsilon=c["epsilon"],
+                        max_epoch=c["max_epoch"], eval_epoch=c["eval_epoch"])
+        golden_check(c, r, A, W)
+        count += 1
+    assert count == 16
+
+
+def test_golden_epoch_orders(hostsim):
+    from tests.golden_util import epoch_orders
+    big, small = epoch_orders()
+    assert np.array_equal(hostsim.epoch_permutations(50000, 2)[:, :64], big)
+    assert np.array_equal(hostsim.epoch_permutations(1000, 3), small)
