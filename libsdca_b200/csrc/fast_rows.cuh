@@ -201,6 +201,18 @@ __device__ __forceinline__ float round_down(float v, float) { return v; }
 __device__ __forceinline__ double round_down(double v, double) { return v; }
 __device__ __forceinline__ double round_down(float v, double) { return static_cast<double>(v); }
 
+// 1 / j for the set sizes that occur among at most 32 candidates: the searches
+// divide by small counts, and a multiplication by the tabulated reciprocal (one
+// rounding more than the division, far inside every tolerance) is a single
+// instruction where the division is a routine of thirty.
+__constant__ double kReciprocal[33] = {
+    0.0, 1.0, 1.0 / 2, 1.0 / 3, 1.0 / 4, 1.0 / 5, 1.0 / 6, 1.0 / 7, 1.0 / 8, 1.0 / 9, 1.0 / 10,
+    1.0 / 11, 1.0 / 12, 1.0 / 13, 1.0 / 14, 1.0 / 15, 1.0 / 16, 1.0 / 17, 1.0 / 18, 1.0 / 19, 1.0 / 20,
+    1.0 / 21, 1.0 / 22, 1.0 / 23, 1.0 / 24, 1.0 / 25, 1.0 / 26, 1.0 / 27, 1.0 / 28, 1.0 / 29, 1.0 / 30,
+    1.0 / 31, 1.0 / 32};
+template <typename R>
+__device__ __forceinline__ R over_count(R x, int j) { return x * static_cast<R>(kReciprocal[j]); }
+
 // ---- the compacted candidates, sorted ---------------------------------------
 // Lane i holds the i-th largest candidate (lanes >= n hold -inf) and the sum
 // of the first i + 1 of them, so a sum or a count over any value range is one
@@ -209,9 +221,13 @@ template <typename R>
 struct Sorted {
   R s, P;
   int n;
-  __device__ __forceinline__ R at(int i) const { return __shfl_sync(kFullMask, s, i); }
+  const R* shared;   // optional copy in shared memory: 32 values, then 32 prefix sums
+  __device__ __forceinline__ R at(int i) const {
+    return shared ? shared[i] : __shfl_sync(kFullMask, s, i);
+  }
   // sum of the i largest candidates
   __device__ __forceinline__ R pre(int i) const {
+    if (shared) return i > 0 ? shared[32 + i - 1] : R(0);
     const R v = __shfl_sync(kFullMask, P, i > 0 ? i - 1 : 0);
     return i > 0 ? v : R(0);
   }
@@ -220,9 +236,13 @@ struct Sorted {
   }
 };
 
+// `shared` (64 entries of this warp, optional) receives the sorted values and their
+// prefix sums, which turns every later look-up by index into one broadcast load.
 template <typename R, typename Data>
-__device__ __forceinline__ Sorted<R> sort_candidates(const LaneRow<Data>& cand, int n, int lane) {
+__device__ __forceinline__ Sorted<R> sort_candidates(const LaneRow<Data>& cand, int n, int lane,
+                                                     R* shared = nullptr) {
   Sorted<R> out;
+  out.shared = shared;
   const Data v = warp_sort_desc(cand.x, lane);
   out.s = static_cast<R>(v);
   out.n = n;
@@ -233,6 +253,12 @@ __device__ __forceinline__ Sorted<R> sort_candidates(const LaneRow<Data>& cand, 
     if (lane >= o) p += up;
   }
   out.P = p;
+  if (shared) {
+    __syncwarp();   // earlier readers of the previous row's copy are done
+    shared[lane] = out.s;
+    shared[32 + lane] = p;
+    __syncwarp();
+  }
   return out;
 }
 
@@ -240,8 +266,8 @@ __device__ __forceinline__ Sorted<R> sort_candidates(const LaneRow<Data>& cand, 
 // (include/sdca/prox/topk_cone.h:18-55 of the reference); `m` is the length of
 // the whole row.  Needs more than k candidates.
 template <typename R>
-__device__ __forceinline__ Projection sorted_special_cases(const Sorted<R>& c, int m, int k, R div,
-                                                           Thr<R>& thr) {
+__device__ __forceinline__ Projection sorted_special_cases(const Sorted<R>& c, int m, int k,
+                                                           R inv_div, Thr<R>& thr) {
   const R eps = 16 * num<R>::eps();
   const R sum_k = c.pre(k);
   if (sum_k <= eps) {
@@ -249,7 +275,7 @@ __device__ __forceinline__ Projection sorted_special_cases(const Sorted<R>& c, i
     return kProjZero;
   }
   const R v_k = c.at(k - 1);
-  const R hi = sum_k / div;
+  const R hi = sum_k * inv_div;
   const R t = v_k - hi;
   if (k == m || t >= c.at(k) - eps) {
     thr = make_thr(t, R(0), hi, k, 0, v_k, v_k);
@@ -304,58 +330,99 @@ __device__ __forceinline__ Thr<R> sorted_knapsack_eq(const Sorted<R>& c, R hi, R
 // With the u largest entries at hi, the others solve an ordinary simplex
 // projection onto the remaining mass rhs - u*hi, whose threshold over sorted
 // data is tau_j = (sum of the first j of them - mass) / j for the largest j with
-// s_j > tau_j; every lane evaluates its own j at once.  u grows from 0 until
-// the pair is consistent (entry u not above hi, entry u-1 above it), which is
-// the unique KKT point that the reference's variable fixing converges to
-// (include/sdca/prox/knapsack_eq.h:25-109); at most k + 1 rounds.
+// s_j > tau_j.  The pair (u, tau) is the solution when it is consistent (entry u
+// not above hi, entry u-1 above it), and the smallest consistent u is the unique
+// KKT point that the reference's variable fixing converges to
+// (include/sdca/prox/knapsack_eq.h:25-109).  Lane u works out its own candidate:
+// the sorted values and prefix sums go to shared memory once and every lane walks
+// over them, so all u <= k are tried in one pass instead of one round each.
+// `sorted` holds 2 x 32 entries of this warp.
 template <typename R>
 __device__ __forceinline__ bool sorted_capped_simplex(const Sorted<R>& c, R hi, R rhs, int k,
-                                                      int lane, Thr<R>& thr, R& sum_U) {
+                                                      int lane, R* sorted, Thr<R>& thr, R& sum_U) {
   const int n = c.n;
   const R inf = num<R>::inf();
-  for (int u = 0; u <= k && u < n; ++u) {
-    const R mass = rhs - static_cast<R>(u) * hi;
-    const R Pu = c.pre(u);
-    const int j_mine = lane - u + 1;
-    const bool valid = (lane >= u) && (lane < n);
-    // s_j > tau_j  <=>  j * s_j > (sum - mass): no division until j is known
-    const R excess = c.P - Pu - mass;
-    const R jr = static_cast<R>(valid ? j_mine : 1);
-    const unsigned above = __ballot_sync(kFullMask, valid && c.s * jr > excess);
-    const R s_u = c.at(u);
-    const R s_um1 = (u > 0) ? c.at(u - 1) : inf;
-    if (above == 0u) {
-      // nothing strictly inside: the u capped entries carry all the mass
-      if (u == 0) continue;
-      const R t = s_um1 - hi;
-      if (s_u <= t) {
-        sum_U = Pu;
-        thr = make_thr(t, R(0), hi, u, 0, s_um1, s_um1);
-        return true;
-      }
-      continue;
+  R* sm_s = sorted;
+  R* sm_P = sorted + 32;
+  sm_s[lane] = c.s;
+  sm_P[lane] = c.P;
+  __syncwarp();
+  const int u = lane;
+  const bool live = (u <= k) && (u < n);
+  const R Pu = (u > 0) ? sm_P[(u - 1) & 31] : R(0);
+  const R s_um1 = (u > 0) ? sm_s[(u - 1) & 31] : inf;
+  // s_j > tau_j  <=>  (j - u + 1) * s_j > P_j - (P_u + mass): no division until j is known
+  const R base = Pu + (rhs - static_cast<R>(u) * hi);
+  // The entries above their tau_j form a prefix of u, u + 1, ..., so the last one is
+  // found by bisection: five probes cover 32 candidates.
+  int last = -1;
+  {
+    int lo_j = u, hi_j = n;          // the last j that passes lies in [lo_j - 1, hi_j)
+#pragma unroll
+    for (int step = 0; step < 5; ++step) {
+      const int mid = (lo_j + hi_j) >> 1;
+      const bool probe = lo_j < hi_j;
+      const int jj = probe ? mid : 0;
+      const R sj = sm_s[jj], Pj = sm_P[jj];
+      const bool ok = probe && (sj * static_cast<R>(jj - u + 1) > Pj - base);
+      lo_j = ok ? mid + 1 : lo_j;
+      hi_j = (probe && !ok) ? mid : hi_j;
     }
-    const int last = 31 - __clz(above);
-    const R t = __shfl_sync(kFullMask, excess, last) / static_cast<R>(last - u + 1);
-    if (s_u - t <= hi && (u == 0 || s_um1 - t > hi)) {
-      sum_U = Pu;
-      thr = make_thr(t, R(0), hi, u, last - u + 1, (u > 0) ? s_um1 : inf, t);
-      return true;
-    }
+    last = lo_j - 1;
+    if (last < u) last = -1;
   }
-  return false;
+  R t;
+  int inside;
+  bool consistent;
+  if (last < 0) {
+    // nothing strictly inside: the u capped entries carry all the mass
+    t = s_um1 - hi;
+    inside = 0;
+    consistent = (u > 0) && (c.s <= t);
+  } else {
+    inside = last - u + 1;
+    t = over_count(sm_P[last] - base, inside);
+    consistent = (c.s - t <= hi) && (u == 0 || s_um1 - t > hi);
+  }
+  __syncwarp();
+  const unsigned found = __ballot_sync(kFullMask, live && consistent);
+  if (found == 0u) return false;
+  const int w = __ffs(found) - 1;
+  const R t_w = __shfl_sync(kFullMask, t, w);
+  const R prev_w = __shfl_sync(kFullMask, s_um1, w);
+  const int inside_w = __shfl_sync(kFullMask, inside, w);
+  sum_U = __shfl_sync(kFullMask, Pu, w);
+  thr = make_thr(t_w, R(0), hi, w, inside_w, prev_w, inside_w > 0 ? t_w : prev_w);
+  return true;
 }
 
 enum FastStatus { kFastDone = 0, kFastNeedsFullRow = 1 };
+
+// Constants of the top-k operators that do not depend on the row; worked out
+// once per thread, outside the loop over rows (three of them are divisions).
+template <typename R>
+struct TopkConsts {
+  R K, H, rho_k2, inv_div, inv_K, eps_rhs;
+  __device__ __forceinline__ TopkConsts(int k, R rhs, R rho) {
+    K = static_cast<R>(k);
+    H = rhs / K;
+    rho_k2 = rho * K * K;
+    inv_div = R(1) / (K + rho_k2);
+    inv_K = R(1) / K;
+    eps_rhs = num<R>::eps() * max_(R(1), abs_(rhs));
+  }
+};
 
 // Top-k simplex (rho = 0) and its biased form.  Returns kFastNeedsFullRow when
 // the row has to go through the general search on the full row.
 template <typename R, typename Data, int NV>
 __device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& row, int k, R rhs,
-                                                        R rho, Data* slots, int* counter, int lane, Thr<R>& thr) {
+                                                        R rho, const TopkConsts<R>& tc, Data* slots,
+                                                        int* counter, R* sorted, int lane,
+                                                        Thr<R>& thr) {
   const int m = row.size();
   if (k > 31 || m <= 32) return kFastNeedsFullRow;
-  const R K = static_cast<R>(k), H = rhs / K;
+  const R K = tc.K, H = tc.H;
   const Data tau = lane_max_cut(row, k, lane);
   // support of the knapsack step: a_i > t >= v_(k+1) - rhs/k >= tau - rhs/k
   const Data cut = round_down(static_cast<R>(tau) - H - abs_(static_cast<R>(tau)) * num<R>::eps() * 4,
@@ -364,19 +431,19 @@ __device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& 
   const int total = compact_candidates(row, cut, slots, counter, lane, cand);
   if (total > 32 || total <= k) return kFastNeedsFullRow;
   const Sorted<R> c = sort_candidates<R>(cand, total, lane);
-  const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
-  const R rho_k2 = rho * K * K;
-  const Projection proj = sorted_special_cases<R>(c, m, k, K + rho_k2, thr);
+  const R eps = tc.eps_rhs;
+  const R rho_k2 = tc.rho_k2;
+  const Projection proj = sorted_special_cases<R>(c, m, k, tc.inv_div, thr);
   if (proj == kProjZero) return kFastDone;
   R sum_U;
   if (proj == kProjConstant) {
     if (K * thr.hi > rhs + eps) {
-      if (!sorted_capped_simplex<R>(c, H, rhs, k, lane, thr, sum_U))
+      if (!sorted_capped_simplex<R>(c, H, rhs, k, lane, sorted, thr, sum_U))
         thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
     }
     return kFastDone;
   }
-  if (!sorted_capped_simplex<R>(c, H, rhs, k, lane, thr, sum_U))
+  if (!sorted_capped_simplex<R>(c, H, rhs, k, lane, sorted, thr, sum_U))
     thr = sorted_knapsack_eq<R>(c, H, rhs, sum_U);
   bool lt;
   if (thr.nU == 0) {
@@ -393,10 +460,11 @@ __device__ __forceinline__ FastStatus fast_topk_simplex(const RegRow<Data, NV>& 
 // it; anything else takes the general search.
 template <typename R, typename Data, int NV>
 __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row, int k, R rho,
-                                                     Data* slots, int* counter, int lane, Thr<R>& thr) {
+                                                     const TopkConsts<R>& tc, Data* slots, int* counter,
+                                                     R* sorted, int lane, Thr<R>& thr) {
   const int m = row.size();
   if (k > 31 || m <= 32 || rho != 0) return kFastNeedsFullRow;
-  const R K = static_cast<R>(k);
+  const R K = tc.K;
   const Data tau = lane_max_cut(row, k, lane);
   const Data cut = round_down(static_cast<R>(tau) - abs_(static_cast<R>(tau)) * num<R>::eps() * 4
                               - num<R>::tiny(), Data(0));
@@ -404,7 +472,8 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
   const int total = compact_candidates(row, cut, slots, counter, lane, cand);
   if (total > 32 || total <= k) return kFastNeedsFullRow;
   const Sorted<R> c = sort_candidates<R>(cand, total, lane);
-  if (sorted_special_cases<R>(c, m, k, K, thr) != kProjGeneral) return kFastDone;
+  const R inv_K = tc.inv_K;
+  if (sorted_special_cases<R>(c, m, k, inv_K, thr) != kProjGeneral) return kFastDone;
   const R eps = 16 * num<R>::eps();
   // sum and count of the positive entries.  U is empty on this branch, so no
   // output attains hi and only the acceptance test below depends on the sum:
@@ -428,7 +497,7 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
     j = warp_sum((cnt[0] + cnt[1]) + (cnt[2] + cnt[3]));
     s = warp_sum((static_cast<R>(acc[0]) + static_cast<R>(acc[1])) +
                  (static_cast<R>(acc[2]) + static_cast<R>(acc[3])));
-    const R hi_est = s / K;
+    const R hi_est = s * inv_K;
     const R mx = c.at(0);
     clear_cut = abs_(mx - hi_est) > R(1e-4) * max_(abs_(hi_est), abs_(mx));
   } else {
@@ -438,9 +507,9 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
     j = warp_sum(j); s = warp_sum(s);
   }
   if (!clear_cut) return kFastNeedsFullRow;
-  const R D = K * K;
-  const R t = (R(0) * s - K * R(0)) / D;
-  const R hi = (R(0) + K * s) / D;
+  // U empty: t = 0 and hi = K s / K^2 = s / K (include/sdca/prox/topk_cone.h:83-98)
+  const R t = R(0);
+  const R hi = s * inv_K;
   if (j > 0 && c.at(0) - eps <= hi + t) {
     thr = make_thr(t, R(0), hi, 0, j, num<R>::inf(), t);
     return kFastDone;
@@ -592,6 +661,7 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps_per_block = kFastThreads / 32;
   __shared__ int counters[kFastThreads / 32];
+  __shared__ R sorted_all[kFastThreads / 32][64];
   Data* slots = slots_all[warp];
   int* counter = &counters[warp];
   if (lane == 0) *counter = 0;
@@ -602,6 +672,8 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
   // operators with a fast path that can decline a row
   constexpr bool kStaged = kTopk || (std::is_same<Data, float>::value &&
                                      (PROX == kTopkEntropy || PROX == kEntropy));
+  const R rho_used = (PROX == kTopkSimplexBiased || PROX == kTopkConeBiased) ? static_cast<R>(q.rho) : R(0);
+  const TopkConsts<R> tc(q.k > 0 ? q.k : 1, static_cast<R>(q.rhs), rho_used);
   for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + warp; r < n;
        r += static_cast<long long>(gridDim.x) * warps_per_block) {
     RegRow<Data, NV> row;
@@ -610,12 +682,10 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
     Thr<R> thr;
     FastStatus st = kFastNeedsFullRow;
     if (PROX == kTopkSimplex || PROX == kTopkSimplexBiased) {
-      st = fast_topk_simplex<R>(row, q.k, static_cast<R>(q.rhs),
-                                PROX == kTopkSimplexBiased ? static_cast<R>(q.rho) : R(0),
-                                slots, counter, lane, thr);
+      st = fast_topk_simplex<R>(row, q.k, static_cast<R>(q.rhs), rho_used, tc, slots, counter,
+                                sorted_all[warp], lane, thr);
     } else if (PROX == kTopkCone || PROX == kTopkConeBiased) {
-      st = fast_topk_cone<R>(row, q.k, PROX == kTopkConeBiased ? static_cast<R>(q.rho) : R(0),
-                             slots, counter, lane, thr);
+      st = fast_topk_cone<R>(row, q.k, rho_used, tc, slots, counter, sorted_all[warp], lane, thr);
     }
     if (std::is_same<Data, float>::value && PROX == kTopkEntropy) {
       st = fast_topk_entropy<R, NV>(reinterpret_cast<const RegRow<float, NV>&>(row), q.k,

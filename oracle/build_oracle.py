@@ -6,7 +6,7 @@ Two libraries are produced:
   built; needs only gcc).
 * ``oracle/_ref/libsdca_ref.so`` -- ``ref_shim.cpp`` compiled against the
   reference's own, unmodified header tree.  Built only where that tree is
-  present (``SDCA_REFERENCE_DIR`` or ``/root/reference``); elsewhere the
+  present (``SDCA_REFERENCE_DIR``, or the default of ``REF_DIR`` below); elsewhere the
   prebuilt file that travelled with the repository is used as it is.
 
 The reference flags follow its default (non ``SDCA_ACCURATE_MATH``) build, but
