@@ -566,32 +566,46 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
 #endif
 }
 
-// S[b][j] = sum over the slices of the split product; G from the kernel matrix
-// (kernel input) or from the sliced Gram product, negated (features).
+// S[b][j] = sum over the slices of the split product, plus (when the product
+// left the previous block's examples out) those examples' share from their final
+// variables: sum_b' A[i'_b'][j] * Gx[b'][b].  With G given it is filled as well:
+// from the kernel matrix (kernel input) or from the sliced Gram product, negated
+// (features).
 template <typename Data>
-__global__ void __launch_bounds__(256)
-fit_pack_kernel(const Data* __restrict__ s_parts, int slices, long long slice_stride,
-                const Data* __restrict__ g_parts, int g_slices, long long g_stride,
-                const Data* __restrict__ K, long long n, const int64_t* __restrict__ order,
-                int count, int m, double* __restrict__ S, double* __restrict__ G) {
-  // 64 outputs per block, the slices of each dealt to four threads (slice z to
+struct PackArgs {
+  const Data* s_parts; int slices; long long slice_stride;
+  const Data* g_parts; int g_slices; long long g_stride;
+  const Data* K; long long n;
+  const int64_t* order; int count, m;
+  double* S; double* G;
+  const Data* A; const int64_t* prev_order; int prev_count; const double* Gx;
+};
+
+template <typename Data>
+__global__ void __launch_bounds__(256) fit_pack_kernel(PackArgs<Data> p) {
+  // 64 outputs per block, the terms of each dealt to four threads (term z to
   // thread z mod 4); the four partial sums are added in a fixed order
   __shared__ double part[4][64];
   const int lane64 = threadIdx.x & 63, group = threadIdx.x >> 6;
   const long long t = static_cast<long long>(blockIdx.x) * 64 + lane64;
-  const long long s_elems = static_cast<long long>(count) * m;
+  const long long s_elems = static_cast<long long>(p.count) * p.m;
   const long long u = t - s_elems;
   double acc = 0.0;
   if (t < s_elems) {
-    for (int z = group; z < slices; z += 4) acc += static_cast<double>(s_parts[z * slice_stride + t]);
-  } else if (u < kBlockSteps * kBlockSteps) {
+    for (int z = group; z < p.slices; z += 4) acc += static_cast<double>(p.s_parts[z * p.slice_stride + t]);
+    if (p.prev_count > 0) {
+      const int b = static_cast<int>(t / p.m), j = static_cast<int>(t % p.m);
+      for (int bp = group; bp < p.prev_count; bp += 4)
+        acc = fma(static_cast<double>(p.A[p.prev_order[bp] * p.m + j]), p.Gx[bp * kBlockSteps + b], acc);
+    }
+  } else if (p.G && u < kBlockSteps * kBlockSteps) {
     const int b = static_cast<int>(u / kBlockSteps), bb = static_cast<int>(u % kBlockSteps);
-    if (b < count && bb < count) {
-      if (K) {
-        if (group == 0) acc = static_cast<double>(K[order[b] + n * order[bb]]);
+    if (b < p.count && bb < p.count) {
+      if (p.K) {
+        if (group == 0) acc = static_cast<double>(p.K[p.order[b] + p.n * p.order[bb]]);
       } else {
-        for (int z = group; z < g_slices; z += 4)
-          acc -= static_cast<double>(g_parts[z * g_stride + b * count + bb]);
+        for (int z = group; z < p.g_slices; z += 4)
+          acc -= static_cast<double>(p.g_parts[z * p.g_stride + b * p.count + bb]);
       }
     }
   }
@@ -599,8 +613,31 @@ fit_pack_kernel(const Data* __restrict__ s_parts, int slices, long long slice_st
   __syncthreads();
   if (group != 0) return;
   const double total = (part[0][lane64] + part[1][lane64]) + (part[2][lane64] + part[3][lane64]);
-  if (t < s_elems) S[t] = total;
-  else if (u < kBlockSteps * kBlockSteps) G[u] = total;
+  if (t < s_elems) p.S[t] = total;
+  else if (p.G && u < kBlockSteps * kBlockSteps) p.G[u] = total;
+}
+
+// owner[i] = the block of 64 steps in which example i is visited this epoch
+__global__ void fit_owner_kernel(const int64_t* __restrict__ order, long long n, int* __restrict__ owner) {
+  const long long s = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (s < n) owner[order[s]] = static_cast<int>(s / kBlockSteps);
+}
+
+// G[b][b'] = K[i_b, i_b'] within a block and Gx[b'][b] = K[i'_b', i_b] from the
+// previous block's examples to this block's (kernel input).
+template <typename Data>
+__global__ void fit_gather_kernel(const Data* __restrict__ K, long long n,
+                                  const int64_t* __restrict__ order, int count,
+                                  const int64_t* __restrict__ prev_order, int prev_count,
+                                  double* __restrict__ G, double* __restrict__ Gx) {
+  const int u = blockIdx.x * blockDim.x + threadIdx.x;
+  const int which = u / (kBlockSteps * kBlockSteps), e = u % (kBlockSteps * kBlockSteps);
+  const int r = e / kBlockSteps, c = e % kBlockSteps;
+  if (which == 0) {
+    G[e] = (r < count && c < count) ? static_cast<double>(K[order[r] + n * order[c]]) : 0.0;
+  } else if (which == 1 && prev_count > 0) {
+    Gx[e] = (r < prev_count && c < count) ? static_cast<double>(K[prev_order[r] + n * order[c]]) : 0.0;
+  }
 }
 
 // W_j <- W_j - x_{i_b} * D[b][j] for the steps of one block in step order, every
@@ -636,13 +673,20 @@ template <> int eval_sums_call<double>(const sdcab_objective* o, const sdcab_pro
 }
 
 struct DeviceBuffers {
-  void* p[12] = {nullptr};
+  void* p[24] = {nullptr};
   int count = 0;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr, ahead = nullptr;
   cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t ev_product[2] = {nullptr, nullptr}, ev_steps[2] = {nullptr, nullptr}, ev_start = nullptr;
   ~DeviceBuffers() {
     for (int i = 0; i < count; ++i) cudaFree(p[i]);
     for (int i = 0; i < 4; ++i) if (ev[i]) cudaEventDestroy(ev[i]);
+    for (int i = 0; i < 2; ++i) {
+      if (ev_product[i]) cudaEventDestroy(ev_product[i]);
+      if (ev_steps[i]) cudaEventDestroy(ev_steps[i]);
+    }
+    if (ev_start) cudaEventDestroy(ev_start);
+    if (ahead) cudaStreamDestroy(ahead);
     if (stream) cudaStreamDestroy(stream);
   }
   template <typename T>
@@ -671,6 +715,11 @@ struct BlockRunner {
   double* G = nullptr;          // 64 x 64
   Data* D = nullptr;            // features: 64 x m
   double* t_keep = nullptr;     // n
+  // kernel input, two of each: block b + 1's product is formed while block b steps
+  Data* s_parts2[2] = {nullptr, nullptr};
+  double* G2[2] = {nullptr, nullptr};
+  double* Gx2[2] = {nullptr, nullptr};
+  int* owner = nullptr;         // n
 
   static int pick_slices(int tiles, long long k, int bk, int sm_count) {
     long long want = (2LL * sm_count + tiles - 1) / tiles;
@@ -694,7 +743,17 @@ struct BlockRunner {
                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(chain_smem)));
     int rc = buf.alloc(&order, static_cast<size_t>(t->n)); if (rc) return rc;
-    rc = buf.alloc(&s_parts, static_cast<size_t>(slices) * kBlockSteps * m); if (rc) return rc;
+    if (t->input_kind == SDCAB_INPUT_KERNEL) {
+      for (int h = 0; h < 2; ++h) {
+        rc = buf.alloc(&s_parts2[h], static_cast<size_t>(slices) * kBlockSteps * m); if (rc) return rc;
+        rc = buf.alloc(&G2[h], static_cast<size_t>(kBlockSteps) * kBlockSteps); if (rc) return rc;
+        rc = buf.alloc(&Gx2[h], static_cast<size_t>(kBlockSteps) * kBlockSteps); if (rc) return rc;
+      }
+      rc = buf.alloc(&owner, static_cast<size_t>(t->n)); if (rc) return rc;
+      s_parts = s_parts2[0];
+    } else {
+      rc = buf.alloc(&s_parts, static_cast<size_t>(slices) * kBlockSteps * m); if (rc) return rc;
+    }
     rc = buf.alloc(&S, static_cast<size_t>(kBlockSteps) * m); if (rc) return rc;
     rc = buf.alloc(&G, static_cast<size_t>(kBlockSteps) * kBlockSteps); if (rc) return rc;
     rc = buf.alloc(&t_keep, static_cast<size_t>(t->n)); if (rc) return rc;
@@ -737,9 +796,12 @@ struct BlockRunner {
     }
     if (rc) return rc;
     const long long pack_threads = static_cast<long long>(count) * m + kBlockSteps * kBlockSteps;
-    fit_pack_kernel<Data><<<static_cast<unsigned>((pack_threads + 63) / 64), 256, 0, s>>>(
-        s_parts, slices, x.c_slice_stride, g_parts, g_slices, static_cast<long long>(count) * count,
-        kernel_input ? X : nullptr, t->n, ord, count, m, S, G);
+    PackArgs<Data> pk;
+    pk.s_parts = s_parts; pk.slices = slices; pk.slice_stride = x.c_slice_stride;
+    pk.g_parts = g_parts; pk.g_slices = g_slices; pk.g_stride = static_cast<long long>(count) * count;
+    pk.K = kernel_input ? X : nullptr; pk.n = t->n; pk.order = ord; pk.count = count; pk.m = m;
+    pk.S = S; pk.G = G; pk.A = nullptr; pk.prev_order = nullptr; pk.prev_count = 0; pk.Gx = nullptr;
+    fit_pack_kernel<Data><<<static_cast<unsigned>((pack_threads + 63) / 64), 256, 0, s>>>(pk);
     SDCAB_CUDA_TRY(cudaGetLastError());
     ChainArgs c;
     c.o = o; c.order = ord; c.labels = t->labels; c.S = S; c.G = G; c.A = A; c.D = D; c.t_keep = t_keep;
@@ -750,6 +812,73 @@ struct BlockRunner {
       dim3 grid(static_cast<unsigned>((t->d + 255) / 256), static_cast<unsigned>(m));
       fit_primal_update_kernel<Data><<<grid, 256, 0, s>>>(W, X, D, ord, count, m, t->d);
       SDCAB_CUDA_TRY(cudaGetLastError());
+    }
+    return SDCAB_OK;
+  }
+
+  // One epoch of a kernel-input fit with the products one block ahead of the
+  // steps.  While block b steps on `sc`, block b + 1's product runs on `sg`
+  // with block b's examples left out of A (their rows are being rewritten); their
+  // share is added afterwards from their final variables (fit_pack_kernel).  Every
+  // other row of A is final by then: the product waits for block b - 1's steps.
+  int run_epoch_ahead(long long n, cudaStream_t sc, cudaStream_t sg, cudaEvent_t (&ev_product)[2],
+                      cudaEvent_t (&ev_steps)[2], cudaEvent_t ev_start) const {
+    typedef SmallGemmTile<Data> GT;
+    const int m = static_cast<int>(t->m);
+    const Data* K = static_cast<const Data*>(t->x);
+    Data* A = static_cast<Data*>(const_cast<void*>(t->a));
+    const long long blocks = (n + kBlockSteps - 1) / kBlockSteps;
+    auto count_of = [&](long long b) { return static_cast<int>(std::min<long long>(kBlockSteps, n - b * kBlockSteps)); };
+    fit_owner_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, sc>>>(order, n, owner);
+    SDCAB_CUDA_TRY(cudaGetLastError());
+    SDCAB_CUDA_TRY(cudaEventRecord(ev_start, sc));
+    SDCAB_CUDA_TRY(cudaStreamWaitEvent(sg, ev_start, 0));
+    auto product = [&](long long b) -> int {
+      const int h = static_cast<int>(b & 1), count = count_of(b);
+      const int64_t* ord = order + b * kBlockSteps;
+      GemmExtras x;
+      x.a_gather = ord; x.slices = slices;
+      x.c_slice_stride = static_cast<long long>(count) * m;
+      x.k_owner = owner; x.skip_owner = static_cast<int>(b - 1);   // -1 for the first block: nothing left out
+      int rc = launch_gemm_tile<Data, GT>(K, A, s_parts2[h], count, m, static_cast<int>(t->n), t->n, m, m,
+                                          false, sg, x);
+      if (rc) return rc;
+      fit_gather_kernel<Data><<<2 * kBlockSteps * kBlockSteps / 256, 256, 0, sg>>>(
+          K, t->n, ord, count, b > 0 ? ord - kBlockSteps : nullptr, b > 0 ? kBlockSteps : 0, G2[h], Gx2[h]);
+      SDCAB_CUDA_TRY(cudaGetLastError());
+      SDCAB_CUDA_TRY(cudaEventRecord(ev_product[h], sg));
+      return SDCAB_OK;
+    };
+    int rc = product(0);
+    if (rc) return rc;
+    for (long long b = 0; b < blocks; ++b) {
+      const int h = static_cast<int>(b & 1), count = count_of(b);
+      const int64_t* ord = order + b * kBlockSteps;
+      SDCAB_CUDA_TRY(cudaStreamWaitEvent(sc, ev_product[h], 0));
+      PackArgs<Data> pk;
+      pk.s_parts = s_parts2[h]; pk.slices = slices; pk.slice_stride = static_cast<long long>(count) * m;
+      pk.g_parts = nullptr; pk.g_slices = 0; pk.g_stride = 0; pk.K = nullptr; pk.n = t->n;
+      pk.order = ord; pk.count = count; pk.m = m; pk.S = S; pk.G = nullptr;
+      pk.A = A; pk.prev_order = b > 0 ? ord - kBlockSteps : nullptr; pk.prev_count = b > 0 ? kBlockSteps : 0;
+      pk.Gx = Gx2[h];
+      const long long pack_threads = static_cast<long long>(count) * m;
+      fit_pack_kernel<Data><<<static_cast<unsigned>((pack_threads + 63) / 64), 256, 0, sc>>>(pk);
+      SDCAB_CUDA_TRY(cudaGetLastError());
+      SDCAB_CUDA_TRY(cudaEventRecord(ev_steps[h], sc));   // block b - 1 has stepped, block b's scores are packed
+      ChainArgs c;
+      c.o = o; c.order = ord; c.labels = t->labels; c.S = S; c.G = G2[h]; c.A = A; c.D = nullptr;
+      c.t_keep = t_keep; c.m = m; c.count = count; c.kernel_input = 1; c.s_on_chip = s_on_chip;
+      fit_chain_kernel<Data, R><<<1, kFitThreads, chain_smem, sc>>>(c);
+      SDCAB_CUDA_TRY(cudaGetLastError());
+      // The next product may start once block b - 1 has stepped; it is released
+      // together with block b's steps (after the pack), on a stream of lower priority,
+      // so that the stepping thread block holds its SM before the product's thread
+      // blocks spread over the others.
+      if (b + 1 < blocks) {
+        SDCAB_CUDA_TRY(cudaStreamWaitEvent(sg, ev_steps[h], 0));
+        rc = product(b + 1);
+        if (rc) return rc;
+      }
     }
     return SDCAB_OK;
   }
@@ -775,8 +904,16 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
   if (rc) return rc;
 
   DeviceBuffers buf;
-  SDCAB_CUDA_TRY(cudaStreamCreateWithFlags(&buf.stream, cudaStreamNonBlocking));
+  int prio_low = 0, prio_high = 0;
+  SDCAB_CUDA_TRY(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high));
+  SDCAB_CUDA_TRY(cudaStreamCreateWithPriority(&buf.stream, cudaStreamNonBlocking, prio_high));
+  SDCAB_CUDA_TRY(cudaStreamCreateWithPriority(&buf.ahead, cudaStreamNonBlocking, prio_low));
   for (int e = 0; e < 4; ++e) SDCAB_CUDA_TRY(cudaEventCreate(&buf.ev[e]));
+  for (int e = 0; e < 2; ++e) {
+    SDCAB_CUDA_TRY(cudaEventCreateWithFlags(&buf.ev_product[e], cudaEventDisableTiming));
+    SDCAB_CUDA_TRY(cudaEventCreateWithFlags(&buf.ev_steps[e], cudaEventDisableTiming));
+  }
+  SDCAB_CUDA_TRY(cudaEventCreateWithFlags(&buf.ev_start, cudaEventDisableTiming));
   cudaStream_t s = buf.stream;
   // everything queued on the caller's stream so far comes first
   SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[0], user_stream));
@@ -850,9 +987,14 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
     SDCAB_CUDA_TRY(cudaMemcpyAsync(runner.order, order_src, static_cast<size_t>(n) * sizeof(int64_t),
                                    cudaMemcpyHostToDevice, s));
     SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[0], s));
-    for (long long first = 0; first < n; first += kBlockSteps) {
-      rc = runner.run(first, static_cast<int>(std::min<long long>(kBlockSteps, n - first)), s);
+    if (train->input_kind == SDCAB_INPUT_KERNEL) {
+      rc = runner.run_epoch_ahead(n, s, buf.ahead, buf.ev_product, buf.ev_steps, buf.ev_start);
       if (rc) return rc;
+    } else {
+      for (long long first = 0; first < n; first += kBlockSteps) {
+        rc = runner.run(first, static_cast<int>(std::min<long long>(kBlockSteps, n - first)), s);
+        if (rc) return rc;
+      }
     }
     SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[1], s));
     SDCAB_CUDA_TRY(cudaStreamSynchronize(s));

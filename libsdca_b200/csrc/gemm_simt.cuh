@@ -56,7 +56,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int M, int N,
             int K, long long lda, long long ldb, long long ldc, int a_vec, int b_vec, int c_vec,
             const int64_t* __restrict__ a_gather, const int64_t* __restrict__ b_gather,
-            int k_per_slice, long long c_slice_stride) {
+            int k_per_slice, long long c_slice_stride, const int* __restrict__ k_owner,
+            int skip_owner) {
   constexpr int NT = (BM / TM) * (BN / TN);
   constexpr int V = 16 / sizeof(T);
   constexpr int PAD = V;
@@ -71,6 +72,7 @@ gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
     const long long kb = static_cast<long long>(blockIdx.z) * k_per_slice;
     A += kb;
     B += B_KMAJOR ? kb : kb * ldb;
+    if (k_owner) k_owner += kb;
     C += static_cast<long long>(blockIdx.z) * c_slice_stride;
     K = (K - kb < k_per_slice) ? static_cast<int>(K - kb) : k_per_slice;
     if (K < 0) K = 0;
@@ -87,7 +89,12 @@ gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
       const int idx = tid + it * NT;
       const int kk = idx / (BN / V), nv = (idx % (BN / V)) * V;
       const int gk = k0 + kk, gn = col0 + nv;
-      if (gk < K && b_vec && gn + V <= N) {
+      // rows of B whose owner is being rewritten elsewhere count as zero and are not read
+      const bool skipped = k_owner && gk < K && k_owner[gk] == skip_owner;
+      if (skipped) {
+#pragma unroll
+        for (int c = 0; c < V; ++c) rb[it][c] = T(0);
+      } else if (gk < K && b_vec && gn + V <= N) {
         const Vec v = *reinterpret_cast<const Vec*>(B + static_cast<long long>(gk) * ldb + gn);
         const T* e = reinterpret_cast<const T*>(&v);
 #pragma unroll
@@ -204,6 +211,10 @@ struct GemmExtras {
   const int64_t* b_gather = nullptr;
   int slices = 1;
   long long c_slice_stride = 0;
+  // B with the contraction index as its row index only: rows k with
+  // k_owner[k] == skip_owner are left out of the product (and not read)
+  const int* k_owner = nullptr;
+  int skip_owner = -1;
 };
 
 template <typename T, typename G>
@@ -225,11 +236,11 @@ int launch_gemm_tile(const T* A, const T* B, T* C, int M, int N, int K, long lon
   if (b_kmajor)
     gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, true><<<grid, threads, 0, stream>>>(
         A, B, C, M, N, K, lda, ldb, ldc, a_vec, b_vec, c_vec, x.a_gather, x.b_gather, k_per_slice,
-        x.c_slice_stride);
+        x.c_slice_stride, nullptr, -1);
   else
     gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, false><<<grid, threads, 0, stream>>>(
         A, B, C, M, N, K, lda, ldb, ldc, a_vec, b_vec, c_vec, x.a_gather, nullptr, k_per_slice,
-        x.c_slice_stride);
+        x.c_slice_stride, x.k_owner, x.skip_owner);
   SDCAB_CUDA_TRY(cudaGetLastError());
   return SDCAB_OK;
 }
