@@ -48,6 +48,11 @@ PROX_CONFIGS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of fast_rows_kernel<float,double,top-k simplex,8>
+# per row, from the ncu capture summarised in profiles/ (262.2 MB + 214.2 MB over 65536 rows)
+NCU_DRAM_BYTES_PER_ROW = 4001 + 3268
+
+
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -593,7 +598,10 @@ def main():
             "dtype": "f32", "data": "synthetic",
             "config": workload_config(rows, world, "device-resident inputs, out-of-place kernels"),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "kernel": slow,
+                         "frac": achieved / peak, "traffic": rows * NCU_DRAM_BYTES_PER_ROW, "kernel": slow,
+                         "traffic_note": "dram read + write bytes of one launch, scaled by rows from the ncu "
+                                         "capture of a 65536-row launch (4001 B read + 3268 B written per row "
+                                         "while the kernel runs; the last 732 B per row leave L2 afterwards)",
                          "peak_kind": "of " + peak_kind,
                          "per_kernel_ms": per_op_ms,
                          "per_kernel_gbs": {k: rows * BYTES_PER_ROW / (v * 1e-3) / 1e9
