@@ -330,8 +330,9 @@ int sdcab_epoch_permutations(int64_t n, int64_t num_epochs, int64_t* perm);
  * (m x n dual variables, read as the starting point) and, for features, w
  * (d x m primal variables, kept equal to X A').  The objective must be one of
  * the hinge family (SDCAB_OBJ_L2_HINGE_TOPK[_SMOOTH], SDCAB_OBJ_L2_TOPK_HINGE[_SMOOTH];
- * Crammer-Singer is SDCAB_OBJ_L2_TOPK_HINGE with k = 1); others return
- * SDCAB_ERR_NOT_IMPLEMENTED.  The steps of one epoch are sequential by
+ * Crammer-Singer is SDCAB_OBJ_L2_TOPK_HINGE with k = 1) or the top-k softmax
+ * SDCAB_OBJ_L2_ENTROPY_TOPK; the others (whose steps need prox_two_entropy or the
+ * multilabel projections) return SDCAB_ERR_NOT_IMPLEMENTED.  The steps of one epoch are sequential by
  * definition; each step spreads its score product over the whole GPU.
  *   permutations: optional host array, max_epoch * n example indices (the
  *                 order of every epoch); NULL uses sdcab_epoch_permutations.

@@ -21,7 +21,8 @@ from tests.util import PROX_SINGLE, random_opts, regime  # noqa: E402
 from tests.test_oracle_restatement import OBJECTIVES, random_problem  # noqa: E402
 
 
-HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth")
+HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth",
+         "l2_entropy_topk")
 
 
 def make_fit(ref):

@@ -10,7 +10,8 @@ from tests.util import stable_seed
 
 pytestmark = pytest.mark.gpu
 
-HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth")
+HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth",
+         "l2_entropy_topk")
 REF_STATUS = ("none", "solving", "solved", "no_progress", "max_epoch", "max_cpu_time",
               "max_wall_time", "failed")
 
@@ -122,7 +123,7 @@ def test_rejects_what_it_cannot_fit(cuda_lib):
     K, labels = kernel_problem(n=50, dim=4, m=4, seed=3)
     A = dev(np.zeros((50, 4)))
     with pytest.raises(SdcabError):
-        cuda_lib.fit_(0, dev(K), dev(labels), A, kernel=True)   # softmax: no device step yet
+        cuda_lib.fit_(0, dev(K), dev(labels), A, kernel=True)   # l2_entropy: its step needs prox_two_entropy
     with pytest.raises(SdcabError):
         cuda_lib.fit_(4, dev(K[:, :40].copy()), dev(labels), A, kernel=True)  # kernel not square
 

@@ -8,7 +8,8 @@ from libsdca_b200.synth import kernel_problem
 from tests.test_oracle_restatement import random_problem
 from tests.util import stable_seed
 
-HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth")
+HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth",
+         "l2_entropy_topk")
 REF_STATUS = ("none", "solving", "solved", "no_progress", "max_epoch", "max_cpu_time",
               "max_wall_time", "failed")
 
@@ -101,7 +102,7 @@ def test_golden_fits(hostsim):
                         max_epoch=c["max_epoch"], eval_epoch=c["eval_epoch"])
         golden_check(c, r, A, W)
         count += 1
-    assert count == 16
+    assert count == 20
 
 
 def test_golden_epoch_orders(hostsim):
