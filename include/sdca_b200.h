@@ -328,11 +328,12 @@ int sdcab_epoch_permutations(int64_t n, int64_t num_epochs, int64_t* perm);
  * matrix (n x n, input_kind SDCAB_INPUT_KERNEL, d == n) or the features
  * (d x n) in x, labels, and the variables the fit updates in place -- a
  * (m x n dual variables, read as the starting point) and, for features, w
- * (d x m primal variables, kept equal to X A').  The objective must be one of
- * the hinge family (SDCAB_OBJ_L2_HINGE_TOPK[_SMOOTH], SDCAB_OBJ_L2_TOPK_HINGE[_SMOOTH];
- * Crammer-Singer is SDCAB_OBJ_L2_TOPK_HINGE with k = 1) or the top-k softmax
- * SDCAB_OBJ_L2_ENTROPY_TOPK; the others (whose steps need prox_two_entropy or the
- * multilabel projections) return SDCAB_ERR_NOT_IMPLEMENTED.  The steps of one epoch are sequential by
+ * (d x m primal variables, kept equal to X A').  Every objective of the list above
+ * has its step (update_dual_variables of include/sdca/solver/objective/*.h);
+ * multilabel objectives take labels / offsets as for the evaluation.  The top-k
+ * hinge (beta) family, Crammer-Singer included, has a register-resident step for
+ * up to 256 classes; the others run the general threshold routines.
+ * The steps of one epoch are sequential by
  * definition; each step spreads its score product over the whole GPU.
  *   permutations: optional host array, max_epoch * n example indices (the
  *                 order of every epoch); NULL uses sdcab_epoch_permutations.

@@ -331,13 +331,13 @@ def epoch_permutations(n, num_epochs):
 
 def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
          precision="double", epsilon=1e-3, max_epoch=1000, eval_epoch=10, eval_on_start=False,
-         permutations=None):
+         permutations=None, offsets=None):
     """SDCA fit on torch CUDA tensors, in place on ``A`` (n x m) and ``W`` (m x d).
 
     Mirrors ``matsdca_fit``'s stopping options (src/matlab/mex_solve.cpp:505-528 of the
     reference); returns status, epochs and the evaluation records."""
     obj = objective if isinstance(objective, Objective) else make_objective(objective, c, gamma, k, precision)
-    prob = make_problem(X, labels, A, W, None, None, kernel, True)
+    prob = make_problem(X, labels, A, W, None, offsets, kernel, True)
     crit = FitCriteria(epsilon, max_epoch, eval_epoch, 1 if eval_on_start else 0, 0)
     cap = int(max_epoch) + 4
     evals = (EvalRecord * cap)()

@@ -44,6 +44,7 @@ struct ChainArgs {
   ObjectiveParams o;
   const int64_t* order;    // the block's examples: order[0 .. count)
   const int64_t* labels;
+  const int64_t* offsets;  // multilabel objectives: the labels of example i are labels[offsets[i] .. offsets[i+1])
   double* S;               // count x m, scores at the start of the block (updated in place
                            // when they do not fit on chip)
   const double* G;         // kBlockSteps x kBlockSteps (row b = example i_b)
@@ -351,6 +352,13 @@ struct StepOutput {
   int kernel_input;
 };
 
+template <typename R, typename Data>
+__device__ __noinline__ void general_update_multilabel(const ObjectiveParams* o, Data norm2,
+                                                       const Data* scores, Data* a, Data* v, int m,
+                                                       const unsigned* mask, int num_labels) {
+  update_dual_variables_multilabel_hinge<R, Data>(*o, norm2, scores, a, v, m, mask, num_labels);
+}
+
 // One step by warp 0 with the row in registers.
 template <typename R, typename Data, int NV>
 __device__ __forceinline__ bool warp_step_topk_hinge(const StepConsts<R, Data>& sc, R hi, R rhs,
@@ -414,6 +422,9 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
   Data* a_s = scores + m;
   Data* v_s = a_s + m;
   Data* a_next = v_s + m;                                           // 2 x m, rows fetched ahead
+  unsigned* label_mask = reinterpret_cast<unsigned*>(a_next + 2 * m);   // (m + 31) / 32 words (multilabel)
+  const bool multilabel = objective_is_multilabel(p.o.id);
+  __shared__ long long s_off[kBlockSteps];
   __shared__ long long s_idx[kBlockSteps];
   __shared__ int s_lab[kBlockSteps];
   __shared__ double s_t[kBlockSteps];
@@ -435,7 +446,12 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
   if (tid < count) {
     const long long i = p.order[tid];
     s_idx[tid] = i;
-    s_lab[tid] = static_cast<int>(p.labels[i]);
+    if (multilabel) {
+      s_off[tid] = p.offsets[i];
+      s_lab[tid] = static_cast<int>(p.offsets[i + 1] - p.offsets[i]);   // number of labels
+    } else {
+      s_lab[tid] = static_cast<int>(p.labels[i]);
+    }
     s_t[tid] = p.t_keep[i];
   }
   if (tid < 2) s_skip[tid] = 1;
@@ -506,7 +522,18 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
           a_s[j] = a_cur[j];
         }
         __syncwarp();
-        general_update<R, Data>(&p.o, norm2, scores, a_s, v_s, m, s_lab[b]);
+        if (multilabel) {
+          for (int w = lane; w < (m + 31) / 32; w += 32) label_mask[w] = 0u;
+          __syncwarp();
+          for (int g = lane; g < s_lab[b]; g += 32) {
+            const int lab = static_cast<int>(p.labels[s_off[b] + g]);
+            atomicOr(&label_mask[lab >> 5], 1u << (lab & 31));
+          }
+          __syncwarp();
+          general_update_multilabel<R, Data>(&p.o, norm2, scores, a_s, v_s, m, label_mask, s_lab[b]);
+        } else {
+          general_update<R, Data>(&p.o, norm2, scores, a_s, v_s, m, s_lab[b]);
+        }
         Data asum = 0;
         for (int j = lane; j < m; j += 32) {
           const Data a_new = a_s[j], a_old = a_cur[j];
@@ -734,7 +761,8 @@ struct BlockRunner {
     const int tiles = static_cast<int>((m + GT::BN - 1) / GT::BN);
     slices = pick_slices(tiles, t->d, GT::BK, sm_count);
     g_slices = pick_slices(1, t->d, GT::BK, sm_count);
-    const size_t fixed = (kBlockSteps * kBlockSteps + 2 * m) * sizeof(double) + 5 * m * sizeof(Data);
+    const size_t fixed = (kBlockSteps * kBlockSteps + 2 * m) * sizeof(double) + 5 * m * sizeof(Data) +
+                         static_cast<size_t>((m + 31) / 32 + 2) * sizeof(unsigned);
     const size_t with_s = fixed + static_cast<size_t>(kBlockSteps) * m * sizeof(double);
     s_on_chip = (with_s + 2048 <= info.smem_optin) ? 1 : 0;
     chain_smem = s_on_chip ? with_s : fixed;
@@ -804,7 +832,8 @@ struct BlockRunner {
     fit_pack_kernel<Data><<<static_cast<unsigned>((pack_threads + 63) / 64), 256, 0, s>>>(pk);
     SDCAB_CUDA_TRY(cudaGetLastError());
     ChainArgs c;
-    c.o = o; c.order = ord; c.labels = t->labels; c.S = S; c.G = G; c.A = A; c.D = D; c.t_keep = t_keep;
+    c.o = o; c.order = ord; c.labels = t->labels; c.offsets = t->offsets; c.S = S; c.G = G; c.A = A; c.D = D;
+    c.t_keep = t_keep;
     c.m = m; c.count = count; c.kernel_input = kernel_input ? 1 : 0; c.s_on_chip = s_on_chip;
     fit_chain_kernel<Data, R><<<1, kFitThreads, chain_smem, s>>>(c);
     SDCAB_CUDA_TRY(cudaGetLastError());
@@ -866,7 +895,8 @@ struct BlockRunner {
       SDCAB_CUDA_TRY(cudaGetLastError());
       SDCAB_CUDA_TRY(cudaEventRecord(ev_steps[h], sc));   // block b - 1 has stepped, block b's scores are packed
       ChainArgs c;
-      c.o = o; c.order = ord; c.labels = t->labels; c.S = S; c.G = G2[h]; c.A = A; c.D = nullptr;
+      c.o = o; c.order = ord; c.labels = t->labels; c.offsets = t->offsets; c.S = S; c.G = G2[h]; c.A = A;
+      c.D = nullptr;
       c.t_keep = t_keep; c.m = m; c.count = count; c.kernel_input = 1; c.s_on_chip = s_on_chip;
       fit_chain_kernel<Data, R><<<1, kFitThreads, chain_smem, sc>>>(c);
       SDCAB_CUDA_TRY(cudaGetLastError());
@@ -1036,6 +1066,7 @@ int check_fit_args(const sdcab_objective* obj, const sdcab_problem* t, const sdc
   if (rc) return rc;
   if (!objective_has_update(obj->id)) return SDCAB_ERR_NOT_IMPLEMENTED;
   if (!t->x || !t->a || !t->labels) return SDCAB_ERR_ARG;
+  if (objective_is_multilabel(obj->id) && !t->offsets) return SDCAB_ERR_ARG;
   if (t->input_kind == SDCAB_INPUT_KERNEL) {
     if (t->d != t->n) return SDCAB_ERR_NUM_DIM;
   } else if (t->input_kind == SDCAB_INPUT_FEATURES) {

@@ -571,6 +571,107 @@ SDCAB_D R solve_sum_w_exp(const Row& row, Pred in, R rhs) {
   return t;
 }
 
+template <typename R>
+struct ThrPair { Thr<R> a, b; };
+
+// A view of a single entry (the label's block of a multiclass example).
+template <typename Data>
+struct OneEntryRow {
+  typedef Data data_type;
+  Data x;
+  int index;
+  SDCAB_D int size() const { return 1; }
+  template <typename F>
+  SDCAB_D void for_each(F&& f) const {
+    if (lane_id() == 0) f(x, index);
+  }
+};
+
+// min over two blocks x, y >= 0 with <1,x> + <1,y> = 1 of the entropic objectives
+// of include/sdca/prox/two_entropy.h:94-231: x = W(exp(a - t)) / alpha,
+// y = W(exp(b - t - c)) / alpha with c = alpha / |a|, t the root of
+//   F(t) = sum_i W(exp(a_i - t)) + sum_j W(exp(b_j - t - c)) - alpha.
+// Same course as the reference: two starting guesses (the function taken as an
+// exponential, and as linear), one Householder step from each to bracket the root,
+// a few bisections if they bracket it, then Householder steps kept inside the
+// bracket.  Returns the thresholds of the two blocks (t and t + c; lo 0, hi 1).
+template <typename R, typename RowA, typename RowB>
+SDCAB_D ThrPair<R> thr_two_entropy(const RowA& ra, const RowB& rb, R alpha) {
+  const R num_a = static_cast<R>(ra.size()), num_b = static_cast<R>(rb.size());
+  R max_a = -num<R>::inf(), max_b = -num<R>::inf(), sum_a = 0, sum_b = 0;
+  ra.for_each([&](typename RowA::data_type xd, int) { const R x = static_cast<R>(xd); max_a = max_(max_a, x); sum_a += x; });
+  rb.for_each([&](typename RowB::data_type xd, int) { const R x = static_cast<R>(xd); max_b = max_(max_b, x); sum_b += x; });
+  max_a = warp_max(max_a); max_b = warp_max(max_b);
+  sum_a = warp_sum(sum_a); sum_b = warp_sum(sum_b);
+  const R c = alpha / num_a;
+  const R mx = max_(max_a, max_b - c);
+  const R eps = num<R>::eps();
+  auto all = [](R, int) { return true; };
+  // F(t) (without the derivatives)
+  auto value = [&](R t) {
+    R f0, f1, f2, f3, g0, g1, g2, g3;
+    row_sum_w_exp<R>(ra, all, t, 1, f0, f1, f2, f3);
+    row_sum_w_exp<R>(rb, all, t + c, 1, g0, g1, g2, g3);
+    return f0 + g0 - alpha;
+  };
+  // one Householder step of order four at t; returns F(t) (two_entropy.h:12-37)
+  auto step = [&](R& t) {
+    R f0, f1, f2, f3, g0, g1, g2, g3;
+    row_sum_w_exp<R>(ra, all, t, 3, f0, f1, f2, f3);
+    row_sum_w_exp<R>(rb, all, t + c, 3, g0, g1, g2, g3);
+    f0 += g0; f1 += g1; f2 += g2; f3 += g3;
+    f0 -= alpha;
+    const R f02 = f0 * f2, f11 = f1 * f1;
+    const R D = 6 * f1 * (f02 - f11) - f0 * (f0 * f3);
+    if (abs_(D) > 64 * num<R>::tiny()) t -= 3 * f0 * (2 * f11 - f02) / D;
+    return f0;
+  };
+  R lb = -num<R>::max(), ub = mx - 64 * num<R>::exp_min_arg();
+  R lf = num<R>::max(), uf = -num<R>::max();
+  R t01 = mx - log_(alpha), t1 = t01;
+  R f1v = step(t1);
+  R t02 = (sum_a + sum_b - num_b * c - alpha) / (num_a + num_b), t2 = t02;
+  R f2v = step(t2);
+  if (f1v > f2v) {
+    R tmp = t01; t01 = t02; t02 = tmp;
+    tmp = t1; t1 = t2; t2 = tmp;
+    tmp = f1v; f1v = f2v; f2v = tmp;
+  }
+  R t;
+  if (f1v > 0) {
+    lb = t01; lf = f1v; t = t1;
+  } else if (f2v < 0) {
+    ub = t02; uf = f2v; t = t2;
+  } else {
+    lb = t02; ub = t01; lf = f2v; uf = f1v;
+    t = max_(lb, min_(abs_(f1v) < abs_(f2v) ? t1 : t2, ub));
+    // a few bisections to improve the guess (two_entropy.h:63-91,198-203)
+    const R width = log_(ub - lb) * R(1.4426950408889634);
+    int num_iter = 0;
+    if (width > 0) num_iter = width < R(32) ? static_cast<int>(width) : 32;
+    for (int iter = 0; iter < num_iter; ++iter) {
+      t = (lb + ub) / 2;
+      const R fm = value(t);
+      if (eps < fm && fm < lf) { lf = fm; lb = t; }
+      else if (uf < fm && fm < -eps) { uf = fm; ub = t; }
+      else break;
+    }
+    t = (lb + ub) / 2;
+  }
+  for (int iter = 0; iter < 32; ++iter) {
+    const R tb = t;
+    const R fv = step(t);
+    if (0 <= fv && fv < lf) { lb = tb; lf = fv; }
+    else if (uf < fv && fv <= 0) { ub = tb; uf = fv; }
+    t = max_(lb, min_(t, ub));
+    if (abs_(tb - t) <= eps) break;
+  }
+  ThrPair<R> out;
+  out.a = make_thr(t, R(0), R(1), 0, ra.size(), num<R>::inf(), -num<R>::inf());
+  out.b = make_thr(t + c, R(0), R(1), 0, rb.size(), num<R>::inf(), -num<R>::inf());
+  return out;
+}
+
 // min 0.5<x,x> + <x,log x> - <a,x>,  <1,x> = rhs,  0 <= x <= hi;
 // x = min(W(exp(a - t)), hi)        (include/sdca/prox/entropy_norm.h:146-181)
 template <typename R, typename Row>
@@ -706,8 +807,7 @@ SDCAB_D Thr<R> thr_topk_entropy_biased(const Row& row, int k, R alpha) {
 // ---- bipartite simplex ------------------------------------------------------
 // min ||x-a||^2 + ||y-b||^2,  <1,x> = <1,y> <= rhs,  x, y >= 0
 // (include/sdca/prox/two_simplex.h:18-119).  Returns the pair (t for a, s for b).
-template <typename R>
-struct ThrPair { Thr<R> a, b; };
+
 
 template <typename R, typename Row>
 SDCAB_D void simplex_phase1(const Row& row, R rhs, R& t, int& n_active, R& cut) {

@@ -49,9 +49,102 @@ SDCAB_HD double add_rn_(double a, double b) {
 }
 template <typename T> SDCAB_HD T sub_rn_(T a, T b) { return add_rn_(a, -b); }
 
-SDCAB_HD bool objective_has_update(int id) {
-  return id == kObjL2HingeTopk || id == kObjL2HingeTopkSmooth || id == kObjL2TopkHinge ||
-         id == kObjL2TopkHingeSmooth || id == kObjL2EntropyTopk;
+SDCAB_HD bool objective_has_update(int id) { return id >= 0 && id < kNumObjectives; }
+
+// Softmax and multilabel softmax (include/sdca/solver/objective/l2_entropy.h:47-74,
+// l2_multilabel_entropy.h:42-69): v = scores - norm2 * a, the labels' block and the
+// others' block are projected together by prox_two_entropy with alpha = c * norm2;
+// a_label = -c x + c / (number of labels), a_other = -c x.  RowP / RowN view the two
+// blocks of v; `is_label(j)` tells them apart when the new variables are written.
+template <typename R, typename Data, typename RowP, typename RowN, typename IsLabel>
+SDCAB_D void finish_entropy_update(const ObjectiveParams& o, Data norm2, const RowP& pos,
+                                   const RowN& neg, int num_labels, const Data* v, Data* a, int m,
+                                   IsLabel is_label) {
+  const R c = static_cast<R>(o.c);
+  const R alpha = c * static_cast<R>(norm2);
+  const ThrPair<R> thr = thr_two_entropy<R>(pos, neg, alpha);
+  Applier<Data> fp(thr.a, kMapScaledLambert, static_cast<double>(alpha));
+  Applier<Data> fn(thr.b, kMapScaledLambert, static_cast<double>(alpha));
+  const Data minus_c = static_cast<Data>(-c);
+  const Data share = static_cast<Data>(c / static_cast<R>(num_labels));
+  for (int j = lane_id(); j < m; j += kLanes) {
+    a[j] = is_label(j) ? add_rn_(mul_rn_(minus_c, fp(v[j])), share) : mul_rn_(minus_c, fn(v[j]));
+  }
+#if defined(__CUDA_ARCH__)
+  __syncwarp();
+#endif
+}
+
+template <typename R, typename Data>
+SDCAB_D void update_dual_variables_multilabel_entropy(const ObjectiveParams& o, Data norm2,
+                                                      const Data* scores, Data* a, Data* v, int m,
+                                                      const unsigned* mask, int num_labels) {
+  for (int j = lane_id(); j < m; j += kLanes) v[j] = add_rn_(mul_rn_(-norm2, a[j]), scores[j]);
+#if defined(__CUDA_ARCH__)
+  __syncwarp();
+#endif
+  MaskedRow<Data> pos, neg;
+  pos.p = v; pos.mask = mask; pos.m = m; pos.count = num_labels; pos.want = true;
+  pos.sign = Data(1); pos.shift = Data(0);
+  neg = pos; neg.count = m - num_labels; neg.want = false;
+  finish_entropy_update<R, Data>(o, norm2, pos, neg, num_labels, v, a, m,
+                                 [&](int j) { return ((mask[j >> 5] >> (j & 31)) & 1u) != 0; });
+}
+
+template <typename R, typename Data>
+SDCAB_D void update_dual_variables_entropy(const ObjectiveParams& o, Data norm2, const Data* scores,
+                                           Data* a, Data* v, int m, int y) {
+  for (int j = lane_id(); j < m; j += kLanes) v[j] = add_rn_(mul_rn_(-norm2, a[j]), scores[j]);
+#if defined(__CUDA_ARCH__)
+  __syncwarp();
+#endif
+  OneEntryRow<Data> pos;
+  pos.x = v[y]; pos.index = y;
+  ShiftedRow<Data> neg(v, m, y, Data(0));
+  finish_entropy_update<R, Data>(o, norm2, pos, neg, 1, v, a, m, [&](int j) { return j == y; });
+}
+
+// Multilabel hinge, smooth or not (include/sdca/solver/objective/l2_multilabel_hinge.h:39-66,
+// 136-165): v = alpha * scores - beta * a; the labels' entries become alpha/2 - v, the others
+// alpha/2 + v; both blocks are projected together by prox_two_simplex with radius c; the
+// labels keep the projection, the others its negative.  `mask` has bit j set for the labels.
+template <typename R, typename Data>
+SDCAB_D void update_dual_variables_multilabel_entropy(const ObjectiveParams& o, Data norm2,
+                                                      const Data* scores, Data* a, Data* v, int m,
+                                                      const unsigned* mask, int num_labels);
+
+template <typename R, typename Data>
+SDCAB_D void update_dual_variables_multilabel_hinge(const ObjectiveParams& o, Data norm2,
+                                                    const Data* scores, Data* a, Data* v, int m,
+                                                    const unsigned* mask, int num_labels) {
+  if (o.id == kObjL2MultilabelEntropy) {
+    update_dual_variables_multilabel_entropy<R, Data>(o, norm2, scores, a, v, m, mask, num_labels);
+    return;
+  }
+  const R c = static_cast<R>(o.c);
+  const bool smooth = (o.id == kObjL2MultilabelHingeSmooth);
+  const R denom = static_cast<R>(norm2) + static_cast<R>(o.gamma) / c;
+  const Data alpha = smooth ? static_cast<Data>(R(1) / denom) : Data(1) / norm2;
+  const Data beta = smooth ? static_cast<Data>(static_cast<R>(norm2) / denom) : Data(1);
+  for (int j = lane_id(); j < m; j += kLanes) v[j] = add_rn_(mul_rn_(-beta, a[j]), mul_rn_(alpha, scores[j]));
+#if defined(__CUDA_ARCH__)
+  __syncwarp();
+#endif
+  const Data half = alpha / 2;
+  MaskedRow<Data> pos, neg;
+  pos.p = v; pos.mask = mask; pos.m = m; pos.count = num_labels; pos.want = true;
+  pos.sign = Data(-1); pos.shift = half;
+  neg.p = v; neg.mask = mask; neg.m = m; neg.count = m - num_labels; neg.want = false;
+  neg.sign = Data(1); neg.shift = half;
+  const ThrPair<R> thr = thr_two_simplex<R>(pos, neg, c);
+  Applier<Data> fp(thr.a, kMapIdentity, 1.0), fn(thr.b, kMapIdentity, 1.0);
+  for (int j = lane_id(); j < m; j += kLanes) {
+    const bool label = (mask[j >> 5] >> (j & 31)) & 1u;
+    a[j] = label ? fp(static_cast<Data>(half - v[j])) : -fn(static_cast<Data>(half + v[j]));
+  }
+#if defined(__CUDA_ARCH__)
+  __syncwarp();
+#endif
 }
 
 // l2_entropy_topk.h:46-71: v = scores - norm2 * a, v_j -= v_y, x = prox_topk_entropy_biased(v, k,
@@ -100,6 +193,10 @@ SDCAB_D void update_dual_variables_multiclass(const ObjectiveParams& o, Data nor
                                               const Data* scores, Data* a, Data* v, int m, int y) {
   if (o.id == kObjL2EntropyTopk) {
     update_dual_variables_entropy_topk<R, Data>(o, norm2, scores, a, v, m, y);
+    return;
+  }
+  if (o.id == kObjL2Entropy) {
+    update_dual_variables_entropy<R, Data>(o, norm2, scores, a, v, m, y);
     return;
   }
   const R c = static_cast<R>(o.c);

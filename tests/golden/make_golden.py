@@ -22,7 +22,7 @@ from tests.test_oracle_restatement import OBJECTIVES, random_problem  # noqa: E4
 
 
 HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth",
-         "l2_entropy_topk")
+         "l2_entropy_topk", "l2_entropy")
 
 
 def make_fit(ref):
@@ -31,22 +31,24 @@ def make_fit(ref):
     rng = np.random.default_rng(20240919)
     out = {}
     idx = 0
-    for objective in HINGE:
+    for objective in HINGE + ("l2_multilabel_hinge", "l2_multilabel_hinge_smooth", "l2_multilabel_entropy"):
+        ml = refapi.OBJECTIVES[objective] in refapi.MULTILABEL
         for dtype in (np.float32, np.float64):
             for kernel in (False, True):
                 n, d, m = 48, 6, 5
-                X, labels, _ = random_problem(rng, n, d, m, dtype, False)
+                X, labels, offsets = random_problem(rng, n, d, m, dtype, ml)
                 data = (X.astype(np.float64) @ X.astype(np.float64).T).astype(dtype) if kernel else X
                 A = np.zeros((n, m), dtype=dtype); W = np.zeros((m, d), dtype=dtype)
                 kw = dict(c=0.8, gamma=0.6, k=2)
                 r = ref.fit(objective, data, A, labels, W=None if kernel else W, kernel=kernel,
-                            epsilon=1e-3, max_epoch=25, eval_epoch=2, **kw)
+                            offsets=offsets, epsilon=1e-3, max_epoch=25, eval_epoch=2, **kw)
                 key = "fit%03d" % idx
                 idx += 1
                 out[key + "_objective"] = np.array(objective)
                 out[key + "_kernel"] = np.array(kernel)
                 out[key + "_data"] = data
                 out[key + "_labels"] = labels
+                out[key + "_offsets"] = offsets if offsets is not None else np.zeros(0, dtype=np.int64)
                 out[key + "_params"] = np.array([kw["c"], kw["gamma"], kw["k"], 1e-3, 25, 2])
                 out[key + "_A"] = A
                 out[key + "_W"] = W

@@ -36,7 +36,9 @@ def fit_cases():
     keys = sorted({k.split("_")[0] for k in z.files if k.startswith("fit")})
     for key in keys:
         prm = z[key + "_params"]
+        offsets = z[key + "_offsets"]
         yield dict(objective=str(z[key + "_objective"]), kernel=bool(z[key + "_kernel"]),
+                   offsets=offsets if len(offsets) else None,
                    data=z[key + "_data"], labels=z[key + "_labels"], c=float(prm[0]),
                    gamma=float(prm[1]), k=int(prm[2]), epsilon=float(prm[3]), max_epoch=int(prm[4]),
                    eval_epoch=int(prm[5]), A=z[key + "_A"], W=z[key + "_W"],

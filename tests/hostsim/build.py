@@ -60,12 +60,12 @@ class HostSim:
 
     def fit(self, objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
             precision="double", epsilon=1e-3, max_epoch=100, eval_epoch=1, eval_on_start=False,
-            permutations=None):
+            permutations=None, offsets=None):
         """Runs the fit in place on A (and W); returns status, epoch and the records."""
         from libsdca_b200 import binding as b
         obj = b.make_objective(objective, c, gamma, k, precision,
                                from_name=self.lib.sdcab_hostsim_objective_from_name)
-        prob = b.make_problem(X, labels, A, W, None, None, kernel, True)
+        prob = b.make_problem(X, labels, A, W, None, offsets, kernel, True)
         crit = b.FitCriteria(epsilon, max_epoch, eval_epoch, 1 if eval_on_start else 0, 0)
         cap = max_epoch + 4
         evals = (b.EvalRecord * cap)()

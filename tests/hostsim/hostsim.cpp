@@ -218,7 +218,15 @@ int run_fit(const sdcab_objective* obj, const sdcab_problem* p, const sdcab_fit_
       }
       Data* a = A + i * m;
       for (int j = 0; j < m; ++j) old[j] = a[j];
-      update_dual_variables_multiclass<R, Data>(q, norm2, s.data(), a, v.data(), m, (int)p->labels[i]);
+      if (objective_is_multilabel(q.id)) {
+        const long long off = p->offsets[i];
+        const int nl = static_cast<int>(p->offsets[i + 1] - off);
+        std::vector<unsigned> mask((m + 31) / 32, 0u);
+        for (int g = 0; g < nl; ++g) mask[p->labels[off + g] >> 5] |= 1u << (p->labels[off + g] & 31);
+        update_dual_variables_multilabel_hinge<R, Data>(q, norm2, s.data(), a, v.data(), m, mask.data(), nl);
+      } else {
+        update_dual_variables_multiclass<R, Data>(q, norm2, s.data(), a, v.data(), m, (int)p->labels[i]);
+      }
       if (!kernel) {
         Data asum = 0;
         for (int j = 0; j < m; ++j) { old[j] -= a[j]; asum += abs_(old[j]); }

@@ -11,7 +11,7 @@ from tests.util import stable_seed
 pytestmark = pytest.mark.gpu
 
 HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth",
-         "l2_entropy_topk")
+         "l2_entropy_topk", "l2_entropy")
 REF_STATUS = ("none", "solving", "solved", "no_progress", "max_epoch", "max_cpu_time",
               "max_wall_time", "failed")
 
@@ -72,6 +72,28 @@ def test_feature_fit_matches_reference(ref, cuda_lib, objective, dtype):
         compare(*out, tol, (objective, n, d, m, k))
 
 
+@pytest.mark.parametrize("objective", ["l2_multilabel_hinge", "l2_multilabel_hinge_smooth",
+                                       "l2_multilabel_entropy"])
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+@pytest.mark.parametrize("kernel", [False, True])
+def test_multilabel_fit_matches_reference(ref, cuda_lib, objective, dtype, kernel):
+    from oracle.refapi import OBJECTIVES as IDS
+    rng = np.random.default_rng(stable_seed("gpu-fit-multilabel", objective, str(dtype), kernel))
+    tol = 1e-9 if dtype == np.float64 else 2e-4
+    for n, d, m in ((70, 6, 7), (500, 40, 45)):
+        X, labels, offsets = random_problem(rng, n, d, m, dtype, True)
+        data = (X.astype(np.float64) @ X.astype(np.float64).T).astype(dtype) if kernel else X
+        kw = dict(c=0.9, gamma=0.7, k=1, epsilon=1e-3, max_epoch=12, eval_epoch=2)
+        A_ref = np.zeros((n, m), dtype=dtype); W_ref = np.zeros((m, d), dtype=dtype)
+        r = ref.fit(objective, data, A_ref, labels, W=None if kernel else W_ref, kernel=kernel,
+                    offsets=offsets, **kw)
+        A = dev(np.zeros((n, m), dtype=dtype)); W = None if kernel else dev(np.zeros((m, d), dtype=dtype))
+        g = cuda_lib.fit_(IDS[objective], dev(data), dev(labels), A, W=W, kernel=kernel,
+                          offsets=dev(offsets), **kw)
+        compare(r, g, A_ref, W_ref, A.cpu().numpy(), None if kernel else W.cpu().numpy(), tol,
+                (objective, n, m, kernel))
+
+
 def test_crammer_singer_medium(ref, cuda_lib):
     """The shape of the full-size problem at a size the CPU solver finishes quickly:
     RBF kernel of Gaussian blobs, msvm (top-k hinge beta, k = 1), gap checked every epoch."""
@@ -123,7 +145,7 @@ def test_rejects_what_it_cannot_fit(cuda_lib):
     K, labels = kernel_problem(n=50, dim=4, m=4, seed=3)
     A = dev(np.zeros((50, 4)))
     with pytest.raises(SdcabError):
-        cuda_lib.fit_(0, dev(K), dev(labels), A, kernel=True)   # l2_entropy: its step needs prox_two_entropy
+        cuda_lib.fit_(6, dev(K), dev(labels), A, kernel=True)   # multilabel objective without offsets
     with pytest.raises(SdcabError):
         cuda_lib.fit_(4, dev(K[:, :40].copy()), dev(labels), A, kernel=True)  # kernel not square
 
@@ -137,7 +159,8 @@ def test_golden_fits(cuda_lib):
         A = dev(np.zeros_like(c["A"])); W = None if c["kernel"] else dev(np.zeros_like(c["W"]))
         r = cuda_lib.fit_(IDS[c["objective"]], dev(c["data"]), dev(c["labels"]), A, W=W,
                           kernel=c["kernel"], c=c["c"], gamma=c["gamma"], k=c["k"],
-                          epsilon=c["epsilon"], max_epoch=c["max_epoch"], eval_epoch=c["eval_epoch"])
+                          epsilon=c["epsilon"], max_epoch=c["max_epoch"], eval_epoch=c["eval_epoch"],
+                          offsets=dev(c["offsets"]))
         golden_check(c, r, A.cpu().numpy(), None if c["kernel"] else W.cpu().numpy())
     big, small = epoch_orders()
     assert np.array_equal(cuda_lib.epoch_permutations(50000, 2)[:, :64], big)

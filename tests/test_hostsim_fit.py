@@ -9,7 +9,7 @@ from tests.test_oracle_restatement import random_problem
 from tests.util import stable_seed
 
 HINGE = ("l2_hinge_topk", "l2_hinge_topk_smooth", "l2_topk_hinge", "l2_topk_hinge_smooth",
-         "l2_entropy_topk")
+         "l2_entropy_topk", "l2_entropy")
 REF_STATUS = ("none", "solving", "solved", "no_progress", "max_epoch", "max_cpu_time",
               "max_wall_time", "failed")
 
@@ -64,6 +64,33 @@ def test_feature_fit_matches_reference(ref, hostsim, objective, dtype):
               max_epoch=12, eval_epoch=3)
 
 
+@pytest.mark.parametrize("objective", ["l2_multilabel_hinge", "l2_multilabel_hinge_smooth",
+                                       "l2_multilabel_entropy"])
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+@pytest.mark.parametrize("kernel", [False, True])
+def test_multilabel_fit_matches_reference(ref, hostsim, objective, dtype, kernel):
+    from oracle.refapi import OBJECTIVES as IDS
+    rng = np.random.default_rng(stable_seed("fit-multilabel", objective, str(dtype), kernel))
+    n, d, m = 70, 6, 7
+    X, labels, offsets = random_problem(rng, n, d, m, dtype, True)
+    data = (X.astype(np.float64) @ X.astype(np.float64).T).astype(dtype) if kernel else X
+    tol = 1e-9 if dtype == np.float64 else 2e-4
+    kw = dict(c=0.9, gamma=0.7, k=1, epsilon=1e-3, max_epoch=15, eval_epoch=2)
+    A_ref = np.zeros((n, m), dtype=dtype); W_ref = np.zeros((m, d), dtype=dtype)
+    A = np.zeros((n, m), dtype=dtype); W = np.zeros((m, d), dtype=dtype)
+    r = ref.fit(objective, data, A_ref, labels, W=None if kernel else W_ref, kernel=kernel,
+                offsets=offsets, **kw)
+    h = hostsim.fit(IDS[objective], data, labels, A, W=None if kernel else W, kernel=kernel,
+                    offsets=offsets, **kw)
+    assert h["status"] == REF_STATUS[r["status"]] and h["epoch"] == r["epoch"]
+    assert h["num_evals"] == len(r["history"])
+    assert np.abs(A - A_ref).max() <= tol * max(1.0, np.abs(A_ref).max())
+    if not kernel:
+        assert np.abs(W - W_ref).max() <= tol * max(1.0, np.abs(W_ref).max()) * d
+    for i, f in enumerate(("primal", "dual")):
+        assert abs(h["history"][-1][f] - r["history"][-1][i]) <= 10 * tol * max(1.0, abs(r["history"][-1][i]))
+
+
 def test_stopping_paths(ref, hostsim):
     K, labels = kernel_problem(n=60, dim=4, m=4, seed=3)
     # evaluation before the first epoch, epoch limit reached, and no evaluation until the end
@@ -99,10 +126,10 @@ def test_golden_fits(hostsim):
         A = np.zeros_like(c["A"]); W = np.zeros_like(c["W"])
         r = hostsim.fit(IDS[c["objective"]], c["data"], c["labels"], A, W=None if c["kernel"] else W,
                         kernel=c["kernel"], c=c["c"], gamma=c["gamma"], k=c["k"], epsilon=c["epsilon"],
-                        max_epoch=c["max_epoch"], eval_epoch=c["eval_epoch"])
+                        max_epoch=c["max_epoch"], eval_epoch=c["eval_epoch"], offsets=c["offsets"])
         golden_check(c, r, A, W)
         count += 1
-    assert count == 20
+    assert count == 36
 
 
 def test_golden_epoch_orders(hostsim):
