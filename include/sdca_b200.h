@@ -350,6 +350,20 @@ int sdcab_fit_f64_dev(const sdcab_objective* obj, const sdcab_problem* train,
                       sdcab_eval_record* evals, int64_t evals_cap,
                       sdcab_fit_result* result, void* stream);
 
+/* The same fit with host buffers on the current device: the problem is copied to
+ * the device, a (and w for features) are read as the starting point and receive
+ * the result -- what matsdca_fit does with its model struct
+ * (src/matlab/mex_solve.cpp:780-800 and the make_context_* / solve_objective
+ * helpers above it).  Labels and offsets are checked as in
+ * include/sdca/solver/data/output.h:169-215 (SDCAB_ERR_LABELS_RANGE; labels are
+ * 0-based here).  Synchronous. */
+int sdcab_fit_f32(const sdcab_objective* obj, const sdcab_problem* host_train,
+                  const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                  sdcab_eval_record* evals, int64_t evals_cap, sdcab_fit_result* result);
+int sdcab_fit_f64(const sdcab_objective* obj, const sdcab_problem* host_train,
+                  const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                  sdcab_eval_record* evals, int64_t evals_cap, sdcab_fit_result* result);
+
 /* ------------------------------------------------------------- memory ---- */
 
 /* Page-locked host memory for callers that want the host-buffer entry points

@@ -153,6 +153,26 @@ inline sdcab_eval_record evaluate_dataset(const sdcab_objective& objective, cons
   return rec;
 }
 
+// solver::solve (include/sdca/solver.h:39-52) on host buffers: runs epochs of
+// SDCA steps until the reference's stopping rule ends them; `problem.a` (and
+// `problem.w` for features) hold the starting point and receive the result.
+// Returns status / epoch count; `evals` receives one record per evaluation.
+template <typename Data>
+inline sdcab_fit_result solve(const sdcab_objective& objective, const sdcab_problem& problem,
+                              const sdcab_fit_criteria& criteria,
+                              std::vector<sdcab_eval_record>* evals = nullptr) {
+  sdcab_fit_result res;
+  std::vector<sdcab_eval_record> local(static_cast<std::size_t>(criteria.max_epoch) + 4);
+  const int rc = std::is_same<Data, float>::value
+      ? sdcab_fit_f32(&objective, &problem, &criteria, nullptr, local.data(),
+                      static_cast<int64_t>(local.size()), &res)
+      : sdcab_fit_f64(&objective, &problem, &criteria, nullptr, local.data(),
+                      static_cast<int64_t>(local.size()), &res);
+  check(rc, "solve");
+  if (evals) evals->assign(local.begin(), local.begin() + static_cast<std::ptrdiff_t>(res.num_evals));
+  return res;
+}
+
 }  // namespace b200
 }  // namespace sdca
 

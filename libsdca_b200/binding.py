@@ -332,7 +332,8 @@ def epoch_permutations(n, num_epochs):
 def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
          precision="double", epsilon=1e-3, max_epoch=1000, eval_epoch=10, eval_on_start=False,
          permutations=None, offsets=None):
-    """SDCA fit on torch CUDA tensors, in place on ``A`` (n x m) and ``W`` (m x d).
+    """SDCA fit, in place on ``A`` (n x m) and ``W`` (m x d): torch CUDA tensors use the
+    device entry point, numpy arrays the host-buffer one (copies inside).
 
     Mirrors ``matsdca_fit``'s stopping options (src/matlab/mex_solve.cpp:505-528 of the
     reference); returns status, epochs and the evaluation records."""
@@ -347,8 +348,13 @@ def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
         perm = np.ascontiguousarray(permutations, dtype=np.int64)
         if perm.size < max_epoch * X.shape[0]:
             raise SdcabError(-1, "fit_: permutations must hold max_epoch * n indices")
-    fn = getattr(lib(), "sdcab_fit_%s_dev" % _suffix(str(X.dtype)))
-    _check(fn(C.byref(obj), C.byref(prob), C.byref(crit),
-              perm.ctypes.data_as(C.c_void_p) if perm is not None else None, evals,
-              C.c_int64(cap), C.byref(res), _torch_stream()), "sdcab_fit_dev")
+    perm_ptr = perm.ctypes.data_as(C.c_void_p) if perm is not None else None
+    if _is_torch(X):
+        fn = getattr(lib(), "sdcab_fit_%s_dev" % _suffix(str(X.dtype)))
+        _check(fn(C.byref(obj), C.byref(prob), C.byref(crit), perm_ptr, evals, C.c_int64(cap),
+                  C.byref(res), _torch_stream()), "sdcab_fit_dev")
+    else:
+        fn = getattr(lib(), "sdcab_fit_%s" % _suffix(X.dtype.name))
+        _check(fn(C.byref(obj), C.byref(prob), C.byref(crit), perm_ptr, evals, C.c_int64(cap),
+                  C.byref(res)), "sdcab_fit")
     return fit_result_to_dict(res, evals)

@@ -1090,6 +1090,57 @@ int fit_entry(const sdcab_objective* obj, const sdcab_problem* t, const sdcab_fi
   return fit_dev<Data, double>(obj, t, c, perm, evals, cap, res, s);
 }
 
+// Host buffers: copy the problem to the device, fit, copy the variables back.
+template <typename Data>
+int fit_host(const sdcab_objective* obj, const sdcab_problem* hp, const sdcab_fit_criteria* c,
+             const int64_t* perm, sdcab_eval_record* evals, int64_t cap, sdcab_fit_result* res) {
+  int rc = check_fit_args(obj, hp, c);
+  if (rc) return rc;
+  const long long n = hp->n, m = hp->m, d = hp->d;
+  const bool kernel = (hp->input_kind == SDCAB_INPUT_KERNEL);
+  const bool ml = objective_is_multilabel(obj->id);
+  const long long num_labels = ml ? hp->offsets[n] : n;
+  // the label checks of include/sdca/solver/data/output.h:169-215 (labels here are 0-based)
+  for (long long i = 0; i < num_labels; ++i)
+    if (hp->labels[i] < 0 || hp->labels[i] >= m) return SDCAB_ERR_LABELS_RANGE;
+  if (ml) {
+    if (hp->offsets[0] != 0) return SDCAB_ERR_LABELS_RANGE;
+    for (long long i = 0; i < n; ++i) {
+      const long long count = hp->offsets[i + 1] - hp->offsets[i];
+      if (count < 1 || count >= m) return SDCAB_ERR_LABELS_RANGE;
+    }
+  }
+  DeviceBuffers buf;
+  Data *dX = nullptr, *dA = nullptr, *dW = nullptr;
+  int64_t *dLab = nullptr, *dOff = nullptr;
+  const size_t x_elems = static_cast<size_t>(n) * d, a_elems = static_cast<size_t>(n) * m,
+               w_elems = static_cast<size_t>(d) * m;
+  rc = buf.alloc(&dX, x_elems); if (rc) return rc;
+  rc = buf.alloc(&dA, a_elems); if (rc) return rc;
+  rc = buf.alloc(&dLab, static_cast<size_t>(num_labels)); if (rc) return rc;
+  SDCAB_CUDA_TRY(cudaMemcpy(dX, hp->x, x_elems * sizeof(Data), cudaMemcpyHostToDevice));
+  SDCAB_CUDA_TRY(cudaMemcpy(dA, hp->a, a_elems * sizeof(Data), cudaMemcpyHostToDevice));
+  SDCAB_CUDA_TRY(cudaMemcpy(dLab, hp->labels, static_cast<size_t>(num_labels) * sizeof(int64_t),
+                            cudaMemcpyHostToDevice));
+  if (!kernel) {
+    rc = buf.alloc(&dW, w_elems); if (rc) return rc;
+    SDCAB_CUDA_TRY(cudaMemcpy(dW, hp->w, w_elems * sizeof(Data), cudaMemcpyHostToDevice));
+  }
+  if (ml) {
+    rc = buf.alloc(&dOff, static_cast<size_t>(n + 1)); if (rc) return rc;
+    SDCAB_CUDA_TRY(cudaMemcpy(dOff, hp->offsets, static_cast<size_t>(n + 1) * sizeof(int64_t),
+                              cudaMemcpyHostToDevice));
+  }
+  sdcab_problem dp = *hp;
+  dp.x = dX; dp.a = dA; dp.w = dW; dp.w0 = nullptr; dp.labels = dLab; dp.offsets = dOff;
+  rc = fit_entry<Data>(obj, &dp, c, perm, evals, cap, res, nullptr);
+  if (rc) return rc;
+  SDCAB_CUDA_TRY(cudaMemcpy(const_cast<void*>(hp->a), dA, a_elems * sizeof(Data), cudaMemcpyDeviceToHost));
+  if (!kernel)
+    SDCAB_CUDA_TRY(cudaMemcpy(const_cast<void*>(hp->w), dW, w_elems * sizeof(Data), cudaMemcpyDeviceToHost));
+  return SDCAB_OK;
+}
+
 }  // namespace
 }  // namespace sdcab
 
@@ -1124,6 +1175,18 @@ int sdcab_fit_f64_dev(const sdcab_objective* obj, const sdcab_problem* train,
                       sdcab_eval_record* evals, int64_t evals_cap, sdcab_fit_result* result,
                       void* stream) {
   return sdcab::fit_entry<double>(obj, train, criteria, permutations, evals, evals_cap, result, stream);
+}
+
+int sdcab_fit_f32(const sdcab_objective* obj, const sdcab_problem* host_train,
+                  const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                  sdcab_eval_record* evals, int64_t evals_cap, sdcab_fit_result* result) {
+  return sdcab::fit_host<float>(obj, host_train, criteria, permutations, evals, evals_cap, result);
+}
+
+int sdcab_fit_f64(const sdcab_objective* obj, const sdcab_problem* host_train,
+                  const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                  sdcab_eval_record* evals, int64_t evals_cap, sdcab_fit_result* result) {
+  return sdcab::fit_host<double>(obj, host_train, criteria, permutations, evals, evals_cap, result);
 }
 
 }  // extern "C"

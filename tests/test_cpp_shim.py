@@ -23,6 +23,10 @@ int main(int argc, char**) {
     sdcab_objective o; sdcab_objective_from_name("msvm_smooth", 1.0, 1.0, 1, &o);
     sdcab_problem p = sdcab_problem();
     sdca::b200::evaluate_dataset<float>(o, p);
+    sdcab_fit_criteria c = {1e-3, 100, 10, 0, 0};
+    std::vector<sdcab_eval_record> evals;
+    sdcab_fit_result r = sdca::b200::solve<double>(o, p, c, &evals);
+    (void)r;
   }
   return 0;
 }

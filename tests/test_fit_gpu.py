@@ -165,3 +165,23 @@ def test_golden_fits(cuda_lib):
     big, small = epoch_orders()
     assert np.array_equal(cuda_lib.epoch_permutations(50000, 2)[:, :64], big)
     assert np.array_equal(cuda_lib.epoch_permutations(1000, 3), small)
+
+
+def test_host_buffer_fit(ref, cuda_lib):
+    """sdcab_fit_f64 / _f32: numpy in, numpy out, copies inside."""
+    from libsdca_b200.binding import SdcabError
+    for dtype, tol in ((np.float64, 1e-9), (np.float32, 2e-4)):
+        K, labels = kernel_problem(n=300, dim=8, m=12, seed=21, dtype=dtype)
+        A_ref = np.zeros((300, 12), dtype=dtype); A = np.zeros((300, 12), dtype=dtype)
+        r = ref.fit("l2_topk_hinge", K, A_ref, labels, kernel=True, c=1.0, k=2, max_epoch=10, eval_epoch=1)
+        g = cuda_lib.fit_(4, K, labels, A, kernel=True, c=1.0, k=2, max_epoch=10, eval_epoch=1)
+        compare(r, g, A_ref, None, A, None, tol, "host buffers, kernel")
+    rng = np.random.default_rng(5)
+    X, labels, _ = random_problem(rng, 200, 9, 6, np.float64, False)
+    A_ref = np.zeros((200, 6)); W_ref = np.zeros((6, 9)); A = np.zeros((200, 6)); W = np.zeros((6, 9))
+    r = ref.fit("l2_entropy", X, A_ref, labels, W=W_ref, c=1.0, max_epoch=6, eval_epoch=2)
+    g = cuda_lib.fit_(0, X, labels, A, W=W, c=1.0, max_epoch=6, eval_epoch=2)
+    compare(r, g, A_ref, W_ref, A, W, 1e-9, "host buffers, features")
+    bad = labels.copy(); bad[3] = 6
+    with pytest.raises(SdcabError):
+        cuda_lib.fit_(0, X, bad, A, W=W, c=1.0, max_epoch=1)
