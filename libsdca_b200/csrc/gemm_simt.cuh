@@ -51,7 +51,19 @@ __device__ __forceinline__ void load_kmajor_tile(const T* __restrict__ base, lon
   }
 }
 
-template <typename T, int BM, int BN, int BK, int TM, int TN, bool B_KMAJOR>
+// FP64 tensor-core product of one 8x4 by 4x8 pair of fragments into an 8x8
+// accumulator (mma.sync m8n8k4): lane l holds A[l / 4][l % 4], B[l % 4][l / 4] and
+// the accumulator entries [l / 4][2 (l % 4)], [l / 4][2 (l % 4) + 1].
+__device__ __forceinline__ void mma_f64(double& c0, double& c1, double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+               : "+d"(c0), "+d"(c1) : "d"(a), "d"(b));
+}
+
+// MMA (double only): the tile product runs on the FP64 tensor cores.  Warps tile
+// the block in 32x32 pieces (4x4 fragments each), so the thread count is
+// BM * BN / 32 and TM * TN must be 32; everything around the product -- loads,
+// gathers, slices, masks, edges -- is shared with the FMA form.
+template <typename T, int BM, int BN, int BK, int TM, int TN, bool B_KMAJOR, bool MMA = false>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int M, int N,
             int K, long long lda, long long ldb, long long ldc, int a_vec, int b_vec, int c_vec,
@@ -60,7 +72,11 @@ gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
             int skip_owner) {
   constexpr int NT = (BM / TM) * (BN / TN);
   constexpr int V = 16 / sizeof(T);
-  constexpr int PAD = V;
+  // fragment loads of the MMA form are conflict free when a row of the staged
+  // tile is 4 (mod 16) doubles long
+  constexpr int PAD = MMA ? 4 : V;
+  static_assert(!MMA || (sizeof(T) == 8 && TM * TN == 32 && BM % 32 == 0 && BN % 32 == 0 && BK % 4 == 0),
+                "the tensor-core form is for double and 32x32 warp tiles");
   typedef typename Vec16<T>::type Vec;
   __shared__ __align__(16) T As[2][BK][BM + PAD];
   __shared__ __align__(16) T Bs[2][BK][BN + PAD];
@@ -134,6 +150,59 @@ gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
     else load_b_nmajor(k0);
   };
 
+  if constexpr (MMA) {
+    const int warp = tid >> 5, lane = tid & 31;
+    constexpr int WN = BN / 32;
+    const int wm = (warp / WN) * 32, wn = (warp % WN) * 32;
+    const int fr = lane >> 2, fc = lane & 3;
+    double acc2[4][4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { acc2[i][j][0] = 0.0; acc2[i][j][1] = 0.0; }
+    load_tiles(0);
+    store_tiles(0);
+    __syncthreads();
+    const int ktiles = (K + BK - 1) / BK;
+    for (int kt = 0; kt < ktiles; ++kt) {
+      const int buf = kt & 1;
+      if (kt + 1 < ktiles) load_tiles((kt + 1) * BK);
+#pragma unroll
+      for (int k4 = 0; k4 < BK; k4 += 4) {
+        double a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = As[buf][k4 + fc][wm + i * 8 + fr];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = Bs[buf][k4 + fc][wn + j * 8 + fr];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mma_f64(acc2[i][j][0], acc2[i][j][1], a[i], b[j]);
+      }
+      if (kt + 1 < ktiles) {
+        store_tiles(buf ^ 1);
+        __syncthreads();
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = row0 + wm + i * 8 + fr;
+      if (r >= M) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c0 = col0 + wn + j * 8 + 2 * fc;
+        T* dst = C + static_cast<long long>(r) * ldc + c0;
+        if (c_vec && c0 + 2 <= N) {
+          *reinterpret_cast<double2*>(dst) = make_double2(acc2[i][j][0], acc2[i][j][1]);
+        } else {
+          if (c0 < N) dst[0] = static_cast<T>(acc2[i][j][0]);
+          if (c0 + 1 < N) dst[1] = static_cast<T>(acc2[i][j][1]);
+        }
+      }
+    }
+    return;
+  }
+
   T acc[TM][TN];
 #pragma unroll
   for (int i = 0; i < TM; ++i)
@@ -197,11 +266,28 @@ gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
 // Tile shapes: the large one for the evaluation's batched scores, the small one
 // for the fit, whose products have at most 64 rows.
 template <typename T> struct GemmTile;
-template <> struct GemmTile<float> { static constexpr int BM = 128, BN = 128, BK = 16, TM = 8, TN = 8; };
-template <> struct GemmTile<double> { static constexpr int BM = 64, BN = 64, BK = 8, TM = 4, TN = 4; };
+template <> struct GemmTile<float> {
+  static constexpr int BM = 128, BN = 128, BK = 16, TM = 8, TN = 8;
+  static constexpr bool MMA = false;
+};
+template <> struct GemmTile<double> {     // FP64 tensor cores, 16 warps of 32x32
+  static constexpr int BM = 128, BN = 128, BK = 8, TM = 8, TN = 4;
+  static constexpr bool MMA = true;
+};
 template <typename T> struct SmallGemmTile;
-template <> struct SmallGemmTile<float> { static constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4; };
-template <> struct SmallGemmTile<double> { static constexpr int BM = 64, BN = 64, BK = 8, TM = 4, TN = 4; };
+template <> struct SmallGemmTile<float> {
+  static constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+  static constexpr bool MMA = false;
+};
+template <> struct SmallGemmTile<double> {  // 8 warps of 32x32
+  static constexpr int BM = 64, BN = 128, BK = 8, TM = 8, TN = 4;
+  static constexpr bool MMA = true;
+};
+// The FMA form for doubles (kept for comparisons and as the check of the tensor-core form).
+struct FmaGemmTileDouble {
+  static constexpr int BM = 64, BN = 64, BK = 8, TM = 4, TN = 4;
+  static constexpr bool MMA = false;
+};
 
 // Optional extras of a launch: row gather lists for the operands whose
 // contraction index is contiguous, and a split of the contraction index into
@@ -234,11 +320,11 @@ int launch_gemm_tile(const T* A, const T* B, T* C, int M, int N, int K, long lon
   dim3 grid((N + G::BN - 1) / G::BN, (M + G::BM - 1) / G::BM, x.slices);
   const int threads = (G::BM / G::TM) * (G::BN / G::TN);
   if (b_kmajor)
-    gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, true><<<grid, threads, 0, stream>>>(
+    gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, true, G::MMA><<<grid, threads, 0, stream>>>(
         A, B, C, M, N, K, lda, ldb, ldc, a_vec, b_vec, c_vec, x.a_gather, x.b_gather, k_per_slice,
         x.c_slice_stride, nullptr, -1);
   else
-    gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, false><<<grid, threads, 0, stream>>>(
+    gemm_kernel<T, G::BM, G::BN, G::BK, G::TM, G::TN, false, G::MMA><<<grid, threads, 0, stream>>>(
         A, B, C, M, N, K, lda, ldb, ldc, a_vec, b_vec, c_vec, x.a_gather, nullptr, k_per_slice,
         x.c_slice_stride, x.k_owner, x.skip_owner);
   SDCAB_CUDA_TRY(cudaGetLastError());
@@ -248,6 +334,10 @@ int launch_gemm_tile(const T* A, const T* B, T* C, int M, int N, int K, long lon
 template <typename T>
 int launch_gemm(const T* A, const T* B, T* C, int M, int N, int K, long long lda, long long ldb,
                 long long ldc, bool b_kmajor, cudaStream_t stream) {
+  // doubles: 64-row tiles keep two thread blocks per SM and even out the last wave
+  if (sizeof(T) == 8)
+    return launch_gemm_tile<T, SmallGemmTile<T>>(A, B, C, M, N, K, lda, ldb, ldc, b_kmajor, stream,
+                                                 GemmExtras());
   return launch_gemm_tile<T, GemmTile<T>>(A, B, C, M, N, K, lda, ldb, ldc, b_kmajor, stream,
                                           GemmExtras());
 }
