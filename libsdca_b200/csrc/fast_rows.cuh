@@ -20,10 +20,19 @@ namespace sdcab {
 
 constexpr int kNoFastPath = 1;
 constexpr int kFastThreads = 128;
-// Resident blocks per SM the register allocation aims for: double thresholds
-// need more live registers, and spilling them costs more than the lost warps.
-template <typename R> struct FastMinBlocks { static constexpr int value = 6; };
-template <> struct FastMinBlocks<double> { static constexpr int value = 5; };
+// Resident blocks per SM the register allocation aims for.  Operators that keep
+// the row in registers through their search: double thresholds need more live
+// registers, and spilling them costs more than the lost warps.  The top-k
+// projections read the row a second time for the final map instead (see the
+// kernel), so their search runs in 64-72 registers and eight (seven for the
+// simplex with double thresholds) blocks fit; measured fastest at these values.
+template <typename R, int PROX> struct FastMinBlocks {
+  static constexpr bool kTopk = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased ||
+                                 PROX == kTopkCone || PROX == kTopkConeBiased);
+  static constexpr bool kSimplex = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased);
+  static constexpr bool kDouble = sizeof(R) == 8;
+  static constexpr int value = kTopk ? ((kDouble && kSimplex) ? 7 : 8) : (kDouble ? 5 : 6);
+};
 
 template <typename Data> struct VecOf;
 template <> struct VecOf<float> { typedef float4 type; static constexpr int N = 4; };
@@ -47,6 +56,23 @@ struct RegRow {
       const int vi = j * 32 + lane;
       if (vi * VN < m) {
         v[j] = __ldcs(gv + vi);
+      } else {
+        Data* e = reinterpret_cast<Data*>(&v[j]);
+#pragma unroll
+        for (int c = 0; c < VN; ++c) e[c] = -num<Data>::inf();
+      }
+    }
+  }
+
+  // First of two reads of a row: cached in L2 (not L1), so that the second read --
+  // after the search, when the row's registers have been given up -- finds it there.
+  __device__ __forceinline__ void load_keep(const Data* __restrict__ g, int lane) {
+    const Vec* gv = reinterpret_cast<const Vec*>(g);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int vi = j * 32 + lane;
+      if (vi * VN < m) {
+        v[j] = __ldcg(gv + vi);
       } else {
         Data* e = reinterpret_cast<Data*>(&v[j]);
 #pragma unroll
@@ -471,17 +497,16 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
   LaneRow<Data> cand;
   const int total = compact_candidates(row, cut, slots, counter, lane, cand);
   if (total > 32 || total <= k) return kFastNeedsFullRow;
-  const Sorted<R> c = sort_candidates<R>(cand, total, lane);
   const R inv_K = tc.inv_K;
-  if (sorted_special_cases<R>(c, m, k, inv_K, thr) != kProjGeneral) return kFastDone;
   const R eps = 16 * num<R>::eps();
-  // sum and count of the positive entries.  U is empty on this branch, so no
+  // sum and count of the positive entries, taken now so that the row's registers
+  // are free during the search.  U is empty on the branch that uses them, so no
   // output attains hi and only the acceptance test below depends on the sum:
   // float data is summed per lane in float (four chains), across lanes in R,
   // and a test that is not clear-cut is left to the general search.
   int j = 0; R s = 0;
-  bool clear_cut = true;
-  if (std::is_same<Data, float>::value && std::is_same<R, double>::value) {
+  constexpr bool kFloatSums = std::is_same<Data, float>::value && std::is_same<R, double>::value;
+  if (kFloatSums) {
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     int cnt[4] = {0, 0, 0, 0};
 #pragma unroll
@@ -497,14 +522,19 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
     j = warp_sum((cnt[0] + cnt[1]) + (cnt[2] + cnt[3]));
     s = warp_sum((static_cast<R>(acc[0]) + static_cast<R>(acc[1])) +
                  (static_cast<R>(acc[2]) + static_cast<R>(acc[3])));
-    const R hi_est = s * inv_K;
-    const R mx = c.at(0);
-    clear_cut = abs_(mx - hi_est) > R(1e-4) * max_(abs_(hi_est), abs_(mx));
   } else {
     row.for_each([&](Data xd, int) {
       if (xd > Data(0)) { ++j; s += static_cast<R>(xd); }
     });
     j = warp_sum(j); s = warp_sum(s);
+  }
+  const Sorted<R> c = sort_candidates<R>(cand, total, lane);
+  if (sorted_special_cases<R>(c, m, k, inv_K, thr) != kProjGeneral) return kFastDone;
+  bool clear_cut = true;
+  if (kFloatSums) {
+    const R hi_est = s * inv_K;
+    const R mx = c.at(0);
+    clear_cut = abs_(mx - hi_est) > R(1e-4) * max_(abs_(hi_est), abs_(mx));
   }
   if (!clear_cut) return kFastNeedsFullRow;
   // U empty: t = 0 and hi = K s / K^2 = s / K (include/sdca/prox/topk_cone.h:83-98)
@@ -653,7 +683,7 @@ __device__ __noinline__ Thr<R> full_row_thresholds(const Data* buf, int m, const
 }
 
 template <typename Data, typename R, int PROX, int NV>
-__global__ void __launch_bounds__(kFastThreads, FastMinBlocks<R>::value)
+__global__ void __launch_bounds__(kFastThreads, FastMinBlocks<R, PROX>::value)
 fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long long n,
                  ProxParams q, int m_pad) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -676,9 +706,12 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
   const TopkConsts<R> tc(q.k > 0 ? q.k : 1, static_cast<R>(q.rhs), rho_used);
   for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + warp; r < n;
        r += static_cast<long long>(gridDim.x) * warps_per_block) {
+    // top-k rows are read twice (the second time from L2): the search between the
+    // two reads needs the registers more than it needs the row
+    constexpr bool kTwice = kTopk;
     RegRow<Data, NV> row;
     row.m = m;
-    row.load(a + r * m, lane);
+    if (kTwice) row.load_keep(a + r * m, lane); else row.load(a + r * m, lane);
     Thr<R> thr;
     FastStatus st = kFastNeedsFullRow;
     if (PROX == kTopkSimplex || PROX == kTopkSimplexBiased) {
@@ -696,6 +729,7 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
     }
     if (kStaged) {
       if (st != kFastDone) {
+        if (kTwice) row.load(a + r * m, lane);
         row.for_each([&](Data x, int i) { stage[i] = x; });
         __syncwarp();
         thr = full_row_thresholds<R, Data, PROX>(stage, m, &q);
@@ -705,7 +739,14 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
       thr = compute_thresholds<R>(PROX, row, q);
     }
     Applier<Data> f(thr, prox_map(PROX), q.alpha);
-    row.store(out + r * m, lane, f);
+    if (kTwice) {
+      RegRow<Data, NV> again;
+      again.m = m;
+      again.load(a + r * m, lane);
+      again.store(out + r * m, lane, f);
+    } else {
+      row.store(out + r * m, lane, f);
+    }
   }
 }
 
