@@ -49,8 +49,8 @@ PROX_CONFIGS = {
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of fast_rows_kernel<float,double,top-k simplex,8>
-# per row, from the ncu capture summarised in profiles/ (262.2 MB + 214.2 MB over 65536 rows)
-NCU_DRAM_BYTES_PER_ROW = 4001 + 3268
+# per row, from the ncu capture summarised in profiles/ (263.1 MB + 209.4 MB over 65536 rows)
+NCU_DRAM_BYTES_PER_ROW = 4015 + 3195
 
 
 def measured_peak_gbs():
@@ -600,8 +600,9 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": rows * NCU_DRAM_BYTES_PER_ROW, "kernel": slow,
                          "traffic_note": "dram read + write bytes of one launch, scaled by rows from the ncu "
-                                         "capture of a 65536-row launch (4001 B read + 3268 B written per row "
-                                         "while the kernel runs; the last 732 B per row leave L2 afterwards)",
+                                         "capture of a 65536-row launch (4015 B read + 3195 B written per row "
+                                         "while the kernel runs; the last 805 B per row leave L2 afterwards; the "
+                                         "row's second read is served by L2)",
                          "peak_kind": "of " + peak_kind,
                          "per_kernel_ms": per_op_ms,
                          "per_kernel_gbs": {k: rows * BYTES_PER_ROW / (v * 1e-3) / 1e9
