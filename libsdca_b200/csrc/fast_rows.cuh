@@ -26,12 +26,13 @@ constexpr int kFastThreads = 128;
 // projections read the row a second time for the final map instead (see the
 // kernel), so their search runs in 64-72 registers and eight (seven for the
 // simplex with double thresholds) blocks fit; measured fastest at these values.
-template <typename R, int PROX> struct FastMinBlocks {
+template <typename Data, typename R, int PROX> struct FastMinBlocks {
   static constexpr bool kTopk = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased ||
                                  PROX == kTopkCone || PROX == kTopkConeBiased);
   static constexpr bool kSimplex = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased);
   static constexpr bool kDouble = sizeof(R) == 8;
-  static constexpr int value = kTopk ? ((kDouble && kSimplex) ? 7 : 8) : (kDouble ? 5 : 6);
+  static constexpr bool kEntropic = sizeof(Data) == 4 && (PROX == kTopkEntropy || PROX == kEntropy);
+  static constexpr int value = kTopk ? ((kDouble && kSimplex) ? 7 : 8) : (kEntropic ? 8 : (kDouble ? 5 : 6));
 };
 
 template <typename Data> struct VecOf;
@@ -683,7 +684,7 @@ __device__ __noinline__ Thr<R> full_row_thresholds(const Data* buf, int m, const
 }
 
 template <typename Data, typename R, int PROX, int NV>
-__global__ void __launch_bounds__(kFastThreads, FastMinBlocks<R, PROX>::value)
+__global__ void __launch_bounds__(kFastThreads, FastMinBlocks<Data, R, PROX>::value)
 fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long long n,
                  ProxParams q, int m_pad) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -708,7 +709,7 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
        r += static_cast<long long>(gridDim.x) * warps_per_block) {
     // top-k rows are read twice (the second time from L2): the search between the
     // two reads needs the registers more than it needs the row
-    constexpr bool kTwice = kTopk;
+    constexpr bool kTwice = kStaged;
     RegRow<Data, NV> row;
     row.m = m;
     if (kTwice) row.load_keep(a + r * m, lane); else row.load(a + r * m, lane);
