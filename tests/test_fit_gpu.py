@@ -140,6 +140,19 @@ def test_many_classes_take_the_general_step(ref, cuda_lib):
     compare(*out, 1e-9, "m=300")
 
 
+def test_score_rows_that_do_not_fit_on_chip(ref, cuda_lib):
+    """600 classes: the 64 score rows of a block (64 x 600 doubles) stay in global memory."""
+    K, labels = kernel_problem(n=260, dim=16, m=600, seed=13)
+    out = run_both(ref, cuda_lib, "l2_hinge_topk", K, labels, 600, True, np.float64, c=1.0, k=3,
+                   max_epoch=3)
+    compare(*out, 1e-9, "m=600")
+    rng = np.random.default_rng(77)
+    X, labels, _ = random_problem(rng, 150, 20, 600, np.float32, False)
+    out = run_both(ref, cuda_lib, "l2_topk_hinge", X, labels, 600, False, np.float32, c=1.0, k=2,
+                   max_epoch=3)
+    compare(*out, 2e-4, "m=600 features")
+
+
 def test_rejects_what_it_cannot_fit(cuda_lib):
     from libsdca_b200.binding import SdcabError
     K, labels = kernel_problem(n=50, dim=4, m=4, seed=3)
