@@ -410,7 +410,9 @@ __device__ __noinline__ bool warp_step_topk_hinge_long(const StepConsts<R, Data>
   return warp_step_topk_hinge<R, Data, 8>(*sc, hi, rhs, *in, *out);
 }
 
-template <typename Data, typename R>
+// ON_CHIP: the block's score rows live in shared memory (a compile-time fact, so
+// that every access to them is a shared-memory instruction).
+template <typename Data, typename R, bool ON_CHIP>
 __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int m = p.m, count = p.count;
@@ -418,7 +420,8 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
   double* G = reinterpret_cast<double*>(smem_raw);                  // 64 x 64
   double* delta = G + kBlockSteps * kBlockSteps;                    // 2 x m: this step's / the previous one's
   double* S = delta + 2 * m;                                        // count x m when on chip
-  Data* scores = reinterpret_cast<Data*>(p.s_on_chip ? S + static_cast<size_t>(kBlockSteps) * m : S);
+  double* const S_shared = S;
+  Data* scores = reinterpret_cast<Data*>(ON_CHIP ? S + static_cast<size_t>(kBlockSteps) * m : S);
   Data* a_s = scores + m;
   Data* v_s = a_s + m;
   Data* a_next = v_s + m;                                           // 2 x m, rows fetched ahead
@@ -455,8 +458,8 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
     s_t[tid] = p.t_keep[i];
   }
   if (tid < 2) s_skip[tid] = 1;
-  if (p.s_on_chip) {
-    for (int t = tid; t < count * m; t += kFitThreads) S[t] = p.S[t];
+  if (ON_CHIP) {
+    for (int t = tid; t < count * m; t += kFitThreads) S_shared[t] = p.S[t];
   } else {
     S = p.S;
   }
@@ -767,9 +770,14 @@ struct BlockRunner {
     s_on_chip = (with_s + 2048 <= info.smem_optin) ? 1 : 0;
     chain_smem = s_on_chip ? with_s : fixed;
     if (chain_smem + 2048 > info.smem_optin) return SDCAB_ERR_TOO_LARGE;
-    SDCAB_CUDA_TRY(cudaFuncSetAttribute(fit_chain_kernel<Data, R>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(chain_smem)));
+    if (s_on_chip)
+      SDCAB_CUDA_TRY(cudaFuncSetAttribute(fit_chain_kernel<Data, R, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(chain_smem)));
+    else
+      SDCAB_CUDA_TRY(cudaFuncSetAttribute(fit_chain_kernel<Data, R, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(chain_smem)));
     int rc = buf.alloc(&order, static_cast<size_t>(t->n)); if (rc) return rc;
     if (t->input_kind == SDCAB_INPUT_KERNEL) {
       for (int h = 0; h < 2; ++h) {
@@ -835,7 +843,8 @@ struct BlockRunner {
     c.o = o; c.order = ord; c.labels = t->labels; c.offsets = t->offsets; c.S = S; c.G = G; c.A = A; c.D = D;
     c.t_keep = t_keep;
     c.m = m; c.count = count; c.kernel_input = kernel_input ? 1 : 0; c.s_on_chip = s_on_chip;
-    fit_chain_kernel<Data, R><<<1, kFitThreads, chain_smem, s>>>(c);
+    if (s_on_chip) fit_chain_kernel<Data, R, true><<<1, kFitThreads, chain_smem, s>>>(c);
+    else fit_chain_kernel<Data, R, false><<<1, kFitThreads, chain_smem, s>>>(c);
     SDCAB_CUDA_TRY(cudaGetLastError());
     if (!kernel_input) {
       dim3 grid(static_cast<unsigned>((t->d + 255) / 256), static_cast<unsigned>(m));
@@ -898,7 +907,8 @@ struct BlockRunner {
       c.o = o; c.order = ord; c.labels = t->labels; c.offsets = t->offsets; c.S = S; c.G = G2[h]; c.A = A;
       c.D = nullptr;
       c.t_keep = t_keep; c.m = m; c.count = count; c.kernel_input = 1; c.s_on_chip = s_on_chip;
-      fit_chain_kernel<Data, R><<<1, kFitThreads, chain_smem, sc>>>(c);
+      if (s_on_chip) fit_chain_kernel<Data, R, true><<<1, kFitThreads, chain_smem, sc>>>(c);
+      else fit_chain_kernel<Data, R, false><<<1, kFitThreads, chain_smem, sc>>>(c);
       SDCAB_CUDA_TRY(cudaGetLastError());
       // The next product may start once block b - 1 has stepped; it is released
       // together with block b's steps (after the pack), on a stream of lower priority,
