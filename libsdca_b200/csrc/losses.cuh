@@ -110,6 +110,80 @@ SDCAB_D R row_log_sum_exp(const Row& row) {
   return mx + log1p_(s);
 }
 
+// The k largest values of a row, summed (all of them, and only the positive ones).
+// On the device every lane keeps the K largest of its own share in registers (a
+// bubble through K slots per entry, in the data type), then the k largest of the
+// whole row are popped off the lanes' heads; which of several equal values is
+// taken does not matter to the sums.  K is the compile-time size that holds k.
+#if defined(__CUDA_ARCH__)
+__device__ __forceinline__ float lanes_max(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ double lanes_max(double v) { return warp_max(v); }
+
+template <typename R, int K, typename Row>
+__device__ __forceinline__ void topk_sums_device(const Row& row, int k, R& sum_all, R& sum_pos) {
+  typedef typename Row::data_type Data;
+  const Data none = -num<Data>::inf();
+  Data top[K];
+#pragma unroll
+  for (int t = 0; t < K; ++t) top[t] = none;
+  row.for_each([&](Data x, int) {
+#pragma unroll
+    for (int t = 0; t < K; ++t) {
+      const Data hi = max_(top[t], x);
+      x = min_(top[t], x);
+      top[t] = hi;
+    }
+  });
+  const int lane = lane_id();
+  sum_all = 0; sum_pos = 0;
+  for (int j = 0; j < k; ++j) {
+    const Data best = lanes_max(top[0]);
+    if (!(best > none)) break;                       // fewer than k entries
+    const unsigned who = __ballot_sync(kFullMask, top[0] == best);
+    if (lane == __ffs(who) - 1) {
+#pragma unroll
+      for (int t = 0; t + 1 < K; ++t) top[t] = top[t + 1];
+      top[K - 1] = none;
+    }
+    const R v = static_cast<R>(best);
+    sum_all += v;
+    if (v > 0) sum_pos += v;
+  }
+}
+#endif
+
+// Sum of the k largest entries of the row and of the positive ones among them
+// (the loop of include/sdca/solver/objective/l2_hinge_topk.h:71-86 on sorted data).
+template <typename R, typename Row>
+SDCAB_D void topk_sums(const Row& row, int k, R& sum_all, R& sum_pos) {
+#if defined(__CUDA_ARCH__)
+  if (k <= 8) {
+    switch (k) {
+      case 1: topk_sums_device<R, 1>(row, k, sum_all, sum_pos); return;
+      case 2: topk_sums_device<R, 2>(row, k, sum_all, sum_pos); return;
+      case 3: topk_sums_device<R, 3>(row, k, sum_all, sum_pos); return;
+      case 4: topk_sums_device<R, 4>(row, k, sum_all, sum_pos); return;
+      case 5: topk_sums_device<R, 5>(row, k, sum_all, sum_pos); return;
+      case 6: topk_sums_device<R, 6>(row, k, sum_all, sum_pos); return;
+      case 7: topk_sums_device<R, 7>(row, k, sum_all, sum_pos); return;
+      default: topk_sums_device<R, 8>(row, k, sum_all, sum_pos); return;
+    }
+  }
+#endif
+  Taken<R> tk;
+  sum_all = 0; sum_pos = 0;
+  for (int j = 0; j < k; ++j) {
+    R v;
+    if (!take_next<R>(row, tk, v)) break;
+    sum_all += v;
+    if (v > 0) sum_pos += v;
+  }
+}
+
 // ---- multiclass --------------------------------------------------------------
 // s[0, m): scores of the example, y: its label.  Returns the primal loss before
 // the objective's coefficient and the number of other classes scoring at least
@@ -140,14 +214,8 @@ SDCAB_D R multiclass_primal_loss(const ObjectiveParams& o, const Data* s, int m,
     }
     case kObjL2HingeTopk: case kObjL2TopkHinge: {  // l2_hinge_topk.h:71-86, l2_topk_hinge.h:72-87
       ShiftedRow<Data> h(s, m, y, static_cast<Data>(Data(1) - sy));
-      Taken<R> tk;
-      R sum_all = 0, sum_pos = 0;
-      for (int j = 0; j < o.k; ++j) {
-        R v;
-        if (!take_next<R>(h, tk, v)) break;
-        sum_all += v;
-        if (v > 0) sum_pos += v;
-      }
+      R sum_all, sum_pos;
+      topk_sums<R>(h, o.k, sum_all, sum_pos);
       return (o.id == kObjL2HingeTopk) ? max_(R(0), sum_all) : sum_pos;
     }
     case kObjL2HingeTopkSmooth: {  // l2_hinge_topk.h:162-179
