@@ -22,7 +22,7 @@
 
 #include "common_host.h"
 #include "eval_host.h"
-#include "gemm_simt.cuh"
+#include "gemm_blocked.cuh"
 #include "gemm_tc.cuh"
 #include "losses.cuh"
 

@@ -21,14 +21,13 @@
 #include "common_host.h"
 #include "eval_host.h"
 #include "fit_host.h"
-#include "gemm_simt.cuh"
+#include "gemm_blocked.cuh"
 #include "update_core.cuh"
 
 namespace sdcab {
 namespace {
 
 constexpr int kFitThreads = 288;   // warp 0 steps, 256 threads keep the score rows current
-constexpr int kFitWarps = kFitThreads / 32;
 constexpr int kBlockSteps = 64;   // steps whose score products are formed together
 
 // ---- the chain ---------------------------------------------------------------

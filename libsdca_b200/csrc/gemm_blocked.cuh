@@ -1,5 +1,7 @@
-// Register-blocked SIMT GEMM for the score products, in the data type (float or
-// double): the evaluation's batched scores and the fit's per-block scores.
+// Blocked GEMM for the score products in the data type: the evaluation's batched
+// scores and the fit's per-block scores.  Doubles run on the FP64 tensor cores
+// (mma.sync m8n8k4), floats that the tcgen05 kernel cannot take on FMA; both share
+// the tile loads with their gathers, slices and masks.
 #pragma once
 
 #include <cstdint>
