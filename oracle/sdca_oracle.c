@@ -1,8 +1,9 @@
 /*
  * Test infrastructure: a plain-C restatement of the reference's CPU algorithms
- * for the batched proximal operators and the objective / duality-gap
- * evaluation (mlapin/libsdca: include/sdca/prox, include/sdca/math,
- * include/sdca/solver/eval*, include/sdca/solver/objective).  The body is
+ * for the batched proximal operators, the objective / duality-gap evaluation
+ * and the SDCA solver around them (mlapin/libsdca: include/sdca/prox,
+ * include/sdca/math, include/sdca/solver/eval*, include/sdca/solver/objective,
+ * include/sdca/solver/update.h, include/sdca/solver.h).  The body is
  * sdca_oracle_impl.inc, compiled here for float/double data and float/double
  * accumulators; each function there cites the file:line it follows.
  *
@@ -49,10 +50,12 @@ typedef struct {
 
 /* float data, float accumulators */
 #define D float
+#define D_EPS FLT_EPSILON
 #define R float
 #define FN(x) CAT(x, ff)
 #define R_EPS FLT_EPSILON
 #define R_MIN FLT_MIN
+#define R_MAX FLT_MAX
 #define R_EXP_MIN_ARG (-8.733654022216796875000000e+01f) /* math/log_exp.h:47-52 */
 #define R_EXP expf
 #define R_LOG logf
@@ -67,6 +70,8 @@ typedef struct {
 #undef FN
 #undef R_EPS
 #undef R_MIN
+#undef R_MAX
+#undef D_EPS
 #undef R_EXP_MIN_ARG
 #undef R_EXP
 #undef R_LOG
@@ -78,10 +83,12 @@ typedef struct {
 
 /* float data, double accumulators (the reference's default for float input) */
 #define D float
+#define D_EPS FLT_EPSILON
 #define R double
 #define FN(x) CAT(x, fd)
 #define R_EPS DBL_EPSILON
 #define R_MIN DBL_MIN
+#define R_MAX DBL_MAX
 #define R_EXP_MIN_ARG (log(DBL_MIN)) /* math/log_exp.h:33-35 */
 #define R_EXP exp
 #define R_LOG log
@@ -96,6 +103,8 @@ typedef struct {
 #undef FN
 #undef R_EPS
 #undef R_MIN
+#undef R_MAX
+#undef D_EPS
 #undef R_EXP_MIN_ARG
 #undef R_EXP
 #undef R_LOG
@@ -107,10 +116,12 @@ typedef struct {
 
 /* double data, float accumulators */
 #define D double
+#define D_EPS DBL_EPSILON
 #define R float
 #define FN(x) CAT(x, df)
 #define R_EPS FLT_EPSILON
 #define R_MIN FLT_MIN
+#define R_MAX FLT_MAX
 #define R_EXP_MIN_ARG (-8.733654022216796875000000e+01f)
 #define R_EXP expf
 #define R_LOG logf
@@ -125,6 +136,8 @@ typedef struct {
 #undef FN
 #undef R_EPS
 #undef R_MIN
+#undef R_MAX
+#undef D_EPS
 #undef R_EXP_MIN_ARG
 #undef R_EXP
 #undef R_LOG
@@ -136,10 +149,12 @@ typedef struct {
 
 /* double data, double accumulators */
 #define D double
+#define D_EPS DBL_EPSILON
 #define R double
 #define FN(x) CAT(x, dd)
 #define R_EPS DBL_EPSILON
 #define R_MIN DBL_MIN
+#define R_MAX DBL_MAX
 #define R_EXP_MIN_ARG (log(DBL_MIN))
 #define R_EXP exp
 #define R_LOG log
@@ -177,6 +192,73 @@ int sdca_oracle_eval(const oracle_eval_args* a, int dtype, int result, double* o
   if (dtype == 1 && result == 0) return eval_df(a, out, acc);
   if (dtype == 1 && result == 1) return eval_dd(a, out, acc);
   return -2;
+}
+
+/* The example order of every epoch of the reference's solver (include/sdca/solver.h:59,
+ * 77-79,96-100): a default-seeded std::minstd_rand (x <- 48271 x mod 2^31 - 1 from 1)
+ * driving std::shuffle as libstdc++ implements it, on one index vector kept across epochs. */
+static uint64_t minstd_next(uint64_t* x) { *x = (*x * 48271ull) % 2147483647ull; return *x; }
+static uint64_t uniform_upto(uint64_t* g, uint64_t hi) {
+  const uint64_t grange = 2147483646ull - 1ull;
+  uint64_t ret;
+  if (grange > hi) {
+    const uint64_t span = hi + 1, scaling = grange / span, past = span * scaling;
+    do { ret = minstd_next(g) - 1; } while (ret >= past);
+    ret /= scaling;
+  } else if (grange < hi) {
+    const uint64_t gspan = grange + 1;
+    uint64_t tmp;
+    do {
+      tmp = gspan * uniform_upto(g, hi / gspan);
+      ret = tmp + (minstd_next(g) - 1);
+    } while (ret > hi || ret < tmp);
+  } else {
+    ret = minstd_next(g) - 1;
+  }
+  return ret;
+}
+int sdca_oracle_epoch_permutations(int64_t n, int64_t num_epochs, int64_t* perm) {
+  uint64_t g = 1;
+  int64_t* v = (int64_t*)malloc(sizeof(int64_t) * (size_t)(n > 0 ? n : 1));
+  if (!v) return -9;
+  for (int64_t i = 0; i < n; ++i) v[i] = i;
+  const uint64_t grange = 2147483646ull - 1ull;
+  for (int64_t e = 0; e < num_epochs; ++e) {
+    const uint64_t un = (uint64_t)n;
+    if (un > 0 && grange / un >= un) {        /* two positions per draw */
+      uint64_t i = 1;
+      if (un % 2 == 0 && un > 1) { uint64_t j = uniform_upto(&g, 1); int64_t t = v[i]; v[i] = v[j]; v[j] = t; ++i; }
+      while (i < un) {
+        const uint64_t b0 = i + 1, b1 = b0 + 1;
+        const uint64_t x = uniform_upto(&g, b0 * b1 - 1);
+        uint64_t j = x / b1; int64_t t = v[i]; v[i] = v[j]; v[j] = t; ++i;
+        j = x % b1; t = v[i]; v[i] = v[j]; v[j] = t; ++i;
+      }
+    } else {
+      for (uint64_t i = 1; i < un; ++i) { uint64_t j = uniform_upto(&g, i); int64_t t = v[i]; v[i] = v[j]; v[j] = t; }
+    }
+    for (int64_t i = 0; i < n; ++i) perm[e * n + i] = v[i];
+  }
+  free(v);
+  return 0;
+}
+
+int sdca_oracle_fit(const oracle_eval_args* a, int dtype, int result, double* hist, int64_t hist_cap,
+                    int64_t* num_evals, int64_t* epoch, int* status, double* acc_last) {
+  if (a->max_epoch < 0 || a->n <= 0) return -2;
+  int64_t epochs = a->max_epoch > 0 ? a->max_epoch : 1;
+  int64_t* perm = (int64_t*)malloc(sizeof(int64_t) * (size_t)(epochs * a->n));
+  if (!perm) return -9;
+  int rc = sdca_oracle_epoch_permutations(a->n, epochs, perm);
+  if (rc == 0) {
+    if (dtype == 0 && result == 0) rc = fit_ff(a, perm, hist, hist_cap, num_evals, epoch, status, acc_last);
+    else if (dtype == 0 && result == 1) rc = fit_fd(a, perm, hist, hist_cap, num_evals, epoch, status, acc_last);
+    else if (dtype == 1 && result == 0) rc = fit_df(a, perm, hist, hist_cap, num_evals, epoch, status, acc_last);
+    else if (dtype == 1 && result == 1) rc = fit_dd(a, perm, hist, hist_cap, num_evals, epoch, status, acc_last);
+    else rc = -2;
+  }
+  free(perm);
+  return rc;
 }
 
 double sdca_oracle_lambert_w_exp_f64(double x) { return lambert_w_exp_d(x); }

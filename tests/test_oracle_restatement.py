@@ -106,3 +106,47 @@ def test_eval_matches_reference(ref, port, objective, dtype, kernel):
     assert abs(rt["primal_loss"] - pt["primal_loss"]) <= tol * max(1, abs(rt["primal_loss"]))
     assert np.allclose(rt["accuracy"], pt["accuracy"], atol=1e-12)
     assert abs(rt["rank_loss"] - pt["rank_loss"]) <= 1e-12
+
+
+@pytest.mark.parametrize("n", [1, 2, 7, 1000, 46340, 46341, 50000])
+def test_epoch_order_matches_reference(ref, port, n):
+    assert np.array_equal(port.epoch_permutations(n, 3), ref.epoch_permutations(n, 3))
+
+
+@pytest.mark.parametrize("objective", OBJECTIVES)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+@pytest.mark.parametrize("kernel", [False, True])
+def test_fit_matches_reference(ref, port, objective, dtype, kernel):
+    """The restated solver (steps of all nine objectives, epoch order, stopping rule)
+    against solver::solve of the reference's headers."""
+    from oracle.refapi import MULTILABEL, OBJECTIVES as IDS
+    rng = np.random.default_rng(stable_seed("port-fit", objective, str(dtype), kernel))
+    ml = IDS[objective] in MULTILABEL
+    n, d, m = 60, 6, 6
+    X, labels, offsets = random_problem(rng, n, d, m, dtype, ml)
+    data = (X.astype(np.float64) @ X.astype(np.float64).T).astype(dtype) if kernel else X
+    kw = dict(c=0.9, gamma=0.7, k=2, epsilon=1e-3, max_epoch=12, eval_epoch=2, offsets=offsets, kernel=kernel)
+    A_ref = np.zeros((n, m), dtype=dtype); W_ref = np.zeros((m, d), dtype=dtype)
+    A = np.zeros((n, m), dtype=dtype); W = np.zeros((m, d), dtype=dtype)
+    r = ref.fit(objective, data, A_ref, labels, W=None if kernel else W_ref, **kw)
+    p = port.fit(objective, data, A, labels, W=None if kernel else W, **kw)
+    tol = 1e-10 if dtype == np.float64 else 2e-4
+    assert p["status"] == r["status"] and p["epoch"] == r["epoch"]
+    assert len(p["history"]) == len(r["history"])
+    assert np.abs(A - A_ref).max() <= tol * max(1.0, np.abs(A_ref).max())
+    if not kernel:
+        assert np.abs(W - W_ref).max() <= tol * max(1.0, np.abs(W_ref).max()) * d
+    assert np.abs(p["history"][:, :2] - r["history"][:, :2]).max() <= 10 * tol * max(1.0, np.abs(r["history"][:, :2]).max())
+
+
+def test_fit_matches_golden(port):
+    """The committed fits of the reference's solver (no reference tree needed)."""
+    from tests.golden_util import fit_cases
+    for c in fit_cases():
+        A = np.zeros_like(c["A"]); W = np.zeros_like(c["W"])
+        p = port.fit(c["objective"], c["data"], A, c["labels"], W=None if c["kernel"] else W,
+                     kernel=c["kernel"], offsets=c["offsets"], c=c["c"], gamma=c["gamma"], k=c["k"],
+                     epsilon=c["epsilon"], max_epoch=c["max_epoch"], eval_epoch=c["eval_epoch"])
+        tol = 1e-10 if c["data"].dtype == np.float64 else 2e-4
+        assert p["status"] == c["status"] and p["epoch"] == c["epoch"]
+        assert np.abs(A - c["A"]).max() <= tol * max(1.0, np.abs(c["A"]).max())
