@@ -792,7 +792,7 @@ struct BlockRunner {
     rc = buf.alloc(&S, static_cast<size_t>(kBlockSteps) * m); if (rc) return rc;
     rc = buf.alloc(&G, static_cast<size_t>(kBlockSteps) * kBlockSteps); if (rc) return rc;
     rc = buf.alloc(&t_keep, static_cast<size_t>(t->n)); if (rc) return rc;
-    SDCAB_CUDA_TRY(cudaMemset(t_keep, 0, static_cast<size_t>(t->n) * sizeof(double)));
+    SDCAB_CUDA_TRY(cudaMemsetAsync(t_keep, 0, static_cast<size_t>(t->n) * sizeof(double), buf.stream));
     if (t->input_kind != SDCAB_INPUT_KERNEL) {
       rc = buf.alloc(&g_parts, static_cast<size_t>(g_slices) * kBlockSteps * kBlockSteps); if (rc) return rc;
       rc = buf.alloc(&D, static_cast<size_t>(kBlockSteps) * m); if (rc) return rc;
