@@ -10,6 +10,7 @@
 #include <cstring>
 
 #include "common_host.h"
+#include "entropic_rows.cuh"
 #include "fast_rows.cuh"
 #include "prox_core.cuh"
 #include "prox_names.h"
@@ -135,11 +136,27 @@ int launch_rows(const Data* a, Data* out, int m, long long n, const ProxParams& 
   return SDCAB_OK;
 }
 
+// Float rows of the entropic projections go to the grouped kernel when the
+// launch qualifies (same alignment rules as the register rows).
+template <typename R>
+int try_entropic_rows(int prox, const float* a, float* out, int m, long long n,
+                      const ProxParams& q, cudaStream_t stream) {
+  if (m % 4 != 0 || m < 8) return kNoFastPath;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15) return kNoFastPath;
+  return launch_entropic_rows<R>(prox, a, out, m, n, q, stream);
+}
+template <typename R>
+int try_entropic_rows(int, const double*, double*, int, long long, const ProxParams&, cudaStream_t) {
+  return kNoFastPath;
+}
+
 template <typename Data, typename R>
 int dispatch_prox(int prox, const Data* a, Data* out, int m, long long n, const ProxParams& q,
                   sdcab_thresholds* thr_out, int apply, cudaStream_t stream) {
   if (apply && !thr_out) {
-    int rc = launch_fast_rows<Data, R>(prox, a, out, m, n, q, stream);
+    int rc = try_entropic_rows<R>(prox, a, out, m, n, q, stream);
+    if (rc != kNoFastPath) return rc;
+    rc = launch_fast_rows<Data, R>(prox, a, out, m, n, q, stream);
     if (rc != kNoFastPath) return rc;
   }
   switch (prox) {

@@ -81,6 +81,40 @@ def test_config3_entropy_f32(ref, cuda_lib, name, kw):
     assert scaled_error(x, x_ref, a).max() <= 1e-5
 
 
+@pytest.mark.parametrize("name", ["entropy", "topk_entropy"])
+@pytest.mark.parametrize("precision", ["double", "float"])
+def test_grouped_entropic_rows_match_reference(ref, cuda_lib, name, precision):
+    """Enough float rows for the kernel that batches the scalar work of the entropic
+    projections over groups of rows (it wants a group for every resident warp).  All
+    regimes are shuffled into one matrix, so that a group mixes rows of the closed
+    forms with rows that are handed to the general routine."""
+    rng = np.random.default_rng(stable_seed(name, precision, 7))
+    for m in (36, 200, 400):
+        a = np.concatenate([regime(rng, 8000, m, np.float32, kind)
+                            for kind in ("normal", "pos", "neg", "mixed", "ties")])
+        rng.shuffle(a, axis=0)
+        if name == "entropy":
+            variants = [dict(hi=1.0, rhs=1.0), dict(hi=0.05, rhs=1.0), dict(hi=0.4, rhs=0.7)]
+        else:
+            variants = [dict(k=1), dict(k=3), dict(k=10), dict(k=min(30, m // 2))]
+        for kw in variants:
+            x = run_dev(cuda_lib, name, a, precision=precision, **kw)
+            x_ref = ref.prox(name, a, result=precision, **kw)
+            tol = tolerance(np.float32, precision, m)
+            if precision == "double":
+                err = scaled_error(x, x_ref, a).max()
+                assert err <= tol, (name, m, kw, err)
+            else:
+                ok, err = float_precision_ok(x, x_ref, ref.prox(name, a, result="double", **kw), a, tol)
+                assert ok, (name, m, kw, err)
+            # in place and out of place agree bit for bit
+            import torch
+            src = torch.from_numpy(a).cuda()
+            dst = torch.empty_like(src)
+            cuda_lib.prox_to(src, dst, name, precision=precision, **kw)
+            assert np.array_equal(dst.cpu().numpy(), x)
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_config3_lambert(ref, cuda_lib, dtype):
     import torch
