@@ -548,6 +548,53 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
   return kFastNeedsFullRow;
 }
 
+// ---- knapsack with lo = 0 (the simplex of include/sdca/prox/knapsack_eq.h) -----
+// When no entry reaches the upper bound, the solution has t >= max - rhs (the
+// largest entry alone contributes max - t <= rhs), so the support lies among the
+// entries above max - rhs: a handful for rows whose entries are not bunched at
+// the top.  Those are compacted to one per lane; every lane ranks its entry
+// among the candidates and sums the candidates ranked before it in one pass of
+// broadcasts (no sort), which gives the threshold of every possible support
+// size at once: t_j = (sum of the j largest - rhs) / j, and the support is the
+// largest j whose j-th largest entry exceeds t_j.  The reference reaches the
+// same t by Kiwiel's variable fixing, several dependent reductions over the row.
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ FastStatus fast_knapsack_eq(const RegRow<Data, NV>& row, R hi, R rhs,
+                                                       Data* slots, int* counter, int lane,
+                                                       Thr<R>& thr) {
+  Data lm = -num<Data>::inf();
+  row.for_each([&](Data x, int) { lm = max_(lm, x); });
+  // a lower bound of the maximum through the one-instruction float reduction
+  const float below = warp_max_fast(round_down(lm, float()));
+  if (!(below > -num<float>::inf())) return kFastNeedsFullRow;
+  const R below_r = static_cast<R>(below);
+  const Data cut = round_down(below_r - rhs - (abs_(below_r) + rhs) * num<R>::eps() * 4, Data());
+  LaneRow<Data> cand;
+  const int total = compact_candidates(row, cut, slots, counter, lane, cand);
+  if (total > 32 || total < 1) return kFastNeedsFullRow;
+  const bool mine = lane < total;
+  const R v = static_cast<R>(cand.x);
+  int rank = 0;
+  R before = 0;                       // sum of the candidates ranked before this one
+  for (int j = 0; j < total; ++j) {
+    const R vj = __shfl_sync(kFullMask, v, j);
+    const bool first = (vj > v) || (vj == v && j < lane);
+    rank += first ? 1 : 0;
+    before += first ? vj : R(0);
+  }
+  const R t_mine = over_count(before + v - rhs, rank + 1);
+  const bool inside = mine && v > t_mine;
+  int size = inside ? rank + 1 : 0;
+  size = __reduce_max_sync(kFullMask, size);
+  if (size < 1) return kFastNeedsFullRow;
+  const unsigned who = __ballot_sync(kFullMask, mine && rank == size - 1);
+  const R t = __shfl_sync(kFullMask, t_mine, __ffs(who) - 1);
+  // an entry at the upper bound: the general routine fixes it first
+  if (__any_sync(kFullMask, mine && v - t > hi)) return kFastNeedsFullRow;
+  thr = make_thr(t, R(0), hi, 0, size, hi + t, t);
+  return kFastDone;
+}
+
 // ---- entropic projections of float rows --------------------------------------
 // For float data the stated accuracy of outputs and thresholds is 1e-5, so the
 // m exponentials of a log-sum-exp are evaluated in float (1e-7 each) and added
@@ -737,7 +784,11 @@ fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long
         __syncwarp();
       }
     } else {
-      thr = compute_thresholds<R>(PROX, row, q);
+      bool done = false;
+      if (PROX == kKnapsackEq && q.lo == 0 && q.hi > 0 && q.rhs > 0)
+        done = fast_knapsack_eq<R>(row, static_cast<R>(q.hi), static_cast<R>(q.rhs), slots, counter,
+                                   lane, thr) == kFastDone;
+      if (!done) thr = compute_thresholds<R>(PROX, row, q);
     }
     Applier<Data> f(thr, prox_map(PROX), q.alpha);
     if (kTwice) {

@@ -47,6 +47,31 @@ def test_config1_simplex_f64(ref, cuda_lib):
     assert np.abs(x.sum(axis=1) - 1).max() < 1e-12
 
 
+@pytest.mark.parametrize("dtype,precision", [(np.float64, "double"), (np.float32, "double"),
+                                              (np.float32, "float")])
+def test_simplex_candidate_path_matches_reference(ref, cuda_lib, dtype, precision):
+    """knapsack_eq with lo = 0: rows whose support lies among the few entries above
+    max - rhs are solved on those candidates; rows with an entry at the upper bound,
+    with more than 32 candidates or with ties take the general routine or must agree
+    with it."""
+    rng = np.random.default_rng(stable_seed("simplex-candidates", str(dtype), precision))
+    for m in (8, 100, 200, 512):
+        a = np.concatenate([regime(rng, 300, m, dtype, kind)
+                            for kind in ("normal", "pos", "neg", "mixed", "ties")])
+        for kw in (dict(lo=0.0, hi=1.0, rhs=1.0), dict(lo=0.0, hi=1e30, rhs=0.3),
+                   dict(lo=0.0, hi=0.4, rhs=1.0), dict(lo=0.0, hi=3.0, rhs=5.0)):
+            x = run_dev(cuda_lib, "knapsack_eq", a, precision=precision, **kw)
+            x_ref = ref.prox("knapsack_eq", a, result=precision, **kw)
+            tol = tolerance(dtype, precision, m)
+            if precision == "double":
+                err = scaled_error(x, x_ref, a).max()
+                assert err <= tol, (m, kw, err)
+                assert np.abs(x.sum(axis=1, dtype=np.float64) - kw["rhs"]).max() <= max(tol, 1e-6 if dtype == np.float32 else 0) * max(1.0, kw["rhs"]) * m
+            else:
+                ok, err = float_precision_ok(x, x_ref, ref.prox("knapsack_eq", a, result="double", **kw), a, tol)
+                assert ok, (m, kw, err)
+
+
 @pytest.mark.parametrize("name,kw", [("topk_simplex", dict(k=5, rhs=1.0)), ("topk_cone", dict(k=5))])
 @pytest.mark.parametrize("precision", ["double", "float"])
 def test_config2_topk_f32_with_ties(ref, cuda_lib, name, kw, precision):
