@@ -51,6 +51,10 @@ PROX_CONFIGS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of fast_rows_kernel<float,double,top-k simplex,8>
 # per row, from the ncu capture summarised in profiles/ (263.1 MB + 209.4 MB over 65536 rows)
 NCU_DRAM_BYTES_PER_ROW = 4015 + 3195
+# Config 3 (m = 200 float32), same kind of capture on 131072 rows: dram bytes read + written
+# per row while the kernel runs (the rest of the 800 B output per row leaves L2 afterwards).
+NCU_DRAM_BYTES_PER_ROW_CONFIG3 = {"topk_entropy(k=1)": 801 + 393, "topk_entropy(k=10)": 801 + 390,
+                                  "entropy": 801 + 384, "lambert_w_exp": 800 + 479}
 
 
 def measured_peak_gbs():
@@ -239,7 +243,10 @@ def other_prox_config(args, rank, world, local_rank):
                    "thresholds_precision": args.precision,
                    "l2": "rotating buffers" if rows * m * dtype.itemsize < (256 << 20) else "inputs exceed L2"},
         "roofline": {"bound": "hbm", "achieved": per_op[slow]["gbs"], "peak": peak, "unit": "GB/s",
-                     "frac": per_op[slow]["frac"], "traffic": None, "kernel": slow,
+                     "frac": per_op[slow]["frac"],
+                     "traffic": (rows * NCU_DRAM_BYTES_PER_ROW_CONFIG3[slow]
+                                 if args.config == 3 and m == 200 else None),
+                     "kernel": slow,
                      "peak_kind": "of " + peak_kind, "per_operator": per_op},
         "cpu_baseline": cpu, "gpu_launches": len(per_op) * max(args.steps, 10)}))
 
