@@ -48,11 +48,26 @@ struct GroupResult {
   bool full;
 };
 
+// Moves the largest of cand[u .. total) to position u (one step of a selection
+// sort): phase B orders only as many candidates as its search over U visits, and
+// does so on one lane per row, where phase A would sort all of them on a warp.
+__device__ __forceinline__ float select_next(float* cand, int u, int total) {
+  float best = cand[u];
+  int where = u;
+  for (int j = u + 1; j < total; ++j) {
+    const float c = cand[j];
+    if (c > best) { best = c; where = j; }
+  }
+  cand[where] = cand[u];
+  cand[u] = best;
+  return best;
+}
+
 // Phase B of the top-k entropy projection for one row: the same closed forms as
 // fast_topk_entropy, the sizes of U tried one after the other by this lane.
 template <typename R>
 __device__ __forceinline__ GroupResult<R> grouped_topk_entropy(R S, float mxf, int total,
-                                                               const float* cand, int k,
+                                                               float* cand, int k,
                                                                const R* log_of) {
   GroupResult<R> out;
   out.full = false;
@@ -72,13 +87,14 @@ __device__ __forceinline__ GroupResult<R> grouped_topk_entropy(R S, float mxf, i
     return out;
   }
   const int last = min(k - 1, total - 1);
-  R pe_prev = static_cast<R>(exp_(cand[0] - mxf));   // sum of the exponentials of U
-  R s_prev = static_cast<R>(cand[0]);                // smallest entry of U
+  const float top = select_next(cand, 0, total);
+  R pe_prev = static_cast<R>(exp_(top - mxf));       // sum of the exponentials of U
+  R s_prev = static_cast<R>(top);                    // smallest entry of U
   R sum_U = s_prev;
   R zs = 0, log_zs = 0, cur_max = 0;
   int ustar = last;
   for (int u = 1; u <= last; ++u) {
-    const float sf = cand[u];
+    const float sf = select_next(cand, u, total);
     const R s = static_cast<R>(sf);
     const R rest = S - pe_prev;                      // relative to the old maximum
     // a rest that is a small fraction of the whole sum has lost too many digits
@@ -148,12 +164,12 @@ entropic_grouped_kernel(const float* __restrict__ a, float* __restrict__ out, in
       row_max_and_expsum<R, NV>(row, mxf, lm, S);
       int total = 0;
       if (kTopkForm && k > 1 && !(S > certain)) {
-        // the k + 1 largest entries, sorted, for phase B
+        // the entries that can be among the k + 1 largest, for phase B
         const float tau = kth_largest_of_lanes(lm, k, lane);
         const float cut = (tau > -num<float>::inf()) ? nextafterf(tau, -num<float>::inf()) : tau;
         LaneRow<float> cand;
         total = compact_candidates(row, cut, slots, counter, lane, cand);
-        if (total <= 32) sc.cand[kTopkForm ? i : 0][lane] = warp_sort_desc(cand.x, lane);
+        if (total <= 32) sc.cand[kTopkForm ? i : 0][lane] = cand.x;
       }
       if (lane == 0) {
         sc.sum_or_t[i] = S;
