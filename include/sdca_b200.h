@@ -301,7 +301,10 @@ typedef struct sdcab_fit_criteria {
   int64_t max_epoch;
   int64_t eval_epoch;     /* evaluate every eval_epoch epochs; 0: only at the end   */
   int32_t eval_on_start;
-  int32_t reserved;
+  int32_t recompute_primal; /* feature input: rebuild W = [W0 +] X A' before every
+                             * evaluation, as the reference does when it is compiled with
+                             * SDCA_ACCURATE_MATH (include/sdca/solver/eval/core.h:148-182);
+                             * 0 = the reference's default build                       */
 } sdcab_fit_criteria;
 
 typedef struct sdcab_fit_result {
@@ -312,6 +315,19 @@ typedef struct sdcab_fit_result {
   double solve_seconds;   /* device time of the update steps                        */
   double eval_seconds;    /* device time of the evaluations                         */
 } sdcab_fit_result;
+
+/*
+ * Primal variables from dual variables on the current device:
+ * eval_recompute_primal of the reference (include/sdca/solver/eval/core.h:148-182,
+ * sdca_blas_gemm(D, M, N, X, D, A, M, W, NoTrans, Trans[, 1, 1])), W = [W0 +] X A'.
+ * x: d x n column major (features), a: m x n column major (dual variables),
+ * w0: d x m column major or NULL, w: d x m column major (written).  All device
+ * pointers; the sum over the examples runs in a fixed order.
+ */
+int sdcab_primal_from_dual_f32_dev(const float* x, const float* a, const float* w0, float* w,
+                                   int64_t d, int64_t m, int64_t n, void* stream);
+int sdcab_primal_from_dual_f64_dev(const double* x, const double* a, const double* w0, double* w,
+                                   int64_t d, int64_t m, int64_t n, void* stream);
 
 /* The example order of the first num_epochs epochs of the reference's solver
  * for n training examples: a default-seeded std::minstd_rand driving

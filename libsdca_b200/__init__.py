@@ -26,4 +26,5 @@ from .binding import (  # noqa: F401
     make_problem,
     fit_,
     epoch_permutations,
+    primal_from_dual,
 )

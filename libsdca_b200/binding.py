@@ -299,7 +299,7 @@ def eval_finish(objective, m, sums_host):
 
 class FitCriteria(C.Structure):
     _fields_ = [("epsilon", C.c_double), ("max_epoch", C.c_int64), ("eval_epoch", C.c_int64),
-                ("eval_on_start", C.c_int32), ("reserved", C.c_int32)]
+                ("eval_on_start", C.c_int32), ("recompute_primal", C.c_int32)]
 
 
 class FitResult(C.Structure):
@@ -331,15 +331,18 @@ def epoch_permutations(n, num_epochs):
 
 def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
          precision="double", epsilon=1e-3, max_epoch=1000, eval_epoch=10, eval_on_start=False,
-         permutations=None, offsets=None):
+         permutations=None, offsets=None, recompute_primal=False):
     """SDCA fit, in place on ``A`` (n x m) and ``W`` (m x d): torch CUDA tensors use the
     device entry point, numpy arrays the host-buffer one (copies inside).
 
     Mirrors ``matsdca_fit``'s stopping options (src/matlab/mex_solve.cpp:505-528 of the
-    reference); returns status, epochs and the evaluation records."""
+    reference); returns status, epochs and the evaluation records.  ``recompute_primal``
+    rebuilds W from A before every evaluation (features only), which the reference does
+    when it is compiled with SDCA_ACCURATE_MATH."""
     obj = objective if isinstance(objective, Objective) else make_objective(objective, c, gamma, k, precision)
     prob = make_problem(X, labels, A, W, None, offsets, kernel, True)
-    crit = FitCriteria(epsilon, max_epoch, eval_epoch, 1 if eval_on_start else 0, 0)
+    crit = FitCriteria(epsilon, max_epoch, eval_epoch, 1 if eval_on_start else 0,
+                       1 if recompute_primal else 0)
     cap = int(max_epoch) + 4
     evals = (EvalRecord * cap)()
     res = FitResult()
@@ -358,3 +361,23 @@ def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
         _check(fn(C.byref(obj), C.byref(prob), C.byref(crit), perm_ptr, evals, C.c_int64(cap),
                   C.byref(res)), "sdcab_fit")
     return fit_result_to_dict(res, evals)
+
+
+def primal_from_dual(X, A, W0=None, out=None):
+    """W = [W0 +] X A' on the device (eval_recompute_primal of the reference,
+    include/sdca/solver/eval/core.h:148-182).  Torch CUDA tensors in the layouts of
+    ``fit_``: X is n x d (rows = examples), A is n x m, W0 / the result m x d."""
+    import torch
+    n, d = X.shape
+    m = A.shape[1]
+    if A.shape[0] != n or X.dtype != A.dtype or not (X.is_contiguous() and A.is_contiguous()):
+        raise SdcabError(-1, "primal_from_dual: X (n x d) and A (n x m), contiguous, same dtype")
+    if W0 is not None and (tuple(W0.shape) != (m, d) or W0.dtype != X.dtype or not W0.is_contiguous()):
+        raise SdcabError(-1, "primal_from_dual: W0 must be m x d")
+    if out is None:
+        out = torch.empty((m, d), dtype=X.dtype, device=X.device)
+    fn = getattr(lib(), "sdcab_primal_from_dual_%s_dev" % _suffix(str(X.dtype)))
+    _check(fn(C.c_void_p(X.data_ptr()), C.c_void_p(A.data_ptr()),
+              C.c_void_p(W0.data_ptr()) if W0 is not None else None, C.c_void_p(out.data_ptr()),
+              C.c_int64(d), C.c_int64(m), C.c_int64(n), _torch_stream()), "sdcab_primal_from_dual")
+    return out

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libsdca_b200.so")
 OBJ_DIR = os.path.join(HERE, "build")
-SOURCES = ["api.cu", "prox.cu", "eval.cu", "fit.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "prox.cu", "eval.cu", "fit.cu", "primal.cu", "noalloc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr"]
 
@@ -50,7 +50,7 @@ def build(force=False, verbose=False):
             raise RuntimeError("nvcc failed on " + src)
         return obj
 
-    with ThreadPoolExecutor(max_workers=4) as pool:
+    with ThreadPoolExecutor(max_workers=5) as pool:
         objs = list(pool.map(compile_one, srcs))
     with open(os.path.join(OBJ_DIR, "ptxas.log"), "w") as f:
         for k, v in logs.items():

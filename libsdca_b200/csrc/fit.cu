@@ -22,6 +22,7 @@
 #include "eval_host.h"
 #include "fit_host.h"
 #include "gemm_blocked.cuh"
+#include "primal.h"
 #include "update_core.cuh"
 
 namespace sdcab {
@@ -974,7 +975,16 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
   double eval_ms = 0, solve_ms = 0;
   auto evaluate = [&]() -> int {
     SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[2], s));
-    int erc = eval_sums_call<Data>(obj, &ep, sums_dev, s);
+    int erc = SDCAB_OK;
+    if (crit->recompute_primal && train->input_kind == SDCAB_INPUT_FEATURES) {
+      // eval_recompute_primal (eval/core.h:148-182): W rebuilt from A, so that the
+      // rounding of the steps' rank-one updates does not accumulate in it
+      erc = primal_from_dual_dev<Data>(static_cast<const Data*>(train->x), static_cast<const Data*>(train->a),
+                                       static_cast<const Data*>(train->w0),
+                                       static_cast<Data*>(const_cast<void*>(train->w)), train->d, m, n, s);
+      if (erc) return erc;
+    }
+    erc = eval_sums_call<Data>(obj, &ep, sums_dev, s);
     if (erc) return erc;
     SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[3], s));
     SDCAB_CUDA_TRY(cudaMemcpyAsync(sums.data(), sums_dev, sums.size() * sizeof(double),

@@ -26,12 +26,13 @@ def run_both(ref, mod, objective, data, labels, m, kernel, dtype, permutations=N
     n, d = data.shape
     fit_kw = dict(epsilon=kw.pop("epsilon", 1e-3), max_epoch=kw.pop("max_epoch", 30),
                   eval_epoch=kw.pop("eval_epoch", 1), eval_on_start=kw.pop("eval_on_start", False))
+    recompute = kw.pop("recompute_primal", False)   # the reference's build here is the default one
     A_ref = np.zeros((n, m), dtype=dtype); W_ref = np.zeros((m, d), dtype=dtype)
     r = ref.fit(objective, data, A_ref, labels, W=None if kernel else W_ref, kernel=kernel,
                 **fit_kw, **kw)
     A = dev(np.zeros((n, m), dtype=dtype)); W = None if kernel else dev(np.zeros((m, d), dtype=dtype))
     g = mod.fit_(IDS[objective], dev(data), dev(labels), A, W=W, kernel=kernel,
-                 permutations=permutations, **fit_kw, **kw)
+                 permutations=permutations, recompute_primal=recompute, **fit_kw, **kw)
     return r, g, A_ref, W_ref, A.cpu().numpy(), None if kernel else W.cpu().numpy()
 
 
@@ -198,3 +199,43 @@ def test_host_buffer_fit(ref, cuda_lib):
     bad = labels.copy(); bad[3] = 6
     with pytest.raises(SdcabError):
         cuda_lib.fit_(0, X, bad, A, W=W, c=1.0, max_epoch=1)
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_primal_from_dual_matches_matrix_product(cuda_lib, dtype):
+    """W = [W0 +] X A' (eval_recompute_primal of the reference): ragged tiles, a
+    launch that splits the examples into slices, with and without W0."""
+    import torch
+    rng = np.random.default_rng(stable_seed("primal-from-dual", str(dtype)))
+    for d, m, n in ((5, 3, 7), (128, 100, 1000), (300, 70, 4097), (4100, 10, 33), (1, 1, 1)):
+        X = rng.standard_normal((n, d)).astype(dtype)
+        A = rng.standard_normal((n, m)).astype(dtype)
+        W0 = rng.standard_normal((m, d)).astype(dtype)
+        exact = A.astype(np.float64).T @ X.astype(np.float64)
+        scale = np.abs(A.astype(np.float64)).T @ np.abs(X.astype(np.float64)) + 1.0
+        tol = 1e-13 if dtype == np.float64 else 2e-6
+        W = cuda_lib.primal_from_dual(dev(X), dev(A)).cpu().numpy()
+        assert (np.abs(W - exact) <= tol * np.sqrt(n) * scale).all(), (d, m, n)
+        W = cuda_lib.primal_from_dual(dev(X), dev(A), W0=dev(W0)).cpu().numpy()
+        assert (np.abs(W - (exact + W0)) <= tol * np.sqrt(n) * (scale + np.abs(W0))).all(), (d, m, n, "W0")
+        # the same call twice gives the same bits (fixed summation order)
+        again = cuda_lib.primal_from_dual(dev(X), dev(A), W0=dev(W0)).cpu().numpy()
+        assert np.array_equal(W, again)
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_feature_fit_with_recomputed_primal(ref, cuda_lib, dtype):
+    """recompute_primal (the reference's SDCA_ACCURATE_MATH build rebuilds W from A
+    before every evaluation): same fit within the tolerance of the default build, and
+    the W it returns is X A' of the A it returns."""
+    rng = np.random.default_rng(stable_seed("gpu-fit-recompute", str(dtype)))
+    tol = 1e-9 if dtype == np.float64 else 2e-4
+    for objective in ("l2_topk_hinge", "l2_entropy_topk"):
+        X, labels, _ = random_problem(rng, 500, 60, 30, dtype, False)
+        out = run_both(ref, cuda_lib, objective, X, labels, 30, False, dtype, c=0.7, gamma=1.0, k=2,
+                       max_epoch=8, eval_epoch=2, recompute_primal=True)
+        compare(*out, tol, (objective, "recompute"))
+        A, W = out[4], out[5]
+        exact = A.astype(np.float64).T @ X.astype(np.float64)
+        wtol = 1e-12 if dtype == np.float64 else 1e-5
+        assert np.abs(W - exact).max() <= wtol * max(1.0, np.abs(exact).max()) * 30
