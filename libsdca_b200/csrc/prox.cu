@@ -220,7 +220,9 @@ int prox_host(const char* name, const Data* a, long long m, long long n,
   const bool want_thr = (thr != nullptr);
   const int per_row_thr = (prox == kTwoSimplex) ? 2 : 1;
   const size_t row_bytes = static_cast<size_t>(m) * sizeof(Data);
-  const size_t target = static_cast<size_t>(64) << 20;
+  // 32 MiB per chunk measured best on PCIe Gen5 (64 MiB: 6 % slower, more of the
+  // transfer runs one-directional at the ends; 16 MiB and below: slower again)
+  const size_t target = static_cast<size_t>(32) << 20;
   long long rows_per_chunk = std::max<long long>(1, static_cast<long long>(target / row_bytes));
   rows_per_chunk = std::min(rows_per_chunk, n);
   const int kBuf = 3;
