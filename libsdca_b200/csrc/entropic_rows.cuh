@@ -21,6 +21,8 @@
 
 namespace sdcab {
 
+// Bytes of rows that all resident blocks together hold between phases A and C
+// (32 MB and more measured equal on a 126 MB L2, less was slower).
 #ifndef SDCAB_GROUP_FOOTPRINT
 #define SDCAB_GROUP_FOOTPRINT (32ll << 20)
 #endif
