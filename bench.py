@@ -566,9 +566,17 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-        time.sleep(0.3)
-    # the sampler's start-up leaves the GPU idle for 0.3 s: the W untimed warm-up steps
-    # run again here, so that the timed region starts on a busy GPU
+
+    def keep_busy(samples_wanted, limit_s):
+        # untimed steps until nvidia-smi has delivered its samples: they are taken while
+        # the kernels of the timed region run (the region itself lasts a few milliseconds)
+        t0 = time.perf_counter()
+        while sampler and len(sampler.samples) < samples_wanted and time.perf_counter() - t0 < limit_s:
+            step()
+            torch.cuda.synchronize()
+
+    keep_busy(2, 3.0)
+    # the W untimed warm-up steps run again here, so that the timed region starts on a busy GPU
     for _ in range(warmup):
         step()
     barrier()
@@ -579,6 +587,7 @@ def main():
     e1.record()
     barrier()
     elapsed_ms = max_over_ranks(e0.elapsed_time(e1))
+    keep_busy(4, 1.5)
     clocks = sampler.finish() if sampler else None
 
     # end to end through the host-buffer C ABI: pinned host in, pinned host out
