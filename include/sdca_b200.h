@@ -244,11 +244,14 @@ int sdcab_eval_sums_f64_dev(const sdcab_objective* obj, const sdcab_problem* p,
  *   - The first call on a device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current) and caches it; make that
  *     first call before any stream capture begins.
- *   - The number of classes is limited: 32 score rows, the rank histogram and
- *     the partial sums must fit the array (about 130 000 float or 65 000 double
- *     classes).  Beyond that the call returns SDCAB_ERR_TOO_LARGE and
- *     sdcab_eval_fixed_scratch_error() holds the reason.  n is not limited:
- *     examples go through the array in chunks.
+ *   - The number of classes is limited by the smaller of two bounds: 32 score
+ *     rows, the rank histogram and the partial sums must fit the array (about
+ *     130 000 float or 65 000 double classes), and four score rows must fit the
+ *     shared memory of a thread block of the loss stage (about 14 000 float or
+ *     7 000 double classes on a B200) -- the second one binds first.  Beyond
+ *     either the call returns SDCAB_ERR_TOO_LARGE and
+ *     sdcab_eval_fixed_scratch_error() holds the reason (it is cleared by a call
+ *     that succeeds).  n is not limited: examples go through the array in chunks.
  *   - All calls on a device share the one array, which keeps what the last call
  *     left in it; the call clears what it accumulates into.  Two calls that
  *     overlap on the GPU (different streams, different host threads) race on
@@ -268,7 +271,15 @@ const char* sdcab_eval_fixed_scratch_error(void);
 int sdcab_eval_finish(const sdcab_objective* obj, int64_t m, const double* sums,
                       sdcab_eval_record* record, double* accuracy);
 
-/* Whole evaluation with host buffers on the current device (copies inside). */
+/* Whole evaluation with host buffers on the current device (copies inside; the
+ * examples are streamed through the device in chunks, uploads overlapping the
+ * evaluation).  For a shard of a training set `a` points at the whole A and
+ * a_row_offset names the shard's first example in it.  Labels and offsets are
+ * checked as the reference checks them (include/sdca/solver/data/output.h:169-215:
+ * range, offsets[0] == 0, between 1 and m - 1 labels per example, labels of an
+ * example strictly increasing) and rejected with SDCAB_ERR_LABELS_RANGE; the
+ * *_dev entry points trust the labels they are given.  Calls from several host
+ * threads on one device are serialised. */
 int sdcab_eval_f32(const sdcab_objective* obj, const sdcab_problem* host_problem,
                    sdcab_eval_record* record, double* accuracy);
 int sdcab_eval_f64(const sdcab_objective* obj, const sdcab_problem* host_problem,
@@ -294,8 +305,7 @@ enum {
   SDCAB_FIT_FAILED = 7
 };
 
-/* stopping_criteria of the reference (include/sdca/solver/solverdef.h:50-57)
- * without the time limits. */
+/* stopping_criteria of the reference (include/sdca/solver/solverdef.h:50-57). */
 typedef struct sdcab_fit_criteria {
   double epsilon;         /* relative duality gap to reach                          */
   int64_t max_epoch;
@@ -305,6 +315,11 @@ typedef struct sdcab_fit_criteria {
                              * evaluation, as the reference does when it is compiled with
                              * SDCA_ACCURATE_MATH (include/sdca/solver/eval/core.h:148-182);
                              * 0 = the reference's default build                       */
+  double max_cpu_time;    /* seconds of processor time of the calling process (std::clock,
+                           * like the reference's stopwatch); 0 = no limit            */
+  double max_wall_time;   /* seconds of wall-clock time; 0 = no limit.  Both limits are
+                           * checked where the reference checks them, after every epoch
+                           * (include/sdca/solver/eval.h:95-107)                       */
 } sdcab_fit_criteria;
 
 typedef struct sdcab_fit_result {
@@ -314,6 +329,8 @@ typedef struct sdcab_fit_result {
   int64_t num_evals;      /* records written to `evals`                             */
   double solve_seconds;   /* device time of the update steps                        */
   double eval_seconds;    /* device time of the evaluations                         */
+  double cpu_seconds;     /* processor time of the calling process inside the fit   */
+  double wall_seconds;    /* wall-clock time inside the fit                         */
 } sdcab_fit_result;
 
 /*
@@ -379,6 +396,19 @@ int sdcab_fit_f32(const sdcab_objective* obj, const sdcab_problem* host_train,
 int sdcab_fit_f64(const sdcab_objective* obj, const sdcab_problem* host_train,
                   const sdcab_fit_criteria* criteria, const int64_t* permutations,
                   sdcab_eval_record* evals, int64_t evals_cap, sdcab_fit_result* result);
+
+/* ------------------------------------------------------------- testing ---- */
+
+/* Switches for the library's own tests; production code never needs them.
+ *   "eval_chunk", n    examples per chunk of an evaluation (0 = automatic), so
+ *                      that small problems run the chunk loop
+ *   "gemm_simt", 0|1   1: score products on the CUDA cores even where the
+ *                      tensor-core kernel applies
+ *   "gemm_lose_a_tile", 0|1   1: the tensor-core product skips one operand tile
+ *                      and runs with a short wait limit, so that one of its bounded
+ *                      waits runs out and the call reports SDCAB_ERR_TIMEOUT
+ * Returns SDCAB_ERR_ARG for an unknown name.  Not thread safe. */
+int sdcab_test_set(const char* name, int64_t value);
 
 /* ------------------------------------------------------------- memory ---- */
 

@@ -299,13 +299,15 @@ def eval_finish(objective, m, sums_host):
 
 class FitCriteria(C.Structure):
     _fields_ = [("epsilon", C.c_double), ("max_epoch", C.c_int64), ("eval_epoch", C.c_int64),
-                ("eval_on_start", C.c_int32), ("recompute_primal", C.c_int32)]
+                ("eval_on_start", C.c_int32), ("recompute_primal", C.c_int32),
+                ("max_cpu_time", C.c_double), ("max_wall_time", C.c_double)]
 
 
 class FitResult(C.Structure):
     _fields_ = [("status", C.c_int32), ("reserved", C.c_int32), ("epoch", C.c_int64),
                 ("num_evals", C.c_int64), ("solve_seconds", C.c_double),
-                ("eval_seconds", C.c_double)]
+                ("eval_seconds", C.c_double), ("cpu_seconds", C.c_double),
+                ("wall_seconds", C.c_double)]
 
 
 FIT_STATUS = ("none", "solving", "solved", "no_progress", "max_epoch", "max_cpu_time",
@@ -316,7 +318,8 @@ def fit_result_to_dict(res, evals):
     count = min(res.num_evals, len(evals))
     return dict(status=FIT_STATUS[res.status], status_code=res.status, epoch=res.epoch,
                 num_evals=res.num_evals, solve_seconds=res.solve_seconds,
-                eval_seconds=res.eval_seconds,
+                eval_seconds=res.eval_seconds, cpu_seconds=res.cpu_seconds,
+                wall_seconds=res.wall_seconds,
                 history=[{f: getattr(evals[i], f) for f in RECORD_FIELDS} for i in range(count)])
 
 
@@ -331,7 +334,8 @@ def epoch_permutations(n, num_epochs):
 
 def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
          precision="double", epsilon=1e-3, max_epoch=1000, eval_epoch=10, eval_on_start=False,
-         permutations=None, offsets=None, recompute_primal=False):
+         permutations=None, offsets=None, recompute_primal=False, W0=None,
+         max_cpu_time=0.0, max_wall_time=0.0):
     """SDCA fit, in place on ``A`` (n x m) and ``W`` (m x d): torch CUDA tensors use the
     device entry point, numpy arrays the host-buffer one (copies inside).
 
@@ -340,9 +344,9 @@ def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
     rebuilds W from A before every evaluation (features only), which the reference does
     when it is compiled with SDCA_ACCURATE_MATH."""
     obj = objective if isinstance(objective, Objective) else make_objective(objective, c, gamma, k, precision)
-    prob = make_problem(X, labels, A, W, None, offsets, kernel, True)
+    prob = make_problem(X, labels, A, W, W0, offsets, kernel, True)
     crit = FitCriteria(epsilon, max_epoch, eval_epoch, 1 if eval_on_start else 0,
-                       1 if recompute_primal else 0)
+                       1 if recompute_primal else 0, max_cpu_time, max_wall_time)
     cap = int(max_epoch) + 4
     evals = (EvalRecord * cap)()
     res = FitResult()
@@ -361,6 +365,11 @@ def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
         _check(fn(C.byref(obj), C.byref(prob), C.byref(crit), perm_ptr, evals, C.c_int64(cap),
                   C.byref(res)), "sdcab_fit")
     return fit_result_to_dict(res, evals)
+
+
+def test_set(name, value):
+    """Switches for the library's own tests (``sdcab_test_set``)."""
+    _check(lib().sdcab_test_set(name.encode(), C.c_int64(int(value))), "sdcab_test_set(%s)" % name)
 
 
 def primal_from_dual(X, A, W0=None, out=None):

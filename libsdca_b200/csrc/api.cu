@@ -18,7 +18,6 @@ int record_cuda_error(cudaError_t err, const char* what) {
   return SDCAB_ERR_CUDA;
 }
 
-static const int kMaxDevices = 64;
 static DeviceInfo g_info[kMaxDevices];
 static std::mutex g_mutex;
 
@@ -56,6 +55,50 @@ int workspace_reserve(int slot, size_t bytes, void** out) {
   return SDCAB_OK;
 }
 
+static Workspace g_pinned[kMaxDevices];
+
+int pinned_reserve(size_t bytes, void** out) {
+  int dev = -1;
+  SDCAB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return SDCAB_ERR_ARG;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  Workspace& w = g_pinned[dev];
+  if (w.bytes < bytes) {
+    if (w.ptr) { cudaFreeHost(w.ptr); w.ptr = nullptr; w.bytes = 0; }
+    SDCAB_CUDA_TRY(cudaHostAlloc(&w.ptr, bytes, cudaHostAllocDefault));
+    w.bytes = bytes;
+  }
+  *out = w.ptr;
+  return SDCAB_OK;
+}
+
+struct StreamSet {
+  cudaStream_t s[4] = {nullptr, nullptr, nullptr, nullptr};
+};
+static PerDevice<StreamSet> g_streams;
+
+int pipeline_streams(int count, cudaStream_t* out) {
+  int dev = -1;
+  SDCAB_CUDA_TRY(cudaGetDevice(&dev));
+  StreamSet* set = g_streams.get(dev);
+  if (!set || count < 0 || count > 4) return SDCAB_ERR_ARG;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (int i = 0; i < count; ++i) {
+    if (!set->s[i]) SDCAB_CUDA_TRY(cudaStreamCreateWithFlags(&set->s[i], cudaStreamNonBlocking));
+    out[i] = set->s[i];
+  }
+  return SDCAB_OK;
+}
+
+static PerDevice<std::mutex> g_call_mutex;
+
+std::mutex* host_call_mutex() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+  std::mutex* m = g_call_mutex.get(dev);
+  return m ? m : g_call_mutex.get(0);
+}
+
 static int workspace_release_all() {
   int dev = -1;
   SDCAB_CUDA_TRY(cudaGetDevice(&dev));
@@ -66,6 +109,8 @@ static int workspace_release_all() {
     if (w.ptr) cudaFree(w.ptr);
     w.ptr = nullptr; w.bytes = 0;
   }
+  if (g_pinned[dev].ptr) cudaFreeHost(g_pinned[dev].ptr);
+  g_pinned[dev].ptr = nullptr; g_pinned[dev].bytes = 0;
   return SDCAB_OK;
 }
 

@@ -6,8 +6,10 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <mutex>
 
 #include "../../include/sdca_b200.h"
+#include "per_device.h"
 
 namespace sdcab {
 
@@ -30,11 +32,21 @@ int get_device_info(DeviceInfo* info);
 
 // Grow-only per-device scratch owned by the library; used only by the
 // host-buffer entry points (the *_dev entry points allocate nothing unless
-// their documentation says so).  Not thread safe across host threads.
+// their documentation says so).  The table is guarded by a mutex, and the
+// host-buffer entry points hold host_call_mutex() of their device while they
+// use the scratch, so concurrent calls from several host threads are
+// serialised per device rather than racing on it.
 struct Workspace {
   void* ptr = nullptr;
   size_t bytes = 0;
 };
 int workspace_reserve(int slot, size_t bytes, void** out);
+// Same for page-locked host memory (staging of small results).
+int pinned_reserve(size_t bytes, void** out);
+// `count` (at most 4) non-blocking streams of the current device, created on
+// first use on that device and kept for the life of the process.
+int pipeline_streams(int count, cudaStream_t* out);
+// The mutex that serialises host-buffer calls on the current device.
+std::mutex* host_call_mutex();
 
 }  // namespace sdcab

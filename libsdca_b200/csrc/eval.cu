@@ -226,15 +226,23 @@ struct EvalLayout {
   size_t err_offset;     // one int: error word of the tensor-core GEMM
 };
 
+// Settings that only tests change (sdcab_test_set): a forced chunk length so that
+// small problems exercise the chunk loop, and the CUDA-core product in place of the
+// tensor-core one.  0 / 0 is the library's normal behaviour.
+static long long g_test_eval_chunk = 0;
+static int g_test_force_simt = 0;
+static int g_test_short_wait = 0;
+
+// Chunks are bounded so that the product's grid (one row of thread blocks per 128
+// examples in grid.y for the CUDA-core kernel) stays inside the launch limits.
+constexpr long long kMaxChunkRows = 65535LL * 64;
+
 static EvalLayout eval_layout(long long n, long long m, long long elem, int sm_count) {
   EvalLayout L;
   const long long budget = 256LL << 20;
   long long chunk = std::max<long long>(128, budget / std::max<long long>(1, m * elem));
-  // test hook: a small chunk exercises the chunk loop on small problems
-  if (const char* env = std::getenv("SDCAB_EVAL_CHUNK")) {
-    const long long forced = std::atoll(env);
-    if (forced > 0) chunk = forced;
-  }
+  if (g_test_eval_chunk > 0) chunk = g_test_eval_chunk;
+  chunk = std::min(chunk, kMaxChunkRows);
   chunk = std::min(chunk, std::max<long long>(n, 1));
   L.chunk = chunk;
   L.scores_bytes = (static_cast<size_t>(chunk) * m * elem + 255) & ~static_cast<size_t>(255);
@@ -268,16 +276,8 @@ static int check_problem(const sdcab_objective* obj, const sdcab_problem* p) {
 
 // scores of examples [first, first + count) into `out` (count x m)
 // The float feature GEMM runs on the tensor cores (gemm_tc.cuh) when the caller
-// provides an error word and the operands meet TMA's alignment rules;
-// SDCAB_GEMM=simt in the environment forces the CUDA-core kernel.
-inline bool tensor_core_gemm_enabled() {
-  static int enabled = -1;
-  if (enabled < 0) {
-    const char* env = std::getenv("SDCAB_GEMM");
-    enabled = (env && std::strcmp(env, "simt") == 0) ? 0 : 1;
-  }
-  return enabled == 1;
-}
+// provides an error word and the operands meet TMA's alignment rules.
+inline bool tensor_core_gemm_enabled() { return g_test_force_simt == 0; }
 
 inline int scores_tc(const float* X, const float* W, float* out, int M, int N, int K, long long ld,
                      int* tc_err, cudaStream_t stream) {
@@ -384,8 +384,13 @@ int eval_sums_dev(const sdcab_objective* obj, const sdcab_problem* p, double* su
   return SDCAB_OK;
 }
 
-// Host buffers: examples are uploaded chunk by chunk; W (or A for a kernel
-// input) stays on the device for the whole call.
+// Host buffers.  W (or A for a kernel input), the labels and W0 stay on the device
+// for the whole call; the examples -- and, for a training set given by features,
+// the rows of A that belong to them -- go through three device buffers on three
+// streams, so that the upload of one chunk overlaps the evaluation of the chunk
+// before it.  Each chunk's sums land in page-locked host memory and are added up
+// in chunk order once the last stream has drained.  Device scratch comes from
+// the library's grow-only workspace, so only the first call of a size allocates.
 template <typename Data>
 int eval_host(const sdcab_objective* obj, const sdcab_problem* hp, sdcab_eval_record* rec,
               double* accuracy) {
@@ -395,63 +400,109 @@ int eval_host(const sdcab_objective* obj, const sdcab_problem* hp, sdcab_eval_re
   const long long m = hp->m, n = hp->n, d = hp->d;
   const bool kernel = (hp->input_kind == SDCAB_INPUT_KERNEL);
   const bool ml = objective_is_multilabel(obj->id);
-  const long long n_a = kernel ? d : n;  // rows of A that matter
+  // include/sdca/solver/data/output.h:169-215: bad labels are an argument error,
+  // they never reach a kernel
+  rc = validate_labels(hp->labels, hp->offsets, n, m, ml);
+  if (rc) return rc;
+  if (hp->a_row_offset < 0) return SDCAB_ERR_ARG_RANGE;
+  if (kernel && hp->is_train && hp->a_row_offset + n > d) return SDCAB_ERR_ARG_RANGE;
+  DeviceInfo info;
+  rc = get_device_info(&info);
+  if (rc) return rc;
+  std::lock_guard<std::mutex> call_lock(*host_call_mutex());
+
   const size_t elem = sizeof(Data);
-  long long chunk = std::max<long long>(1, (128LL << 20) / std::max<long long>(1, d * static_cast<long long>(elem)));
+  const bool a_chunked = hp->is_train && !kernel;  // A rows travel with their examples
+  long long chunk = std::max<long long>(1, (64LL << 20) / std::max<long long>(1, d * static_cast<long long>(elem)));
+  if (g_test_eval_chunk > 0) chunk = g_test_eval_chunk;
   chunk = std::min(chunk, n);
+  const long long num_chunks = (n + chunk - 1) / chunk;
   const long long num_labels = ml ? hp->offsets[n] : n;
   const size_t sums_count = SDCAB_EVAL_SUMS(m);
-  void *dX = nullptr, *dA = nullptr, *dW = nullptr, *dW0 = nullptr, *dLab = nullptr,
-       *dOff = nullptr, *dSums = nullptr;
-  auto release = [&]() {
-    cudaFree(dX); cudaFree(dA); cudaFree(dW); cudaFree(dW0); cudaFree(dLab); cudaFree(dOff);
-    cudaFree(dSums);
-  };
-#define EVAL_TRY(expr)                                                   \
-  do {                                                                   \
-    cudaError_t e__ = (expr);                                            \
-    if (e__ != cudaSuccess) { release(); return record_cuda_error(e__, #expr); } \
-  } while (0)
-  EVAL_TRY(cudaMalloc(&dX, static_cast<size_t>(chunk) * d * elem));
-  if (hp->a) {
-    EVAL_TRY(cudaMalloc(&dA, static_cast<size_t>(n_a) * m * elem));
-    EVAL_TRY(cudaMemcpy(dA, hp->a, static_cast<size_t>(n_a) * m * elem, cudaMemcpyHostToDevice));
-  }
-  if (hp->w) {
-    EVAL_TRY(cudaMalloc(&dW, static_cast<size_t>(d) * m * elem));
-    EVAL_TRY(cudaMemcpy(dW, hp->w, static_cast<size_t>(d) * m * elem, cudaMemcpyHostToDevice));
-  }
-  if (hp->w0) {
-    EVAL_TRY(cudaMalloc(&dW0, static_cast<size_t>(d) * m * elem));
-    EVAL_TRY(cudaMemcpy(dW0, hp->w0, static_cast<size_t>(d) * m * elem, cudaMemcpyHostToDevice));
-  }
-  EVAL_TRY(cudaMalloc(&dLab, static_cast<size_t>(num_labels) * sizeof(int64_t)));
-  EVAL_TRY(cudaMemcpy(dLab, hp->labels, static_cast<size_t>(num_labels) * sizeof(int64_t), cudaMemcpyHostToDevice));
-  if (ml) {
-    EVAL_TRY(cudaMalloc(&dOff, static_cast<size_t>(n + 1) * sizeof(int64_t)));
-    EVAL_TRY(cudaMemcpy(dOff, hp->offsets, static_cast<size_t>(n + 1) * sizeof(int64_t), cudaMemcpyHostToDevice));
-  }
-  EVAL_TRY(cudaMalloc(&dSums, sums_count * sizeof(double)));
-  std::vector<double> total(sums_count, 0.0), part(sums_count);
-  for (long long first = 0; first < n; first += chunk) {
+  constexpr int kBuf = 3;
+  auto round256 = [](size_t b) { return (b + 255) & ~static_cast<size_t>(255); };
+  const EvalLayout L = eval_layout(chunk, m, static_cast<long long>(elem), info.sm_count);
+  const size_t x_bytes = round256(static_cast<size_t>(chunk) * d * elem);
+  const size_t a_chunk_bytes = a_chunked ? round256(static_cast<size_t>(chunk) * m * elem) : 0;
+  const size_t sums_bytes = round256(sums_count * sizeof(double));
+  const size_t slot_bytes = x_bytes + a_chunk_bytes + round256(L.total) + sums_bytes;
+  const size_t a_full_bytes = (kernel && hp->a) ? round256(static_cast<size_t>(d) * m * elem) : 0;
+  const size_t w_bytes = hp->w ? round256(static_cast<size_t>(d) * m * elem) : 0;
+  const size_t w0_bytes = hp->w0 ? w_bytes : 0;
+  const size_t lab_bytes = round256(static_cast<size_t>(num_labels) * sizeof(int64_t));
+  const size_t off_bytes = ml ? round256(static_cast<size_t>(n + 1) * sizeof(int64_t)) : 0;
+  void* arena = nullptr;
+  rc = workspace_reserve(4, kBuf * slot_bytes + a_full_bytes + w_bytes + w0_bytes + lab_bytes + off_bytes,
+                         &arena);
+  if (rc) return rc;
+  void* pinned = nullptr;
+  rc = pinned_reserve(static_cast<size_t>(num_chunks) * sums_bytes, &pinned);
+  if (rc) return rc;
+  cudaStream_t streams[kBuf];
+  rc = pipeline_streams(kBuf, streams);
+  if (rc) return rc;
+
+  unsigned char* base = static_cast<unsigned char*>(arena);
+  unsigned char* slots = base;
+  unsigned char* cur = base + kBuf * slot_bytes;
+  void* dA = nullptr; void* dW = nullptr; void* dW0 = nullptr;
+  if (a_full_bytes) { dA = cur; cur += a_full_bytes; }
+  if (w_bytes) { dW = cur; cur += w_bytes; }
+  if (w0_bytes) { dW0 = cur; cur += w0_bytes; }
+  int64_t* dLab = reinterpret_cast<int64_t*>(cur); cur += lab_bytes;
+  int64_t* dOff = ml ? reinterpret_cast<int64_t*>(cur) : nullptr;
+
+  // resident operands on the first stream; the other streams wait for them
+  cudaStream_t s0 = streams[0];
+  if (dA) SDCAB_CUDA_TRY(cudaMemcpyAsync(dA, hp->a, static_cast<size_t>(d) * m * elem, cudaMemcpyHostToDevice, s0));
+  if (dW) SDCAB_CUDA_TRY(cudaMemcpyAsync(dW, hp->w, static_cast<size_t>(d) * m * elem, cudaMemcpyHostToDevice, s0));
+  if (dW0) SDCAB_CUDA_TRY(cudaMemcpyAsync(dW0, hp->w0, static_cast<size_t>(d) * m * elem, cudaMemcpyHostToDevice, s0));
+  SDCAB_CUDA_TRY(cudaMemcpyAsync(dLab, hp->labels, static_cast<size_t>(num_labels) * sizeof(int64_t),
+                                 cudaMemcpyHostToDevice, s0));
+  if (ml) SDCAB_CUDA_TRY(cudaMemcpyAsync(dOff, hp->offsets, static_cast<size_t>(n + 1) * sizeof(int64_t),
+                                         cudaMemcpyHostToDevice, s0));
+  SDCAB_CUDA_TRY(cudaStreamSynchronize(s0));
+
+  long long index = 0;
+  for (long long first = 0; first < n; first += chunk, ++index) {
     const long long count = std::min(chunk, n - first);
-    EVAL_TRY(cudaMemcpy(dX, static_cast<const Data*>(hp->x) + first * d,
-                        static_cast<size_t>(count) * d * elem, cudaMemcpyHostToDevice));
+    const int slot = static_cast<int>(index % kBuf);
+    cudaStream_t s = streams[slot];
+    // a slot is reused only after the stream that owns it has drained
+    if (index >= kBuf) SDCAB_CUDA_TRY(cudaStreamSynchronize(s));
+    unsigned char* sb = slots + static_cast<size_t>(slot) * slot_bytes;
+    Data* dX = reinterpret_cast<Data*>(sb);
+    Data* dAc = a_chunked ? reinterpret_cast<Data*>(sb + x_bytes) : nullptr;
+    void* ws = sb + x_bytes + a_chunk_bytes;
+    double* dSums = reinterpret_cast<double*>(sb + x_bytes + a_chunk_bytes + round256(L.total));
+    SDCAB_CUDA_TRY(cudaMemcpyAsync(dX, static_cast<const Data*>(hp->x) + first * d,
+                                   static_cast<size_t>(count) * d * elem, cudaMemcpyHostToDevice, s));
     sdcab_problem dp = *hp;
-    dp.x = dX; dp.a = dA; dp.w = dW; dp.w0 = dW0;
+    dp.x = dX; dp.w = dW; dp.w0 = dW0;
     dp.n = count;
-    dp.a_row_offset = hp->a_row_offset + first;
-    dp.labels = ml ? static_cast<const int64_t*>(dLab)
-                   : static_cast<const int64_t*>(dLab) + first;
-    dp.offsets = ml ? static_cast<const int64_t*>(dOff) + first : nullptr;
-    dp.include_primal_regularizer = (first == 0) ? 1 : 0;
-    rc = eval_sums_dev<Data>(obj, &dp, static_cast<double*>(dSums), nullptr, 0, nullptr);
-    if (rc) { release(); return rc; }
-    EVAL_TRY(cudaMemcpy(part.data(), dSums, sums_count * sizeof(double), cudaMemcpyDeviceToHost));
+    if (a_chunked) {
+      // the chunk's own rows of A: row 0 of the buffer is example `first` of the shard
+      SDCAB_CUDA_TRY(cudaMemcpyAsync(dAc, static_cast<const Data*>(hp->a) + (hp->a_row_offset + first) * m,
+                                     static_cast<size_t>(count) * m * elem, cudaMemcpyHostToDevice, s));
+      dp.a = dAc; dp.a_row_offset = 0;
+    } else {
+      dp.a = dA; dp.a_row_offset = hp->a_row_offset + first;
+    }
+    dp.labels = ml ? dLab : dLab + first;
+    dp.offsets = ml ? dOff + first : nullptr;
+    dp.include_primal_regularizer = (first == 0) ? hp->include_primal_regularizer : 0;
+    rc = eval_sums_dev<Data>(obj, &dp, dSums, ws, L.total, s);
+    if (rc) return rc;
+    SDCAB_CUDA_TRY(cudaMemcpyAsync(static_cast<unsigned char*>(pinned) + static_cast<size_t>(index) * sums_bytes,
+                                   dSums, sums_count * sizeof(double), cudaMemcpyDeviceToHost, s));
+  }
+  for (int i = 0; i < kBuf; ++i) SDCAB_CUDA_TRY(cudaStreamSynchronize(streams[i]));
+  std::vector<double> total(sums_count, 0.0);
+  for (long long c = 0; c < num_chunks; ++c) {
+    const double* part = reinterpret_cast<const double*>(static_cast<unsigned char*>(pinned) +
+                                                         static_cast<size_t>(c) * sums_bytes);
     for (size_t i = 0; i < sums_count; ++i) total[i] += part[i];
   }
-#undef EVAL_TRY
-  release();
   return eval_finish(obj, m, total.data(), rec, accuracy);
 }
 
@@ -508,24 +559,31 @@ int eval_sums_fixed_scratch(const sdcab_objective* obj, const sdcab_problem* p, 
   const size_t partials_bytes = (static_cast<size_t>(max_blocks) * 4 * sizeof(double) + 255) & ~static_cast<size_t>(255);
   const size_t hist_bytes = (static_cast<size_t>(m) * sizeof(unsigned long long) + 255) & ~static_cast<size_t>(255);
   const size_t row_bytes = static_cast<size_t>(m) * sizeof(Data);
-  // at least 32 score rows must fit beside the partial sums and the histogram
-  if (partials_bytes + hist_bytes + 32 * row_bytes + 256 > kFixedScratchBytes) {
+  g_fixed_scratch_error[0] = 0;
+  // at least 32 score rows must fit beside the partial sums, the histogram and the
+  // error word of the tensor-core product
+  constexpr size_t kErrBytes = 256;
+  if (partials_bytes + hist_bytes + kErrBytes + 32 * row_bytes + 256 > kFixedScratchBytes) {
     std::snprintf(g_fixed_scratch_error, sizeof(g_fixed_scratch_error),
                   "the fixed scratch of %zu bytes cannot hold 32 score rows of %lld classes",
                   kFixedScratchBytes, m);
     return SDCAB_ERR_TOO_LARGE;
   }
-  const size_t scores_room = (kFixedScratchBytes - partials_bytes - hist_bytes) & ~static_cast<size_t>(255);
-  const long long chunk = std::min<long long>(n, static_cast<long long>(scores_room / row_bytes));
+  const size_t scores_room =
+      (kFixedScratchBytes - partials_bytes - hist_bytes - kErrBytes) & ~static_cast<size_t>(255);
+  const long long chunk = std::min<long long>(
+      std::min<long long>(n, kMaxChunkRows), static_cast<long long>(scores_room / row_bytes));
   unsigned char* base = static_cast<unsigned char*>(scratch);
   Data* scores = reinterpret_cast<Data*>(base);
   double* partials = reinterpret_cast<double*>(base + scores_room);
   unsigned long long* hist = reinterpret_cast<unsigned long long*>(base + scores_room + partials_bytes);
+  int* tc_err = reinterpret_cast<int*>(base + scores_room + partials_bytes + hist_bytes);
 
   // the array keeps whatever the previous call left: everything that is
   // accumulated into starts from zero here, the rest is overwritten before use
   SDCAB_CUDA_TRY(cudaMemsetAsync(sums, 0, sizeof(double) * SDCAB_EVAL_SUMS(m), stream));
   SDCAB_CUDA_TRY(cudaMemsetAsync(hist, 0, sizeof(unsigned long long) * m, stream));
+  SDCAB_CUDA_TRY(cudaMemsetAsync(tc_err, 0, sizeof(int), stream));
   set_count_kernel<<<1, 32, 0, stream>>>(sums, static_cast<double>(n));
   if (p->is_train && p->input_kind == SDCAB_INPUT_FEATURES && p->include_primal_regularizer) {
     const long long count = p->d * m;
@@ -547,7 +605,14 @@ int eval_sums_fixed_scratch(const sdcab_objective* obj, const sdcab_problem* p, 
   const int warps = kLossThreads / 32;
   const size_t smem = static_cast<size_t>(warps) * g.m_pad * sizeof(Data) +
                       static_cast<size_t>(warps) * g.mask_words * sizeof(unsigned);
-  if (smem > info.smem_optin) return SDCAB_ERR_TOO_LARGE;
+  if (smem > info.smem_optin) {
+    // the loss stage stages four score rows per thread block in shared memory: this
+    // bound (about 14 000 float or 7 000 double classes) is the one that binds first
+    std::snprintf(g_fixed_scratch_error, sizeof(g_fixed_scratch_error),
+                  "%lld classes need %zu bytes of shared memory per thread block, the device offers %zu",
+                  m, smem, info.smem_optin);
+    return SDCAB_ERR_TOO_LARGE;
+  }
   const bool fl = (obj->precision == SDCAB_PRECISION_FLOAT);
   auto kd = eval_loss_kernel<Data, double>;
   auto kf = eval_loss_kernel<Data, float>;
@@ -557,7 +622,7 @@ int eval_sums_fixed_scratch(const sdcab_objective* obj, const sdcab_problem* p, 
   }
   for (long long first = 0; first < n; first += chunk) {
     const long long count = std::min(chunk, n - first);
-    rc = scores_chunk<Data>(p, first, count, scores, stream);
+    rc = scores_chunk<Data>(p, first, count, scores, stream, tc_err);
     if (rc) return rc;
     g.n = count; g.first = first;
     const int blocks = static_cast<int>(std::max<long long>(
@@ -569,6 +634,7 @@ int eval_sums_fixed_scratch(const sdcab_objective* obj, const sdcab_problem* p, 
   }
   hist_to_sums_kernel<<<std::max(1, static_cast<int>((m + 255) / 256)), 256, 0, stream>>>(
       hist, static_cast<int>(m), sums);
+  report_gemm_error_kernel<<<1, 32, 0, stream>>>(tc_err, sums);
   SDCAB_CUDA_TRY(cudaGetLastError());
   return SDCAB_OK;
 }
@@ -580,6 +646,17 @@ extern "C" {
 int sdcab_objective_from_name(const char* name, double c, double gamma, int64_t k,
                               sdcab_objective* out) {
   return sdcab::objective_from_name(name, c, gamma, k, out);
+}
+
+int sdcab_test_set(const char* name, int64_t value) {
+  if (!name) return SDCAB_ERR_ARG;
+  if (std::strcmp(name, "eval_chunk") == 0) { sdcab::g_test_eval_chunk = value; return SDCAB_OK; }
+  if (std::strcmp(name, "gemm_simt") == 0) { sdcab::g_test_force_simt = value ? 1 : 0; return SDCAB_OK; }
+  if (std::strcmp(name, "gemm_lose_a_tile") == 0) {
+    sdcab::g_test_short_wait = value ? 1 : 0;
+    return SDCAB_OK;
+  }
+  return SDCAB_ERR_ARG;
 }
 
 size_t sdcab_eval_workspace_bytes(int64_t n, int64_t m, int64_t elem_size) {

@@ -64,6 +64,32 @@ inline int check_objective(const sdcab_objective* o, int64_t m) {
   return SDCAB_OK;
 }
 
+// The label checks of the reference (include/sdca/solver/data/output.h:169-215)
+// on host arrays, labels 0-based: every label inside [0, m); multilabel examples
+// have offsets[0] == 0, between 1 and m - 1 labels each, and their labels
+// strictly increasing (distinct and sorted).
+inline int validate_labels(const int64_t* labels, const int64_t* offsets, int64_t n, int64_t m,
+                           bool multilabel) {
+  if (!labels || n < 0) return SDCAB_ERR_ARG;
+  if (!multilabel) {
+    for (int64_t i = 0; i < n; ++i)
+      if (labels[i] < 0 || labels[i] >= m) return SDCAB_ERR_LABELS_RANGE;
+    return SDCAB_OK;
+  }
+  if (!offsets) return SDCAB_ERR_ARG;
+  if (offsets[0] != 0) return SDCAB_ERR_LABELS_RANGE;
+  for (int64_t i = 0; i < n; ++i) {
+    const int64_t first = offsets[i], count = offsets[i + 1] - first;
+    if (count < 1 || count >= m) return SDCAB_ERR_LABELS_RANGE;
+    for (int64_t q = 0; q < count; ++q) {
+      const int64_t c = labels[first + q];
+      if (c < 0 || c >= m) return SDCAB_ERR_LABELS_RANGE;
+      if (q > 0 && c <= labels[first + q - 1]) return SDCAB_ERR_LABELS_RANGE;
+    }
+  }
+  return SDCAB_OK;
+}
+
 inline ObjectiveParams to_params(const sdcab_objective* o) {
   ObjectiveParams q;
   q.id = o->id; q.k = static_cast<int>(o->k); q.c = o->c; q.gamma = o->gamma;

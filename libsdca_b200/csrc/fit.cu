@@ -14,8 +14,10 @@
 // the primal variables receive the block's rank-one changes afterwards, in
 // step order.
 #include <algorithm>
+#include <chrono>
 #include <cstdio>
 #include <cstring>
+#include <ctime>
 #include <vector>
 
 #include "common_host.h"
@@ -54,19 +56,6 @@ struct ChainArgs {
   int m, count, kernel_input, s_on_chip;
 };
 
-#ifdef SDCAB_FIT_PROFILE
-// Cycle counts of the chain's phases (a build for measurements only): thread 0
-// adds up in shared memory and the totals go to global memory at the end.
-__device__ unsigned long long g_chain_clk[24];
-__shared__ unsigned long long s_chain_clk[24];
-#define CHAIN_CLK(slot, t0) do { if (threadIdx.x == 0) s_chain_clk[slot] += clock64() - (t0); } while (0)
-#define STAGE_CLK(slot) do { if (threadIdx.x == 0) { const long long now__ = clock64(); s_chain_clk[slot] += now__ - t_stage; t_stage = now__; } } while (0)
-#define STAGE_BEGIN() long long t_stage = clock64()
-#else
-#define CHAIN_CLK(slot, t0) do { } while (0)
-#define STAGE_CLK(slot) do { } while (0)
-#define STAGE_BEGIN() do { } while (0)
-#endif
 
 constexpr int kSmallRow = 256;   // rows up to this length take the block-wide update
 
@@ -180,7 +169,6 @@ __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>
   const int lane = threadIdx.x & 31;
   const int m = in.m, y = in.y;
   const R neg_inf = -num<R>::inf(), pos_inf = num<R>::inf();
-  STAGE_BEGIN();
   // the vector to project (objective/l2_topk_hinge.h:55-59)
   const Data score_y = static_cast<Data>(fma(in.pending[y], in.pending_g, in.Sb[y]));
   const Data vy = add_rn_(mul_rn_(sc.beta, in.a_cur[y]), mul_rn_(sc.alpha, score_y));
@@ -206,15 +194,10 @@ __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>
   const R rho = sc.rho, t_split = rho * rhs;
   R t = (in.t_start >= R(0) && in.t_start < t_split) ? in.t_start : R(0);
   R tl = neg_inf, tr = pos_inf;
-  STAGE_CLK(8);
   ClipSum<R> c = clip_sum<R, NV>(v, t, hi, fs);
-  STAGE_CLK(9);
   bool equality = false;
   // phi(t) = rhs - f(t) (equality) or t - rho f(t) (biased): increasing, root wanted
   bool settled = false;
-#ifdef SDCAB_FIT_PROFILE
-  int evals = 1;
-#endif
   // The common course first, as a loop without side exits: t = rho f(t), Newton
   // steps that stay inside the bracket and left of rho rhs.  Anything else drops
   // into the general loop below with the state reached so far.
@@ -227,9 +210,6 @@ __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>
     const bool plain = tn > tl_n && tn < tr_n && tn < t_split;
     if (__any_sync(0xffffffffu, at_root || !plain)) break;
     tl = tl_n; tr = tr_n;
-#ifdef SDCAB_FIT_PROFILE
-    ++evals;
-#endif
     const ClipSum<R> cn = clip_sum<R, NV>(v, tn, hi, fs);
     const bool same = (cn.u == c.u && cn.q == c.q);
     t = tn; c = cn;
@@ -276,9 +256,6 @@ __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>
       newton = false;
       if (!(tn > tl && tn < tr)) return false;
     }
-#ifdef SDCAB_FIT_PROFILE
-    ++evals;
-#endif
     const ClipSum<R> cn = clip_sum<R, NV>(v, tn, hi, fs);
     // a Newton step that finds the sets it started from has solved its piece exactly
     settled = newton && (cn.u == c.u && cn.q == c.q) && (!equality || inside > 0);
@@ -289,10 +266,6 @@ __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>
       tl = t; tr = pos_inf;
     }
   }
-#ifdef SDCAB_FIT_PROFILE
-  if (threadIdx.x == 0) { s_chain_clk[15] += evals; s_chain_clk[16] += equality ? 1 : 0; s_chain_clk[17] += settled ? 0 : 1; }
-#endif
-  STAGE_CLK(10);
   if (!settled) return false;
   // the reference's closed forms for the sets found (knapsack_le_biased.h:52;
   // knapsack_eq.h for the equality case): entries at hi, entries strictly inside
@@ -304,7 +277,6 @@ __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>
   } else {
     t = (hi * static_cast<R>(c.u) + sum_inside) / (sc.rho_inv + static_cast<R>(inside));
   }
-  STAGE_CLK(11);
   // new variables (objective/l2_topk_hinge.h:64-68)
   const Data td = static_cast<Data>(t), hid = static_cast<Data>(hi);
   R part[NV];
@@ -327,7 +299,6 @@ __device__ __forceinline__ bool warp_update_topk_hinge(const StepConsts<R, Data>
     for (int e = 0; e < NV; ++e) if (e == (y >> 5)) a_new[e] = ay;
   }
   t_out = t;
-  STAGE_CLK(12);
   return true;
 }
 
@@ -439,11 +410,6 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
   Data* A = static_cast<Data*>(p.A);
   Data* D = static_cast<Data*>(p.D);
 
-#ifdef SDCAB_FIT_PROFILE
-  if (tid < 24) s_chain_clk[tid] = 0;
-  __syncthreads();
-  long long t_begin = clock64();
-#endif
   for (int t = tid; t < kBlockSteps * kBlockSteps; t += kFitThreads) G[t] = p.G[t];
   for (int t = tid; t < 2 * m; t += kFitThreads) delta[t] = 0.0;
   if (tid < count) {
@@ -479,14 +445,10 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
   }
   __syncthreads();
 
-  CHAIN_CLK(0, t_begin);
   // Step b is worked by warp 0.  Meanwhile the other warps bring the rows after b
   // up to date with the change of step b - 1; row b itself receives that change
   // from warp 0 as it reads the row, so nobody waits for anybody inside a step.
   for (int b = 0; b < count; ++b) {
-#ifdef SDCAB_FIT_PROFILE
-    long long t_step = clock64();
-#endif
     const int cur = b & 1, prev = cur ^ 1;
     const bool pending = (b > 0) && (s_skip[prev] == 0);
     const double* d_prev = delta + prev * m;
@@ -511,10 +473,8 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
         StepOutput<Data> out;
         out.a_row = A + i * m; out.delta = d_cur; out.d_row = d_row; out.t_keep = p.t_keep + i;
         out.skip = &s_skip[cur]; out.kernel_input = p.kernel_input;
-        CHAIN_CLK(1, t_step);
         done = (m <= 128) ? warp_step_topk_hinge<R, Data, 4>(s_consts[b], hi_small, rhs_small, in, out)
                           : warp_step_topk_hinge_long<R, Data>(&s_consts[b], hi_small, rhs_small, &in, &out);
-        CHAIN_CLK(2, t_step);
       }
       if (!done) {
         // the general routine on the row in shared memory
@@ -589,11 +549,7 @@ __global__ void __launch_bounds__(kFitThreads, 1) fit_chain_kernel(ChainArgs p) 
       }
     }
     __syncthreads();
-    CHAIN_CLK(4, t_step);
   }
-#ifdef SDCAB_FIT_PROFILE
-  if (tid < 24) g_chain_clk[tid] += s_chain_clk[tid];
-#endif
 }
 
 // S[b][j] = sum over the slices of the split product, plus (when the product
@@ -1002,10 +958,19 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
   };
   const double eps_floor = std::max(
       static_cast<double>(num<Data>::eps()), static_cast<double>(num<R>::eps()));
+  // the reference's stopwatches run while it solves and evaluates (solver.h:81-131):
+  // processor time by std::clock, wall time by a steady clock
+  const std::clock_t cpu_begin = std::clock();
+  const auto wall_begin = std::chrono::steady_clock::now();
+  auto cpu_now = [&]() { return static_cast<double>(std::clock() - cpu_begin) / CLOCKS_PER_SEC; };
+  auto wall_now = [&]() {
+    return std::chrono::duration<double>(std::chrono::steady_clock::now() - wall_begin).count();
+  };
   auto check = [&](int status, int64_t epoch) {
     const sdcab_eval_record* last = history.empty() ? nullptr : &history.back();
     const sdcab_eval_record* before = history.size() > 1 ? &history[history.size() - 2] : nullptr;
-    return check_stopping(status, last, before, crit->epsilon, epoch, crit->max_epoch, eps_floor);
+    return check_stopping(status, last, before, crit->epsilon, epoch, crit->max_epoch, eps_floor,
+                          crit->max_cpu_time, cpu_now(), crit->max_wall_time, wall_now());
   };
 
   // begin_solve (solver.h:59-80)
@@ -1072,6 +1037,8 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
     result->num_evals = static_cast<int64_t>(history.size());
     result->solve_seconds = solve_ms * 1e-3;
     result->eval_seconds = eval_ms * 1e-3;
+    result->cpu_seconds = cpu_now();
+    result->wall_seconds = wall_now();
   }
   return SDCAB_OK;
 }
@@ -1094,6 +1061,7 @@ int check_fit_args(const sdcab_objective* obj, const sdcab_problem* t, const sdc
     return SDCAB_ERR_ARG;
   }
   if (!(c->epsilon >= 0) || c->max_epoch < 0 || c->eval_epoch < 0) return SDCAB_ERR_ARG_RANGE;
+  if (!(c->max_cpu_time >= 0) || !(c->max_wall_time >= 0)) return SDCAB_ERR_ARG_RANGE;
   return SDCAB_OK;
 }
 
@@ -1118,19 +1086,12 @@ int fit_host(const sdcab_objective* obj, const sdcab_problem* hp, const sdcab_fi
   const long long n = hp->n, m = hp->m, d = hp->d;
   const bool kernel = (hp->input_kind == SDCAB_INPUT_KERNEL);
   const bool ml = objective_is_multilabel(obj->id);
-  const long long num_labels = ml ? hp->offsets[n] : n;
   // the label checks of include/sdca/solver/data/output.h:169-215 (labels here are 0-based)
-  for (long long i = 0; i < num_labels; ++i)
-    if (hp->labels[i] < 0 || hp->labels[i] >= m) return SDCAB_ERR_LABELS_RANGE;
-  if (ml) {
-    if (hp->offsets[0] != 0) return SDCAB_ERR_LABELS_RANGE;
-    for (long long i = 0; i < n; ++i) {
-      const long long count = hp->offsets[i + 1] - hp->offsets[i];
-      if (count < 1 || count >= m) return SDCAB_ERR_LABELS_RANGE;
-    }
-  }
+  rc = validate_labels(hp->labels, hp->offsets, n, m, ml);
+  if (rc) return rc;
+  const long long num_labels = ml ? hp->offsets[n] : n;
   DeviceBuffers buf;
-  Data *dX = nullptr, *dA = nullptr, *dW = nullptr;
+  Data *dX = nullptr, *dA = nullptr, *dW = nullptr, *dW0 = nullptr;
   int64_t *dLab = nullptr, *dOff = nullptr;
   const size_t x_elems = static_cast<size_t>(n) * d, a_elems = static_cast<size_t>(n) * m,
                w_elems = static_cast<size_t>(d) * m;
@@ -1144,6 +1105,12 @@ int fit_host(const sdcab_objective* obj, const sdcab_problem* hp, const sdcab_fi
   if (!kernel) {
     rc = buf.alloc(&dW, w_elems); if (rc) return rc;
     SDCAB_CUDA_TRY(cudaMemcpy(dW, hp->w, w_elems * sizeof(Data), cudaMemcpyHostToDevice));
+    if (hp->w0) {
+      // the proximal centre of a restarted fit (src/matlab/mex_solve.cpp:529-586): it enters
+      // the primal regulariser of every evaluation and the rebuilt W
+      rc = buf.alloc(&dW0, w_elems); if (rc) return rc;
+      SDCAB_CUDA_TRY(cudaMemcpy(dW0, hp->w0, w_elems * sizeof(Data), cudaMemcpyHostToDevice));
+    }
   }
   if (ml) {
     rc = buf.alloc(&dOff, static_cast<size_t>(n + 1)); if (rc) return rc;
@@ -1151,7 +1118,7 @@ int fit_host(const sdcab_objective* obj, const sdcab_problem* hp, const sdcab_fi
                               cudaMemcpyHostToDevice));
   }
   sdcab_problem dp = *hp;
-  dp.x = dX; dp.a = dA; dp.w = dW; dp.w0 = nullptr; dp.labels = dLab; dp.offsets = dOff;
+  dp.x = dX; dp.a = dA; dp.w = dW; dp.w0 = dW0; dp.labels = dLab; dp.offsets = dOff;
   rc = fit_entry<Data>(obj, &dp, c, perm, evals, cap, res, nullptr);
   if (rc) return rc;
   SDCAB_CUDA_TRY(cudaMemcpy(const_cast<void*>(hp->a), dA, a_elems * sizeof(Data), cudaMemcpyDeviceToHost));
@@ -1163,16 +1130,6 @@ int fit_host(const sdcab_objective* obj, const sdcab_problem* hp, const sdcab_fi
 }  // namespace
 }  // namespace sdcab
 
-#ifdef SDCAB_FIT_PROFILE
-extern "C" int sdcab_debug_chain_clocks(unsigned long long* out, int reset) {
-  cudaMemcpyFromSymbol(out, sdcab::g_chain_clk, sizeof(unsigned long long) * 24);
-  if (reset) {
-    unsigned long long z[24] = {0};
-    cudaMemcpyToSymbol(sdcab::g_chain_clk, z, sizeof(z));
-  }
-  return 0;
-}
-#endif
 
 extern "C" {
 

@@ -81,12 +81,14 @@ inline void epoch_permutations(int64_t n, int64_t num_epochs, int64_t* perm) {
   }
 }
 
-// check_stopping_criteria of the reference (include/sdca/solver/eval.h:56-109)
-// without the time limits: `last` / `before` are the two most recent
-// evaluations of the training set (either may be null).  Returns the new status.
+// check_stopping_criteria of the reference (include/sdca/solver/eval.h:56-109):
+// `last` / `before` are the two most recent evaluations of the training set
+// (either may be null); cpu_now / wall_now are the seconds spent so far, compared
+// with the limits when those are positive.  Returns the new status.
 inline int check_stopping(int status, const sdcab_eval_record* last,
                           const sdcab_eval_record* before, double epsilon, int64_t epoch,
-                          int64_t max_epoch, double data_epsilon) {
+                          int64_t max_epoch, double data_epsilon, double max_cpu_time = 0,
+                          double cpu_now = 0, double max_wall_time = 0, double wall_now = 0) {
   if (status != SDCAB_FIT_SOLVING) return status;
   if (last) {
     const double gap = last->primal - last->dual;
@@ -100,7 +102,11 @@ inline int check_stopping(int status, const sdcab_eval_record* last,
       if (last->dual + eps * std::fabs(before->dual) < before->dual) status = SDCAB_FIT_NO_PROGRESS;
     }
   }
-  if (status == SDCAB_FIT_SOLVING && epoch >= max_epoch) status = SDCAB_FIT_MAX_EPOCH;
+  if (status == SDCAB_FIT_SOLVING) {
+    if (epoch >= max_epoch) status = SDCAB_FIT_MAX_EPOCH;
+    else if (max_cpu_time > 0 && cpu_now >= max_cpu_time) status = SDCAB_FIT_MAX_CPU_TIME;
+    else if (max_wall_time > 0 && wall_now >= max_wall_time) status = SDCAB_FIT_MAX_WALL_TIME;
+  }
   return status;
 }
 

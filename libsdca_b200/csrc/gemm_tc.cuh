@@ -361,12 +361,10 @@ inline int launch(const float* A, const float* B, float* C, int M, int N, int K,
   CUtensorMap map_a, map_b;
   if (!make_map(&map_a, A, M, K, lda, kBM) || !make_map(&map_b, B, N, K, ldb, kBN))
     return SDCAB_ERR_CUDA;
-  static bool attr_set = false;
-  if (!attr_set) {
-    SDCAB_CUDA_TRY(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        kSmemBytes));
-    attr_set = true;
-  }
+  // the opt-in to large dynamic shared memory is a property of the function on
+  // each device, so it is set on every launch (a cheap host-side call)
+  SDCAB_CUDA_TRY(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemBytes));
   Params p;
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.err = err_dev;
   dim3 grid((N + kBN - 1) / kBN, (M + kBM - 1) / kBM);

@@ -14,6 +14,7 @@
 #include "fast_rows.cuh"
 #include "prox_core.cuh"
 #include "prox_names.h"
+#include "two_simplex_sort.cuh"
 
 namespace sdcab {
 
@@ -151,8 +152,32 @@ int try_entropic_rows(int, const double*, double*, int, long long, const ProxPar
 }
 
 template <typename Data, typename R>
+int launch_two_simplex_sort(const Data* a, Data* out, int m, long long n, const ProxParams& q,
+                            sdcab_thresholds* thr_out, int apply, cudaStream_t stream) {
+  DeviceInfo info;
+  int rc = get_device_info(&info);
+  if (rc) return rc;
+  const int pa = pow2_ceil(q.p), pb = pow2_ceil(m - q.p);
+  const int warps = kSortThreads / 32;
+  const size_t smem = static_cast<size_t>(warps) * (pa + pb) * sizeof(Data);
+  // the sorted copies of both blocks live in shared memory: rows beyond that are refused
+  if (smem > info.smem_optin) return SDCAB_ERR_TOO_LARGE;
+  auto kernel = two_simplex_sort_kernel<Data, R>;
+  if (smem > 48 * 1024)
+    SDCAB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(smem)));
+  const long long want = (n + warps - 1) / warps;
+  const int blocks = static_cast<int>(std::max<long long>(1, std::min<long long>(want, 8LL * info.sm_count)));
+  kernel<<<blocks, kSortThreads, smem, stream>>>(a, out, m, n, q, thr_out, apply, pa, pb);
+  SDCAB_CUDA_TRY(cudaGetLastError());
+  return SDCAB_OK;
+}
+
+template <typename Data, typename R>
 int dispatch_prox(int prox, const Data* a, Data* out, int m, long long n, const ProxParams& q,
                   sdcab_thresholds* thr_out, int apply, cudaStream_t stream) {
+  if (prox == kTwoSimplexSort)
+    return launch_two_simplex_sort<Data, R>(a, out, m, n, q, thr_out, apply, stream);
   if (apply && !thr_out) {
     int rc = try_entropic_rows<R>(prox, a, out, m, n, q, stream);
     if (rc != kNoFastPath) return rc;
@@ -179,7 +204,10 @@ static int check_args(int prox, long long m, long long n, const sdcab_prox_opts*
   if (m > 0x7fffffffLL) return SDCAB_ERR_TOO_LARGE;
   if (!(o->rhs >= 0) || !(o->rho >= 0) || !(o->alpha > 0)) return SDCAB_ERR_ARG_RANGE;
   if (o->k < 1 || o->k > m) return SDCAB_ERR_ARG_RANGE;
-  if (prox == kTwoSimplex && (o->p < 1 || o->p > m - 1)) return SDCAB_ERR_ARG_RANGE;
+  if ((prox == kTwoSimplex || prox == kTwoSimplexSort) && (o->p < 1 || o->p > m - 1))
+    return SDCAB_ERR_ARG_RANGE;
+  // two_simplex_sort.h:34: rhs > 0 is a precondition of the sort-based routine
+  if (prox == kTwoSimplexSort && !(o->rhs > 0)) return SDCAB_ERR_ARG_RANGE;
   if (o->precision != SDCAB_PRECISION_DOUBLE && o->precision != SDCAB_PRECISION_FLOAT)
     return SDCAB_ERR_PRECISION;
   return SDCAB_OK;
@@ -218,7 +246,7 @@ int prox_host(const char* name, const Data* a, long long m, long long n,
   int rc = check_args(prox, m, n, o);
   if (rc) return rc;
   const bool want_thr = (thr != nullptr);
-  const int per_row_thr = (prox == kTwoSimplex) ? 2 : 1;
+  const int per_row_thr = (prox == kTwoSimplex || prox == kTwoSimplexSort) ? 2 : 1;
   const size_t row_bytes = static_cast<size_t>(m) * sizeof(Data);
   // 32 MiB per chunk measured best on PCIe Gen5 (64 MiB: 6 % slower, more of the
   // transfer runs one-directional at the ends; 16 MiB and below: slower again)
@@ -227,15 +255,17 @@ int prox_host(const char* name, const Data* a, long long m, long long n,
   rows_per_chunk = std::min(rows_per_chunk, n);
   const int kBuf = 3;
   void* dbuf = nullptr; void* tbuf = nullptr;
+  // one host-buffer call at a time per device: the scratch and the streams are shared
+  std::lock_guard<std::mutex> call_lock(*host_call_mutex());
   rc = workspace_reserve(0, kBuf * rows_per_chunk * row_bytes, &dbuf);
   if (rc) return rc;
   if (want_thr) {
     rc = workspace_reserve(1, kBuf * rows_per_chunk * per_row_thr * sizeof(sdcab_thresholds), &tbuf);
     if (rc) return rc;
   }
-  static thread_local cudaStream_t streams[kBuf] = {nullptr, nullptr, nullptr};
-  for (int i = 0; i < kBuf; ++i)
-    if (!streams[i]) SDCAB_CUDA_TRY(cudaStreamCreateWithFlags(&streams[i], cudaStreamNonBlocking));
+  cudaStream_t streams[kBuf];
+  rc = pipeline_streams(kBuf, streams);
+  if (rc) return rc;
   long long done = 0;
   int slot = 0;
   while (done < n) {

@@ -21,6 +21,7 @@ enum ProxId {
   kTopkEntropy,
   kTopkEntropyBiased,
   kTwoSimplex,
+  kTwoSimplexSort,
   kLambertWExp,
   kNumProx
 };

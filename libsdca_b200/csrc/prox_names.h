@@ -25,8 +25,9 @@ inline int prox_id_from_name(const char* name) {
       {"topk_entropy", kTopkEntropy},
       {"topk_entropy_biased", kTopkEntropyBiased},
       {"two_simplex", kTwoSimplex},
-      // the sort-based variant solves the same problem; one kernel serves both
-      {"two_simplex_sort", kTwoSimplex},
+      // the sort-based variant is its own routine (two_simplex_sort.cuh): it differs
+      // from two_simplex where a block ends up empty or the common sum is zero
+      {"two_simplex_sort", kTwoSimplexSort},
       {"lambert_w_exp", kLambertWExp},
   };
   for (const Entry& e : table)

@@ -3,13 +3,17 @@
 // against the reference without a GPU.  Reductions are the identity here, so
 // this exercises the algorithms, not the warp plumbing.  Never linked into the
 // product library.
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
+#include <functional>
 #include <string>
+#include <vector>
 
 #include "../../include/sdca_b200.h"
 #include "../../libsdca_b200/csrc/prox_core.cuh"
 #include "../../libsdca_b200/csrc/prox_names.h"
+#include "../../libsdca_b200/csrc/two_simplex_sort.cuh"
 
 namespace {
 
@@ -34,6 +38,25 @@ int run(int prox, Data* a, int64_t m, int64_t n, const sdcab::ProxParams& q,
         Applier<Data> fa(pr.a, kMapIdentity, 1.0), fb(pr.b, kMapIdentity, 1.0);
         for (int i = 0; i < q.p; ++i) x[i] = fa(x[i]);
         for (int64_t i = q.p; i < m; ++i) x[i] = fb(x[i]);
+      }
+      continue;
+    }
+    if (prox == kTwoSimplexSort) {
+      const int na = q.p, nb = static_cast<int>(m) - q.p;
+      std::vector<Data> sa(x, x + na), sb(x + na, x + m);
+      std::sort(sa.begin(), sa.end(), std::greater<Data>());
+      std::sort(sb.begin(), sb.end(), std::greater<Data>());
+      R ta, tb; int rr, ss;
+      two_simplex_sort_walk<R, Data>(sa.data(), na, sb.data(), nb, static_cast<R>(q.rhs), ta, tb, rr, ss);
+      if (thr) {
+        thr[2 * r] = {double(ta), 0.0, q.rhs, 0, rr};
+        thr[2 * r + 1] = {double(tb), 0.0, q.rhs, 0, ss};
+      }
+      if (apply) {
+        Applier<Data> fa(make_thr(ta, R(0), static_cast<R>(q.rhs), 0, 0, R(0), R(0)), kMapIdentity, 1.0);
+        Applier<Data> fb(make_thr(tb, R(0), static_cast<R>(q.rhs), 0, 0, R(0), R(0)), kMapIdentity, 1.0);
+        for (int i = 0; i < na; ++i) x[i] = fa(x[i]);
+        for (int64_t i = na; i < m; ++i) x[i] = fb(x[i]);
       }
       continue;
     }
@@ -152,7 +175,10 @@ extern "C" int sdcab_hostsim_objective_from_name(const char* name, double c, dou
 
 // ---- fit: the device code's update step with one lane, driven by the host-side
 // epoch order and stopping rule the library uses ---------------------------------
+#include <chrono>
+#include <ctime>
 #include "../../libsdca_b200/csrc/fit_host.h"
+#include "../../libsdca_b200/csrc/per_device.h"
 #include "../../libsdca_b200/csrc/update_core.cuh"
 
 namespace {
@@ -182,10 +208,15 @@ int run_fit(const sdcab_objective* obj, const sdcab_problem* p, const sdcab_fit_
     if (evals && (int64_t)hist.size() <= cap) evals[hist.size() - 1] = rec;
   };
   const double eps_floor = std::max(double(num<Data>::eps()), double(num<R>::eps()));
+  const std::clock_t cpu_begin = std::clock();
+  const auto wall_begin = std::chrono::steady_clock::now();
   auto check = [&](int st, int64_t epoch) {
+    const double cpu = double(std::clock() - cpu_begin) / CLOCKS_PER_SEC;
+    const double wall = std::chrono::duration<double>(std::chrono::steady_clock::now() - wall_begin).count();
     return check_stopping(st, hist.empty() ? nullptr : &hist.back(),
                           hist.size() > 1 ? &hist[hist.size() - 2] : nullptr, crit->epsilon,
-                          epoch, crit->max_epoch, eps_floor);
+                          epoch, crit->max_epoch, eps_floor, crit->max_cpu_time, cpu,
+                          crit->max_wall_time, wall);
   };
   int64_t epoch = 0;
   int status = crit->max_epoch > 0 ? SDCAB_FIT_SOLVING : SDCAB_FIT_MAX_EPOCH;
@@ -242,6 +273,8 @@ int run_fit(const sdcab_objective* obj, const sdcab_problem* p, const sdcab_fit_
   if (!evaluated && !(crit->eval_on_start && epoch == 0)) evaluate();
   res->status = status; res->epoch = epoch; res->num_evals = (int64_t)hist.size();
   res->solve_seconds = 0; res->eval_seconds = 0;
+  res->cpu_seconds = double(std::clock() - cpu_begin) / CLOCKS_PER_SEC;
+  res->wall_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - wall_begin).count();
   return 0;
 }
 
@@ -261,4 +294,29 @@ extern "C" int sdcab_hostsim_fit(const sdcab_objective* obj, const sdcab_problem
 extern "C" int sdcab_hostsim_epoch_permutations(int64_t n, int64_t epochs, int64_t* perm) {
   sdcab::epoch_permutations(n, epochs, perm);
   return 0;
+}
+
+// The library's stopping rule and label checks, as they are (host code).
+extern "C" int sdcab_hostsim_check_stopping(int status, const sdcab_eval_record* last,
+                                            const sdcab_eval_record* before, double epsilon,
+                                            int64_t epoch, int64_t max_epoch, double data_epsilon,
+                                            double max_cpu, double cpu_now, double max_wall,
+                                            double wall_now) {
+  return sdcab::check_stopping(status, last, before, epsilon, epoch, max_epoch, data_epsilon, max_cpu,
+                               cpu_now, max_wall, wall_now);
+}
+
+extern "C" int sdcab_hostsim_validate_labels(const int64_t* labels, const int64_t* offsets, int64_t n,
+                                             int64_t m, int multilabel) {
+  return sdcab::validate_labels(labels, offsets, n, m, multilabel != 0);
+}
+
+// Per-device bookkeeping: visits the devices in `order` and reports, for each
+// visit, whether it was the first one on that device (bit i of the result).
+extern "C" uint64_t sdcab_hostsim_once_per_device(const int* order, int count) {
+  sdcab::OncePerDevice once;
+  uint64_t bits = 0;
+  for (int i = 0; i < count && i < 64; ++i)
+    if (once.first_time(order[i])) bits |= uint64_t(1) << i;
+  return bits;
 }

@@ -2,6 +2,8 @@
 with the reference's evaluate_dataset, term by term."""
 import os
 
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -139,23 +141,96 @@ def test_config4_gap_terms_reduced_n(ref, cuda_lib):
 
 
 def test_chunked_evaluation_is_the_same(ref, cuda_lib):
-    import subprocess
-    import sys
-    code = (
-        "import numpy as np, sys; sys.path.insert(0, %r)\n"
-        "import libsdca_b200 as sd, torch\n"
-        "from tests.test_oracle_restatement import random_problem\n"
-        "rng = np.random.default_rng(8)\n"
-        "X, labels, _ = random_problem(rng, 700, 16, 9, np.float64, False)\n"
-        "A = rng.standard_normal((700, 9)) * 0.01; W = rng.standard_normal((9, 16))\n"
-        "t = lambda a: torch.from_numpy(a).cuda()\n"
-        "r = sd.evaluate(5, t(X), t(labels), A=t(A), W=t(W), c=1.0, gamma=0.5, k=1)\n"
-        "print(repr([r[f] for f in ('primal','dual','primal_loss','dual_loss')] + r['accuracy'][:3].tolist()))\n"
-    ) % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    """A forced chunk length (the library's test switch) runs the chunk loop on a small
+    problem; device and host-buffer forms must both give the unchunked result."""
+    import torch
+    from libsdca_b200 import binding as b
+    from tests.test_oracle_restatement import random_problem
+    rng = np.random.default_rng(8)
+    X, labels, _ = random_problem(rng, 700, 16, 9, np.float64, False)
+    A = rng.standard_normal((700, 9)) * 0.01
+    W = rng.standard_normal((9, 16))
+    t = lambda a: torch.from_numpy(a).cuda()
+    fields = ("primal", "dual", "primal_loss", "dual_loss")
     outs = []
-    for chunk in ("", "128"):
-        env = dict(os.environ, SDCAB_EVAL_CHUNK=chunk)
-        res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True)
-        assert res.returncode == 0, res.stderr
-        outs.append(np.array(eval(res.stdout.strip().splitlines()[-1])))
-    assert np.allclose(outs[0], outs[1], rtol=1e-13, atol=0)
+    try:
+        for chunk in (0, 128):
+            b.test_set("eval_chunk", chunk)
+            for args in ((t(X), t(labels), t(A), t(W)), (X, labels, A, W)):
+                r = cuda_lib.evaluate(5, args[0], args[1], A=args[2], W=args[3], c=1.0, gamma=0.5, k=1)
+                outs.append(np.array([r[f] for f in fields] + r["accuracy"][:3].tolist()))
+    finally:
+        b.test_set("eval_chunk", 0)
+    for o in outs[1:]:
+        assert np.allclose(outs[0], o, rtol=1e-13, atol=0)
+
+
+def test_host_form_shards_with_row_offsets(ref, cuda_lib):
+    """Two shards of a training set through the host-buffer entry point, the second with
+    a_row_offset > 0 into the whole A: their sums give the unsharded record and the
+    reference's."""
+    from libsdca_b200 import binding as b
+    from tests.test_oracle_restatement import random_problem
+    rng = np.random.default_rng(18)
+    n, d, m = 600, 24, 11
+    for kernel in (False, True):
+        X, labels, _ = random_problem(rng, n, d, m, np.float64, kernel)
+        A = -np.abs(rng.standard_normal((n, m))) * 0.01
+        A[np.arange(n), labels] = 0.03
+        W = None if kernel else rng.standard_normal((m, d))
+        whole = cuda_lib.evaluate("l2_entropy_topk", X, labels, A=A, W=W, kernel=kernel, c=1.0, k=3)
+        r = ref.evaluate("l2_entropy_topk", X, A, labels, W=W, kernel=kernel, c=1.0, k=3)
+        for f in ("primal", "dual", "primal_loss", "dual_loss"):
+            assert abs(whole[f] - r[f]) <= 1e-12 * max(1, abs(r[f])), (kernel, f)
+        # the same evaluation as two shards: device sums of each shard's host call are not
+        # exposed, so compare the record terms that add up over shards
+        cut = 250
+        obj = b.make_objective("l2_entropy_topk", c=1.0, k=3)
+        parts = []
+        for first, count in ((0, cut), (cut, n - cut)):
+            prob = b.make_problem(np.ascontiguousarray(X[first:first + count]),
+                                  np.ascontiguousarray(labels[first:first + count]), A=A, W=W,
+                                  kernel=kernel, a_row_offset=first,
+                                  include_primal_regularizer=(first == 0))
+            prob.m = m
+            rec = b.EvalRecord()
+            acc = np.zeros(m)
+            fn = cuda_lib.lib().sdcab_eval_f64
+            rc = fn(C.byref(obj), C.byref(prob), C.byref(rec), acc.ctypes.data_as(C.c_void_p))
+            assert rc == 0
+            parts.append((rec.primal_loss, rec.dual_loss, rec.primal_regularizer, rec.dual_regularizer))
+        sums = np.sum(np.array(parts), axis=0)
+        want = (whole["primal_loss"], whole["dual_loss"], whole["primal_regularizer"],
+                whole["dual_regularizer"])
+        assert np.allclose(sums, want, rtol=1e-12, atol=1e-14), (kernel, sums, want)
+
+
+def test_host_forms_reject_bad_labels(cuda_lib):
+    """Label checks of the reference (data/output.h:169-215) happen on the host, before
+    anything is launched."""
+    rng = np.random.default_rng(4)
+    n, d, m = 20, 5, 4
+    X = rng.standard_normal((n, d)); W = rng.standard_normal((m, d)); A = np.zeros((n, m))
+    labels = rng.integers(0, m, n).astype(np.int64)
+    bad = labels.copy(); bad[7] = m
+    with pytest.raises(cuda_lib.SdcabError) as e:
+        cuda_lib.evaluate("msvm", X, bad, A=A, W=W)
+    assert e.value.status == -5
+    bad[7] = -1
+    with pytest.raises(cuda_lib.SdcabError) as e:
+        cuda_lib.evaluate("msvm", X, bad, A=A, W=W)
+    assert e.value.status == -5
+    # multilabel: duplicate / unsorted labels, empty example, first offset not zero
+    offsets = np.arange(0, 2 * n + 1, 2).astype(np.int64)
+    ml = np.tile(np.array([0, 2], dtype=np.int64), n)
+    assert cuda_lib.evaluate("mlsvm", X, ml, A=A, W=W, offsets=offsets)["primal"] == \
+        cuda_lib.evaluate("mlsvm", X, ml, A=A, W=W, offsets=offsets)["primal"]
+    for mutate in ("dup", "unsorted", "empty", "first"):
+        l2, o2 = ml.copy(), offsets.copy()
+        if mutate == "dup": l2[1] = 0
+        if mutate == "unsorted": l2[0], l2[1] = 2, 0
+        if mutate == "empty": o2[3] = o2[2]
+        if mutate == "first": o2[0] = 1
+        with pytest.raises(cuda_lib.SdcabError) as e:
+            cuda_lib.evaluate("mlsvm", X, l2, A=A, W=W, offsets=o2)
+        assert e.value.status == -5, mutate

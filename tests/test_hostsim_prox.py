@@ -4,20 +4,24 @@ This checks the algorithms; the warp plumbing is covered by the gpu tests."""
 import numpy as np
 import pytest
 
-from tests.util import float_precision_ok, stable_seed, PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree
+from tests.util import float_precision_ok, stable_seed, PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree, two_simplex_sort_defined
 
 
-@pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex"])
+@pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex", "two_simplex_sort"])
 @pytest.mark.parametrize("dtype,precision", [(np.float64, "double"), (np.float32, "double"),
                                               (np.float32, "float")])
 def test_matches_reference(ref, hostsim, name, dtype, precision):
     rng = np.random.default_rng(stable_seed(name, str(dtype), precision))
     for kind in ("normal", "pos", "neg", "mixed", "ties"):
         for m in (1, 2, 3, 5, 33, 200):
-            if name == "two_simplex" and m < 2:
+            if name.startswith("two_simplex") and m < 2:
                 continue
             a = regime(rng, 24, m, dtype, kind)
             kw = random_opts(rng, name, m)
+            if name == "two_simplex_sort":
+                a = a[two_simplex_sort_defined(ref, a, result=precision, **kw)]
+                if len(a) == 0:
+                    continue
             x_ref = ref.prox(name, a, result=precision, **kw)
             x, _ = hostsim.run(name, a, precision=precision, **kw)
             tol = tolerance(dtype, precision, m)

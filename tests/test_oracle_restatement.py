@@ -4,7 +4,7 @@ tests, and every objective's evaluation record on small random problems."""
 import numpy as np
 import pytest
 
-from tests.util import (PROX_SINGLE, float_precision_ok, random_opts, regime, scaled_error,
+from tests.util import (PROX_SINGLE, two_simplex_sort_defined, float_precision_ok, random_opts, regime, scaled_error,
                         stable_seed, tolerance)
 
 
@@ -15,17 +15,21 @@ def port():
     return refapi.restatement()
 
 
-@pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex"])
+@pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex", "two_simplex_sort"])
 @pytest.mark.parametrize("dtype,precision", [(np.float64, "double"), (np.float32, "double"),
                                               (np.float32, "float")])
 def test_prox_matches_reference(ref, port, name, dtype, precision):
     rng = np.random.default_rng(stable_seed("port", name, str(dtype), precision))
     for kind in ("normal", "pos", "neg", "mixed", "ties"):
         for m in (1, 2, 5, 33, 200):
-            if name == "two_simplex" and m < 2:
+            if name.startswith("two_simplex") and m < 2:
                 continue
             a = regime(rng, 16, m, dtype, kind)
             kw = random_opts(rng, name, m)
+            if name == "two_simplex_sort":
+                a = a[two_simplex_sort_defined(ref, a, result=precision, **kw)]
+                if len(a) == 0:
+                    continue
             x_ref = ref.prox(name, a, result=precision, **kw)
             x = port.prox(name, a, result=precision, **kw)
             tol = tolerance(dtype, precision, m)

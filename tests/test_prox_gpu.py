@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from tests.util import float_precision_ok, stable_seed, PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree
+from tests.util import float_precision_ok, stable_seed, PROX_SINGLE, random_opts, regime, scaled_error, tolerance, thresholds_agree, two_simplex_sort_defined
 
 pytestmark = pytest.mark.gpu
 
@@ -15,18 +15,25 @@ def run_dev(mod, name, a, **kw):
     return t.cpu().numpy()
 
 
-@pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex"])
+@pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex", "two_simplex_sort"])
 @pytest.mark.parametrize("dtype,precision", [(np.float64, "double"), (np.float32, "double"),
                                               (np.float32, "float")])
 def test_regimes_match_reference(ref, cuda_lib, name, dtype, precision):
+    # two_simplex_sort (prox/two_simplex_sort.h:24-111 of the reference) solves the same
+    # problem as two_simplex by sorting; here it is compared under its own name with the
+    # reference's sort-based routine
     rng = np.random.default_rng(stable_seed(name, str(dtype), precision, 1))
     for kind in ("normal", "pos", "neg", "mixed", "ties"):
         for m in (1, 2, 3, 5, 31, 32, 33, 200, 1023, 1024, 1025):
-            if name == "two_simplex" and m < 2:
+            if name.startswith("two_simplex") and m < 2:
                 continue
             n = 37 if m < 1000 else 9
             a = regime(rng, n, m, dtype, kind)
             kw = random_opts(rng, name, m)
+            if name == "two_simplex_sort":
+                a = a[two_simplex_sort_defined(ref, a, result=precision, **kw)]
+                if len(a) == 0:
+                    continue
             x_ref = ref.prox(name, a, result=precision, **kw)
             x = run_dev(cuda_lib, name, a, precision=precision, **kw)
             tol = tolerance(dtype, precision, m)

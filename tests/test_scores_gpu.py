@@ -54,23 +54,18 @@ def test_scores_match_float64_product(cuda_lib, dtype):
 
 
 def test_tensor_core_and_cuda_core_gemm_agree(cuda_lib):
-    """SDCAB_GEMM=simt forces the CUDA-core kernel: both must agree to float accuracy."""
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    code = (
-        "import sys; sys.path.insert(0, %r)\n"
-        "import numpy as np, libsdca_b200 as sd\n"
-        "from tests.test_scores_gpu import scores\n"
-        "rng = np.random.default_rng(3)\n"
-        "X = rng.standard_normal((384, 1024)).astype(np.float32); W = rng.standard_normal((1000, 1024)).astype(np.float32)\n"
-        "np.save(sys.argv[1], scores(sd, X, W=W))\n") % root
-    import tempfile
-    with tempfile.TemporaryDirectory() as tmp:
-        outs = []
-        for mode in ("tc", "simt"):
-            path = os.path.join(tmp, mode + ".npy")
-            env = dict(os.environ, SDCAB_GEMM=mode)
-            res = subprocess.run([sys.executable, "-c", code, path], env=env, capture_output=True, text=True)
-            assert res.returncode == 0, res.stderr
-            outs.append(np.load(path))
+    """The library's test switch forces the CUDA-core kernel: both must agree to float
+    accuracy, and they are two different kernels."""
+    from libsdca_b200 import binding as b
+    rng = np.random.default_rng(3)
+    X = rng.standard_normal((384, 1024)).astype(np.float32)
+    W = rng.standard_normal((1000, 1024)).astype(np.float32)
+    outs = []
+    try:
+        for simt in (0, 1):
+            b.test_set("gemm_simt", simt)
+            outs.append(scores(cuda_lib, X, W=W))
+    finally:
+        b.test_set("gemm_simt", 0)
     assert not np.array_equal(outs[0], outs[1])          # two different kernels really ran
     assert np.abs(outs[0] - outs[1]).max() <= 1e-5 * np.abs(outs[1]).max()
