@@ -115,52 +115,77 @@ class ClockSampler(threading.Thread):
                 "samples": len(sm)}
 
 
+def _checker():
+    from oracle import refapi
+    if refapi.have_reference():
+        return refapi.reference(), "reference"
+    from oracle import build_oracle
+    build_oracle.build_restatement()
+    return refapi.restatement(), "port"
+
+
+def cpu_prox_step(checker, a, work, threads):
+    """One step of the workload on the host: both operators, in place on a prepared
+    buffer (what matsdca_prox does without an output argument); refilling the buffer
+    is outside the timed part.  Returns the timed seconds."""
+    dt = 0.0
+    for name, kw in OPS:
+        np.copyto(work, a)
+        t0 = time.perf_counter()
+        checker.prox(name, work, nthreads=threads, inplace=True, **kw)
+        dt += time.perf_counter() - t0
+    return dt
+
+
 def cpu_baseline(sample_rows, threads, seed):
     """The reference's CPU implementation (its own headers, compiled unmodified)
     on a bounded sample of the same workload."""
     from libsdca_b200 import synth
-    from oracle import refapi
-    if refapi.have_reference():
-        checker, kind = refapi.reference(), "reference"
-    else:
-        from oracle import build_oracle
-        build_oracle.build_restatement()
-        checker, kind = refapi.restatement(), "port"
+    checker, kind = _checker()
     a = synth.topk_rows(rows=sample_rows, seed=seed)
-    t0 = time.perf_counter()
-    for name, kw in OPS:
-        checker.prox(name, a, nthreads=threads, **kw)
-    dt = time.perf_counter() - t0
+    work = np.empty_like(a)
+    dt = cpu_prox_step(checker, a, work, threads)
     return {"value": 2 * sample_rows / dt, "unit": "rows/s", "cores": threads, "kind": kind,
             "sample": "%d rows x %d float32 (same generator as the bench), top-k simplex + "
-                      "top-k cone, k=5, thresholds in double, rows split over %d host threads"
+                      "top-k cone, k=5, thresholds in double, in place, rows split over %d host threads"
                       % (sample_rows, M, threads), "seconds": dt}
 
 
 def run_reference(args, rank, world):
-    """`--impl reference`: the reference's own CPU path for the same metric."""
+    """`--impl reference`: the reference's own CPU path for the same metric, on the same
+    number of rows per step as the GPU arm."""
     if rank != 0:
         return
+    from libsdca_b200 import synth
     threads = max(1, min(os.cpu_count() or 1, 64))
-    sample_rows = args.cpu_rows
+    rows = args.rows
+    checker, kind = _checker()
+    a = synth.topk_rows(rows=rows, seed=2)
+    work = np.empty_like(a)
     times = []
-    base = None
     for i in range(args.warmup + args.steps):
-        base = cpu_baseline(sample_rows, threads, seed=2)
+        dt = cpu_prox_step(checker, a, work, threads)
         if i >= args.warmup:
-            times.append(base["seconds"])
+            times.append(dt)
     total = sum(times)
-    value = 2 * sample_rows * args.steps / total
-    base["value"] = value
+    value = 2 * rows * args.steps / total
+    base = {"value": value, "unit": "rows/s", "cores": threads, "kind": kind,
+            "sample": "every step: %d rows x %d float32 (the GPU arm's rows per GPU), top-k simplex + "
+                      "top-k cone, k=5, thresholds in double, in place on a prepared buffer, rows split "
+                      "over %d host threads" % (rows, M, threads),
+            "seconds": total, "median_step_seconds": float(np.median(times))}
     out = {"impl": "reference", "metric": "prox rows/s (top-k simplex + top-k cone, k=5)",
            "value": value, "unit": "rows/s", "n_gpus": args.gpus, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-           "data": "synthetic", "config": workload_config(sample_rows, world, "bounded sample per step"),
+           "data": "synthetic",
+           "config": workload_config(rows, world, "host arm: one process on this box's cores at every N"),
            "cpu_baseline": base,
            "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0,
                    "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
+    if not args.no_gap:
+        out["gap_eval"] = {"cpu_baseline": gap_cpu_baseline(args, threads)}
     print(json.dumps(out))
 
 
@@ -271,21 +296,17 @@ def gap_roofline(tflops):
             "kernel": "gemm_tf32x3_kernel (tcgen05, TMA) + eval_loss_kernel"}
 
 
-def gap_config(args, rank, world, local_rank):
-    """Config 4: duality-gap evaluation, top-k hinge alpha (k = 5), feature input,
-    d = 4096, m = 1000, float32; examples sharded over the ranks, one all-reduce
-    of the sums vector.  --rows sets the examples per GPU (default 1048576 / N)."""
-    import torch
-    import libsdca_b200 as sd
-    from libsdca_b200 import binding as b
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    d, m, k, c = 4096, 1000, 5, 1.0
-    n_total = 1048576
-    n = args.rows if args.rows != FULL_ROWS else n_total // world
+GAP = dict(d=4096, m=1000, k=5, c=1.0, n_total=1048576)
+GAP_OBJECTIVES = (("l2_hinge_topk (gamma=0)", 0.0), ("l2_hinge_topk_smooth (gamma=1)", 1.0))
+GAP_FIELDS = ("primal", "dual", "primal_loss", "dual_loss", "primal_regularizer", "dual_regularizer")
+
+
+def gap_problem_device(torch, sd, n, rank):
+    """Config 4's data for one rank, generated on the device: class-conditional Gaussian
+    blobs (class means ~ N(0, I), noise sigma = 2, labels uniform), and a random feasible
+    dual point: v ~ N(0,1)^(m-1) projected onto the top-k simplex, a_j = -v_j, a_y = min(c, sum v)
+    -- the form an SDCA step leaves (objective/l2_hinge_topk.h:63-67 of the reference)."""
+    d, m, k, c = GAP["d"], GAP["m"], GAP["k"], GAP["c"]
     gen = torch.Generator(device="cuda").manual_seed(5)          # same class means on every rank
     means = torch.randn((m, d), generator=gen, device="cuda")
     gen.manual_seed(50 + rank)
@@ -295,15 +316,86 @@ def gap_config(args, rank, world, local_rank):
     for i in range(0, n, step_rows):                                # x_i = mean[y_i] + 2 N(0, I)
         j = min(n, i + step_rows)
         X[i:j] = means[labels[i:j]] + 2.0 * torch.randn((j - i, d), generator=gen, device="cuda")
-    # a random feasible dual point: v ~ N(0,1)^(m-1) projected onto the top-k simplex
     v = torch.randn((n, m - 1), generator=gen, device="cuda")
     # rows of 999 floats are not 16-byte aligned: the general kernel handles them
     sd.prox_(v, "topk_simplex", k=k, rhs=c)
     A = torch.zeros((n, m), device="cuda")
-    cols = torch.arange(m - 1, device="cuda")[None, :] + (torch.arange(m - 1, device="cuda")[None, :] >= labels[:, None])
+    ar = torch.arange(m - 1, device="cuda")[None, :]
+    cols = ar + (ar >= labels[:, None])
     A.scatter_(1, cols, -v)
     A[torch.arange(n, device="cuda"), labels] = torch.clamp(v.double().sum(dim=1), max=c).float()
     del v, cols
+    return X, labels, A
+
+
+def gap_problem_host(n, threads):
+    """The same family generated on the host with numpy and the reference's own prox, for
+    the arm that must not touch the GPU library."""
+    d, m, k, c = GAP["d"], GAP["m"], GAP["k"], GAP["c"]
+    checker, _ = _checker()
+    rng = np.random.default_rng(5)
+    means = rng.standard_normal((m, d), dtype=np.float32)
+    labels = rng.integers(0, m, n).astype(np.int64)
+    X = means[labels] + 2.0 * rng.standard_normal((n, d), dtype=np.float32)
+    v = rng.standard_normal((n, m - 1), dtype=np.float32)
+    checker.prox("topk_simplex", v, nthreads=threads, inplace=True, k=k, rhs=c)
+    A = np.zeros((n, m), dtype=np.float32)
+    ar = np.arange(m - 1)[None, :]
+    np.put_along_axis(A, ar + (ar >= labels[:, None]), -v, axis=1)
+    A[np.arange(n), labels] = np.minimum(c, v.astype(np.float64).sum(axis=1)).astype(np.float32)
+    W = np.ascontiguousarray(A.T @ X)                               # d x m column major == (m, d)
+    return X, labels, A, W
+
+
+def gap_cpu_baseline(args, threads, sample=None):
+    """The reference's evaluate_dataset (include/sdca/solver/eval.h:15-51: one gemv per
+    example, then loss, conjugate and rank) on a contiguous subsample of config 4, examples
+    split over the host threads and, for the reference as shipped, on one thread.  The loop
+    is linear in the number of examples, so the time for the full 1 048 576 is the sample's
+    time scaled by the ratio."""
+    from oracle import refapi
+    checker, kind = _checker()
+    n_s = args.gap_cpu_examples
+    if sample is None:
+        X, labels, A, W = gap_problem_host(n_s, threads)
+    else:
+        X, labels, A, W = sample
+        n_s = X.shape[0]
+    blas = refapi.find_openblas() if kind == "reference" else None
+    blas_name = "this repository's sequential CBLAS"
+    if blas and checker.use_blas(blas, 1) == 0:
+        blas_name = "OpenBLAS from the image, one BLAS thread per host thread"
+    kw = dict(W=W, c=GAP["c"], k=GAP["k"])
+    t0 = time.perf_counter()
+    rec_all = checker.evaluate("l2_hinge_topk", X, A, labels, nthreads=threads, **kw)
+    t_all = time.perf_counter() - t0
+    n_one = max(1024, n_s // 8)
+    t0 = time.perf_counter()
+    checker.evaluate("l2_hinge_topk", X[:n_one], A[:n_one], labels[:n_one], nthreads=1, **kw)
+    t_one = time.perf_counter() - t0
+    if blas:
+        checker.use_blas(None, 1)
+    scale = GAP["n_total"] / float(n_s)
+    return {"value": t_all * scale, "unit": "s per evaluation of 1048576 examples (scaled)",
+            "cores": threads, "kind": kind,
+            "sample": "evaluate_dataset, top-k hinge alpha k=5 gamma=0, on %d examples of config 4 "
+                      "(d=4096, m=1000, float32) split over %d host threads: %.2f s, scaled by %g; "
+                      "%s" % (n_s, threads, t_all, scale, blas_name),
+            "seconds_sample": t_all,
+            "one_thread": {"examples": n_one, "seconds": t_one,
+                           "scaled_seconds": t_one * GAP["n_total"] / float(n_one)},
+            "record_sample": {f: rec_all[f] for f in GAP_FIELDS}}
+
+
+def gap_measure(args, rank, world, dist, torch, sd):
+    """Seconds per duality-gap evaluation of config 4 (top-k hinge alpha k = 5, features,
+    d = 4096, m = 1000, 1 048 576 examples, float32) with the examples sharded over the
+    ranks and one all-reduce of the 8 + m sums inside the timed region; the same through
+    the host-buffer C ABI; the reference's evaluate_dataset on a subsample beside it."""
+    from libsdca_b200 import binding as b
+    d, m, k, c, n_total = GAP["d"], GAP["m"], GAP["k"], GAP["c"], GAP["n_total"]
+    n = args.gap_examples if args.gap_examples > 0 else n_total // world
+    X, labels, A = gap_problem_device(torch, sd, n, rank)
     # W = X A' (d x m, stored (m, d)): the library's eval_recompute_primal, timed as setup
     torch.cuda.synchronize()
     t_primal = time.perf_counter()
@@ -313,11 +405,13 @@ def gap_config(args, rank, world, local_rank):
     if dist is not None:
         dist.all_reduce(W)
     torch.cuda.synchronize()
-    results = {}
     ws_bytes = sd.lib().sdcab_eval_workspace_bytes
     ws_bytes.restype = C.c_size_t
     workspace = torch.empty(ws_bytes(C.c_int64(n), C.c_int64(m), C.c_int64(4)), dtype=torch.uint8, device="cuda")
-    for label, gamma in (("l2_hinge_topk (gamma=0)", 0.0), ("l2_hinge_topk_smooth (gamma=1)", 1.0)):
+    reps = max(5, min(args.steps, 10))
+    warm = max(3, min(args.warmup, 5))
+    results = {}
+    for label, gamma in GAP_OBJECTIVES:
         obj = b.make_objective("topk_hinge_alpha", c=c, gamma=gamma, k=k)
         prob = b.make_problem(X, labels, A=A, W=W, include_primal_regularizer=(rank == 0))
         sums = torch.zeros(8 + m, dtype=torch.float64, device="cuda")
@@ -326,46 +420,165 @@ def gap_config(args, rank, world, local_rank):
             sd.eval_sums_(obj, prob, sums, "f32", workspace, workspace.numel())
             if dist is not None:
                 dist.all_reduce(sums)
-            return sums
 
-        for _ in range(max(1, min(args.warmup, 3))):
+        for _ in range(warm):
             one_eval()
+        times = []
+        for _ in range(reps):
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(); one_eval(); e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            if dist is not None:
+                t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            times.append(ms)
+        med = float(np.median(times))
+        rec = sd.eval_finish(obj, m, sums.cpu().numpy())
+        results[label] = {"seconds_per_eval": med * 1e-3, "best_seconds": min(times) * 1e-3,
+                          "evaluations_timed": reps,
+                          "tflops": 2.0 * d * m * n * world / (med * 1e-3) / 1e12,
+                          "record": {f: rec[f] for f in GAP_FIELDS + ("relative_gap",)},
+                          "top1": float(rec["accuracy"][0])}
+
+    # ---- end to end: host buffers through sdcab_eval_f32, each rank its shard, the record
+    # terms (sums over the shard's examples) added over the ranks
+    obj = b.make_objective("topk_hinge_alpha", c=c, gamma=0.0, k=k)
+    hX = torch.empty((n, d), dtype=torch.float32, pin_memory=True)
+    hA = torch.empty((n, m), dtype=torch.float32, pin_memory=True)
+    hX.copy_(X); hA.copy_(A)
+    hW = W.cpu().numpy(); hl = labels.cpu().numpy()
+    torch.cuda.synchronize()
+    hprob = b.make_problem(hX.numpy(), hl, A=hA.numpy(), W=hW, include_primal_regularizer=(rank == 0))
+    rec = b.EvalRecord()
+    acc = np.zeros(m)
+    fn = sd.lib().sdcab_eval_f32
+
+    def e2e_eval():
+        rc = fn(C.byref(obj), C.byref(hprob), C.byref(rec), acc.ctypes.data_as(C.c_void_p))
+        if rc != 0:
+            raise sd.SdcabError(rc, "sdcab_eval_f32")
+        terms = np.array([rec.primal_loss, rec.dual_loss, rec.primal_regularizer, rec.dual_regularizer,
+                          acc[0] * n], dtype=np.float64)
+        if dist is not None:
+            t = torch.from_numpy(terms).cuda()
+            dist.all_reduce(t)
+            terms = t.cpu().numpy()
+        return terms
+
+    e2e_eval()
+    e2e_times = []
+    terms = None
+    for _ in range(max(2, args.e2e_steps)):
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
-        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-        steps = max(1, min(args.steps, 5))
-        e0.record()
-        for _ in range(steps):
-            one_eval()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
+        t0 = time.perf_counter()
+        terms = e2e_eval()
+        dt = time.perf_counter() - t0
         if dist is not None:
-            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            t = torch.tensor([dt], dtype=torch.float64, device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        rec = sd.eval_finish(obj, m, sums.cpu().numpy())
-        results[label] = {"seconds_per_eval": ms * 1e-3,
-                          "tflops": 2.0 * d * m * n * world / (ms * 1e-3) / 1e12,
-                          "record": {f: rec[f] for f in ("primal", "dual", "primal_loss", "dual_loss",
-                                                         "primal_regularizer", "relative_gap")},
-                          "top1": float(rec["accuracy"][0])}
+            dt = float(t.item())
+        e2e_times.append(dt)
+    e2e_s = float(np.median(e2e_times))
+    first = results[GAP_OBJECTIVES[0][0]]
+    dev_rec = first["record"]
+    e2e = {"seconds_per_eval": e2e_s, "evaluations_timed": len(e2e_times),
+           "h2d_bytes_per_eval": (n * d * 4 + n * m * 4 + n * 8) * world + d * m * 4 * world,
+           "d2h_bytes_per_eval": (8 + m) * 8 * world,
+           "pcie_gbs_per_rank": (n * d * 4 + n * m * 4) / e2e_s / 1e9,
+           "record_vs_device": {
+               "primal_loss": abs(terms[0] - dev_rec["primal_loss"]) / max(1.0, abs(dev_rec["primal_loss"])),
+               "dual_loss": abs(terms[1] - dev_rec["dual_loss"]) / max(1.0, abs(dev_rec["dual_loss"])),
+               "primal_regularizer": abs(terms[2] - dev_rec["primal_regularizer"]) / max(1.0, abs(dev_rec["primal_regularizer"])),
+               "top1": abs(terms[4] / (n * world) - first["top1"])}}
+    del hX, hA
+
+    # ---- the reference on a subsample of rank 0's shard, every term compared with the
+    # device evaluation of the same examples
+    cpu = None
+    parity = None
+    if rank == 0 and not args.no_cpu_baseline:
+        n_s = min(n, args.gap_cpu_examples)
+        Xs, As, ls = X[:n_s].contiguous(), A[:n_s].contiguous(), labels[:n_s].contiguous()
+        Ws = sd.primal_from_dual(Xs, As)        # the sample's own W, so that its gap is a real gap
+        sample = (Xs.cpu().numpy(), ls.cpu().numpy(), As.cpu().numpy(), Ws.cpu().numpy())
+        threads = max(1, min(os.cpu_count() or 1, 64))
+        cpu = gap_cpu_baseline(args, threads, sample)
+        dev = sd.evaluate(b.make_objective("topk_hinge_alpha", c=c, gamma=0.0, k=k), Xs, ls, A=As, W=Ws)
+        ref_rec = cpu["record_sample"]
+        exact_reg = 0.5 * float((sample[3].astype(np.float64) ** 2).sum())
+        parity = {f: abs(dev[f] - ref_rec[f]) / max(1.0, abs(ref_rec[f])) for f in GAP_FIELDS}
+        # the same examples with the dual point scaled down until the margins are of order
+        # one and some are violated (at the benchmark's own dual point every primal loss is 0)
+        s2 = 0.5 / (n_s / 1000.0 * 4096.0 + 2.0e4)
+        As2 = (As * s2).contiguous()
+        Ws2 = sd.primal_from_dual(Xs, As2)
+        checker, _ = _checker()
+        parity_scaled = {}
+        for label, gamma in GAP_OBJECTIVES:
+            name = "l2_hinge_topk" if gamma == 0.0 else "l2_hinge_topk_smooth"
+            r2 = checker.evaluate(name, sample[0], As2.cpu().numpy(), sample[1], W=Ws2.cpu().numpy(),
+                                  c=c, gamma=gamma, k=k, nthreads=threads)
+            d2 = sd.evaluate(b.make_objective("topk_hinge_alpha", c=c, gamma=gamma, k=k), Xs, ls, A=As2, W=Ws2)
+            parity_scaled[label] = {
+                "reference_primal_loss": r2["primal_loss"], "reference_dual_loss": r2["dual_loss"],
+                "primal_loss": abs(d2["primal_loss"] - r2["primal_loss"]) / max(1.0, abs(r2["primal_loss"])),
+                "dual_loss": abs(d2["dual_loss"] - r2["dual_loss"]) / max(1.0, abs(r2["dual_loss"])),
+                "accuracy_max_abs": float(np.abs(d2["accuracy"] - r2["accuracy"]).max())}
+        parity["scaled_dual_point"] = parity_scaled
+        parity["note"] = ("relative to max(1, |reference|) on %d examples; the reference sums 0.5 ||W||^2 "
+                          "over 4.1e6 float32 terms in float, this library in double: the regulariser "
+                          "terms (and primal / dual, which contain them) differ by the reference's own "
+                          "rounding; against the exact double value this library is at %.1e"
+                          % (n_s, abs(dev["primal_regularizer"] - exact_reg) / exact_reg))
+    out = {"workload": "config 4: duality-gap evaluation, top-k hinge alpha k=5, features d=%d, m=%d, "
+                       "%d examples in total, float32" % (d, m, n * world),
+           "examples_per_gpu": n, "n_gpus": world,
+           "scaling": "strong" if args.gap_examples <= 0 else "weak",
+           "collective": "one all_reduce(sum) of %d doubles per evaluation, inside the timed region" % (8 + m),
+           "timing": "CUDA events around each evaluation, median of %d, max over ranks" % reps,
+           "seconds_per_eval": first["seconds_per_eval"],
+           "results": results, "roofline": gap_roofline(first["tflops"] / world),
+           "e2e": e2e, "cpu_baseline": cpu, "parity_on_sample": parity,
+           "setup_primal_from_dual": {"seconds": t_primal, "tflops": 2.0 * d * m * n / t_primal / 1e12}}
+    del X, A, W, workspace
+    torch.cuda.empty_cache()
+    return out
+
+
+def gap_config(args, rank, world, local_rank):
+    """Config 4 on its own (`--config 4`): the gap evaluation as the line's metric."""
+    import torch
+    import libsdca_b200 as sd
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.rows != FULL_ROWS and args.gap_examples <= 0:
+        args.gap_examples = args.rows
+    g = gap_measure(args, rank, world, dist, torch, sd)
     if rank == 0:
-        first = results["l2_hinge_topk (gamma=0)"]
+        first = g["results"][GAP_OBJECTIVES[0][0]]
         print(json.dumps({
             "metric": "duality-gap evaluation seconds", "value": first["seconds_per_eval"], "unit": "s",
-            "n_gpus": world, "steps": max(1, min(args.steps, 5)), "warmup": max(1, min(args.warmup, 3)),
+            "n_gpus": world, "steps": first["evaluations_timed"], "warmup": 3,
             "ms_per_step": first["seconds_per_eval"] * 1e3, "higher_is_better": False,
-            "scaling": "strong" if args.rows == FULL_ROWS else "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": "config 4: gap evaluation, top-k hinge alpha k=5, features d=4096, m=1000, "
-                                   "%d examples per GPU, float32" % n, "examples_per_gpu": n,
-                       "collective": "one all_reduce(sum) of %d doubles" % (8 + m),
-                       "setup_primal_from_dual": {"seconds": t_primal,
-                                                  "tflops": 2.0 * d * m * n / t_primal / 1e12}},
-            "roofline": gap_roofline(first["tflops"]),
-            "results": results}))
+            "scaling": g["scaling"], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": g["workload"], "examples_per_gpu": g["examples_per_gpu"],
+                       "collective": g["collective"]},
+            "roofline": g["roofline"], "cpu_baseline": g["cpu_baseline"],
+            "e2e": {"value": g["e2e"]["seconds_per_eval"], "unit": "s",
+                    "h2d_bytes_per_step": g["e2e"]["h2d_bytes_per_eval"],
+                    "d2h_bytes_per_step": g["e2e"]["d2h_bytes_per_eval"]},
+            "gpu_launches": 8 * first["evaluations_timed"] * world,
+            "gap_eval": g}))
     if dist is not None:
         dist.destroy_process_group()
 
@@ -486,6 +699,14 @@ def main():
                     help="config 5: size of the problem the reference's solver is timed on")
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="benchmark configuration; 2 (default) is the headline")
+    ap.add_argument("--no-gap", action="store_true",
+                    help="leave the duality-gap evaluation (config 4) out of the default line")
+    ap.add_argument("--gap-examples", type=int, default=0,
+                    help="config 4: examples per GPU (default: 1048576 / N, strong scaling)")
+    ap.add_argument("--gap-cpu-examples", type=int, default=65536,
+                    help="config 4: examples of the subsample the reference's evaluate_dataset is timed on")
+    ap.add_argument("--regions", type=int, default=5,
+                    help="timed regions of --steps steps each; the median region is reported")
     ap.add_argument("--precision", default="double", choices=["double", "float"],
                     help="precision of thresholds and accumulators")
     args = ap.parse_args()
@@ -579,14 +800,20 @@ def main():
     # the W untimed warm-up steps run again here, so that the timed region starts on a busy GPU
     for _ in range(warmup):
         step()
-    barrier()
-    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    elapsed_ms = max_over_ranks(e0.elapsed_time(e1))
+    # `--regions` timed regions of exactly `--steps` steps each, every one bracketed by a
+    # barrier and a device synchronisation; the median region is the one reported (a single
+    # region of a few milliseconds reads a few per cent off from run to run)
+    region_ms = []
+    for _ in range(max(1, args.regions)):
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+        region_ms.append(max_over_ranks(e0.elapsed_time(e1)))
+    elapsed_ms = float(np.median(region_ms))
     keep_busy(4, 1.5)
     clocks = sampler.finish() if sampler else None
 
@@ -607,9 +834,38 @@ def main():
     t0 = time.perf_counter()
     for _ in range(args.e2e_steps):
         e2e_step()
+    own_e2e_s = time.perf_counter() - t0
     barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     checksum = float(pinned_out[:: max(1, rows // 64)].double().sum())
+    # per-rank PCIe rate of the host-buffer path (both directions run at once): slowest rank
+    pcie_gbs = -max_over_ranks(-(2 * rows * M * 4 * args.e2e_steps) / own_e2e_s / 1e9)
+    # what the platform gives the same buffers with no kernel in between: every rank copies its
+    # pinned input to the device and a device buffer to its pinned output at the same time
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def plain_copies():
+        with torch.cuda.stream(s_in):
+            a.copy_(pinned_in, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            pinned_out.copy_(out, non_blocking=True)
+        s_in.synchronize(); s_out.synchronize()
+
+    plain_copies()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        plain_copies()
+    own_copy_s = (time.perf_counter() - t0) / 3
+    barrier()
+    copy_gbs = -max_over_ranks(-(rows * M * 4) / own_copy_s / 1e9)
+    del pinned_in, pinned_out, a, out
+    torch.cuda.empty_cache()
+    sd.lib().sdcab_release_workspace()
+
+    gap = None
+    if not args.no_gap:
+        gap = gap_measure(args, rank, world, dist, torch, sd)
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
@@ -638,10 +894,19 @@ def main():
                              {k: rows * BYTES_PER_ROW / (v * 1e-3) / 1e9 for k, v in per_op_other.items()}},
             "e2e": {"value": 2.0 * rows * world * args.e2e_steps / e2e_s, "unit": "rows/s",
                     "h2d_bytes_per_step": 2 * rows * M * 4 * world, "d2h_bytes_per_step": 2 * rows * M * 4 * world,
-                    "steps": args.e2e_steps, "checksum": checksum},
-            "gpu_launches": 2 * args.steps * world,
+                    "steps": args.e2e_steps, "checksum": checksum,
+                    "pcie_gbs_each_way_slowest_rank": pcie_gbs,
+                    "plain_copy_gbs_each_way_slowest_rank": copy_gbs,
+                    "note": "the second figure is the same pinned buffers copied both ways at once by "
+                            "every rank with no kernel in between: the host side's ceiling for this path"},
+            "gpu_launches": 2 * args.steps * world * max(1, args.regions),
+            "timed_regions_ms": region_ms,
             "clocks": clocks,
         }
+        result["config"]["timing"] = ("%d regions of %d steps, each bracketed by barrier + synchronize; "
+                                      "value and ms_per_step are the median region's" % (len(region_ms), args.steps))
+        if gap is not None:
+            result["gap_eval"] = gap
         if not args.no_cpu_baseline and world == 1:
             threads = max(1, min(os.cpu_count() or 1, 64))
             result["cpu_baseline"] = cpu_baseline(args.cpu_rows, threads, seed=2)

@@ -85,8 +85,14 @@ class _Backend:
         return hasattr(self.lib, self.prefix + name)
 
     # rows of ``a`` are the vectors (n x m, C order)
-    def prox(self, name, a, result="double", nthreads=1, **kw):
-        a = np.array(a, order="C", copy=True)
+    def prox(self, name, a, result="double", nthreads=1, inplace=False, **kw):
+        """``inplace=True`` works on ``a`` itself (C-contiguous), as matsdca_prox does when
+        it is called without an output argument (src/matlab/mex_prox.cpp:113-119)."""
+        if inplace:
+            if not (isinstance(a, np.ndarray) and a.flags.c_contiguous and a.flags.writeable):
+                raise ValueError("inplace needs a writeable C-contiguous array")
+        else:
+            a = np.array(a, order="C", copy=True)
         n, m = a.shape
         o = make_opts(**kw)
         rc = self._fn("prox")(name.encode(), _dtype_code(a.dtype),
@@ -212,7 +218,16 @@ def find_openblas():
     import glob
     import sys
     for sp in sys.path:
-        hits = glob.glob(os.path.join(sp, "opencv_python_headless.libs", "libopenblas*.so*"))
+        folder = os.path.join(sp, "opencv_python_headless.libs")
+        hits = glob.glob(os.path.join(folder, "libopenblas*.so*"))
         if hits:
+            # its Fortran run-time lies beside it, outside the loader's search path: bring it
+            # in first so that the dlopen of the BLAS resolves it
+            try:
+                for dep in ("libquadmath*.so*", "libgfortran*.so*"):
+                    for f in glob.glob(os.path.join(folder, dep)):
+                        C.CDLL(f, mode=C.RTLD_GLOBAL)
+            except OSError:
+                return None
             return hits[0]
     return None

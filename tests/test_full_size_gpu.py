@@ -147,6 +147,42 @@ def test_config4_gap_1048576_examples_is_additive_over_shards(cuda_lib):
     g = cuda_lib.eval_finish(obj, m, small.cpu().numpy())
     for f in ("primal_loss", "dual_loss"):
         assert abs(g[f] - r[f]) <= 1e-5 * max(1.0, abs(r[f])), (f, g[f], r[f])
+    # At this dual point the margins are huge (W sums a million examples), so every primal
+    # loss above is zero.  The same slice with the dual point scaled down, and W built from
+    # the slice alone, has margins of order one, some of them violated: there the loss terms of
+    # both the plain and the smoothed objective are compared with the CPU checker's.
+    scale = 2.5e-5
+    Xs, ls = X[sl].contiguous(), labels[sl].contiguous()
+    As = (A[sl] * scale).contiguous()
+    Ws = (As.T @ Xs).contiguous()
+    for name, gamma in (("l2_hinge_topk", 0.0), ("l2_hinge_topk_smooth", 1.0)):
+        o = b.make_objective("topk_hinge_alpha", c=c, gamma=gamma, k=k)
+        r = checker().evaluate(name, Xs.cpu().numpy(), As.cpu().numpy(), ls.cpu().numpy(),
+                               W=Ws.cpu().numpy(), c=c, gamma=gamma, k=k)
+        assert r["primal_loss"] > 1.0, (name, r["primal_loss"])    # margins really are violated
+        small.zero_()
+        cuda_lib.eval_sums_(o, b.make_problem(Xs, ls, A=As, W=Ws), small, "f32")
+        g = cuda_lib.eval_finish(o, m, small.cpu().numpy())
+        for f in ("primal_loss", "dual_loss"):
+            assert abs(g[f] - r[f]) <= 1e-5 * max(1.0, abs(r[f])), (name, f, g[f], r[f])
+        assert np.abs(g["accuracy"] - r["accuracy"]).max() <= 2.0 / 256
+    # the smoothed objective (gamma = 1, the default of matsdca_fit) at full size: additive
+    # over shards, primal >= dual
+    obj1 = b.make_objective("topk_hinge_alpha", c=c, gamma=1.0, k=k)
+    whole1 = torch.zeros(8 + m, dtype=torch.float64, device="cuda")
+    cuda_lib.eval_sums_(obj1, b.make_problem(X, labels, A=A, W=W), whole1, "f32")
+    parts1 = torch.zeros(8 + m, dtype=torch.float64, device="cuda")
+    for s in range(4):
+        part = torch.zeros(8 + m, dtype=torch.float64, device="cuda")
+        prob = b.make_problem(X[s * q:(s + 1) * q], labels[s * q:(s + 1) * q], A=A, W=W,
+                              a_row_offset=s * q, include_primal_regularizer=(s == 0))
+        cuda_lib.eval_sums_(obj1, prob, part, "f32")
+        parts1 += part
+    whole1, parts1 = whole1.cpu().numpy(), parts1.cpu().numpy()
+    assert np.abs(whole1 - parts1).max() <= 1e-9 * np.abs(whole1).max()
+    rec1 = cuda_lib.eval_finish(obj1, m, whole1)
+    assert rec1["primal"] >= rec1["dual"] - 1e-9 * abs(rec1["primal"])
+    assert rec1["dual_loss"] < rec["dual_loss"]     # the smoothing term -gamma/(2c) sum a_j^2 is there
 
 
 def test_config5_crammer_singer_fit_50000_f64(cuda_lib):
