@@ -407,6 +407,11 @@ int sdcab_fit_f64(const sdcab_objective* obj, const sdcab_problem* host_train,
  *   "gemm_lose_a_tile", 0|1   1: the tensor-core product skips one operand tile
  *                      and runs with a short wait limit, so that one of its bounded
  *                      waits runs out and the call reports SDCAB_ERR_TIMEOUT
+ *   "gemm_single_cta", 0|1   1: the one-CTA tensor-core kernel instead of the
+ *                      paired-CTA one
+ *   "gemm_write_hi", 0|1   1: the paired kernel stores the TF32 head of every
+ *                      operand explicitly instead of leaving the truncation to the
+ *                      tensor core
  * Returns SDCAB_ERR_ARG for an unknown name.  Not thread safe. */
 int sdcab_test_set(const char* name, int64_t value);
 

@@ -23,6 +23,7 @@
 #include "common_host.h"
 #include "eval_host.h"
 #include "gemm_blocked.cuh"
+#include "gemm_pair.cuh"
 #include "gemm_tc.cuh"
 #include "losses.cuh"
 
@@ -231,7 +232,9 @@ struct EvalLayout {
 // tensor-core one.  0 / 0 is the library's normal behaviour.
 static long long g_test_eval_chunk = 0;
 static int g_test_force_simt = 0;
-static int g_test_short_wait = 0;
+static int g_test_lose_a_tile = 0;
+static int g_test_single_cta = 0;   // the one-CTA tensor-core kernel instead of the paired one
+static int g_test_write_hi = 0;     // the paired kernel writes the TF32 head explicitly
 
 // Chunks are bounded so that the product's grid (one row of thread blocks per 128
 // examples in grid.y for the CUDA-core kernel) stays inside the launch limits.
@@ -281,7 +284,9 @@ inline bool tensor_core_gemm_enabled() { return g_test_force_simt == 0; }
 
 inline int scores_tc(const float* X, const float* W, float* out, int M, int N, int K, long long ld,
                      int* tc_err, cudaStream_t stream) {
-  return tc::launch(X, W, out, M, N, K, ld, ld, N, tc_err, stream);
+  if (g_test_single_cta) return tc::launch(X, W, out, M, N, K, ld, ld, N, tc_err, stream);
+  return tc2::launch(X, W, out, M, N, K, ld, ld, N, tc_err, g_test_write_hi != 0,
+                     g_test_lose_a_tile != 0, stream);
 }
 inline int scores_tc(const double*, const double*, double*, int, int, int, long long, int*,
                      cudaStream_t) {
@@ -652,10 +657,9 @@ int sdcab_test_set(const char* name, int64_t value) {
   if (!name) return SDCAB_ERR_ARG;
   if (std::strcmp(name, "eval_chunk") == 0) { sdcab::g_test_eval_chunk = value; return SDCAB_OK; }
   if (std::strcmp(name, "gemm_simt") == 0) { sdcab::g_test_force_simt = value ? 1 : 0; return SDCAB_OK; }
-  if (std::strcmp(name, "gemm_lose_a_tile") == 0) {
-    sdcab::g_test_short_wait = value ? 1 : 0;
-    return SDCAB_OK;
-  }
+  if (std::strcmp(name, "gemm_lose_a_tile") == 0) { sdcab::g_test_lose_a_tile = value ? 1 : 0; return SDCAB_OK; }
+  if (std::strcmp(name, "gemm_single_cta") == 0) { sdcab::g_test_single_cta = value ? 1 : 0; return SDCAB_OK; }
+  if (std::strcmp(name, "gemm_write_hi") == 0) { sdcab::g_test_write_hi = value ? 1 : 0; return SDCAB_OK; }
   return SDCAB_ERR_ARG;
 }
 

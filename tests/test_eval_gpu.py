@@ -174,7 +174,8 @@ def test_host_form_shards_with_row_offsets(ref, cuda_lib):
     rng = np.random.default_rng(18)
     n, d, m = 600, 24, 11
     for kernel in (False, True):
-        X, labels, _ = random_problem(rng, n, d, m, np.float64, kernel)
+        X = rng.standard_normal((n, n if kernel else d))      # kernel input: n columns of K
+        labels = rng.integers(0, m, n).astype(np.int64)
         A = -np.abs(rng.standard_normal((n, m))) * 0.01
         A[np.arange(n), labels] = 0.03
         W = None if kernel else rng.standard_normal((m, d))
@@ -223,8 +224,7 @@ def test_host_forms_reject_bad_labels(cuda_lib):
     # multilabel: duplicate / unsorted labels, empty example, first offset not zero
     offsets = np.arange(0, 2 * n + 1, 2).astype(np.int64)
     ml = np.tile(np.array([0, 2], dtype=np.int64), n)
-    assert cuda_lib.evaluate("mlsvm", X, ml, A=A, W=W, offsets=offsets)["primal"] == \
-        cuda_lib.evaluate("mlsvm", X, ml, A=A, W=W, offsets=offsets)["primal"]
+    assert np.isfinite(cuda_lib.evaluate("mlsvm", X, ml, A=A, W=W, offsets=offsets)["primal"])
     for mutate in ("dup", "unsorted", "empty", "first"):
         l2, o2 = ml.copy(), offsets.copy()
         if mutate == "dup": l2[1] = 0

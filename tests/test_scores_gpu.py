@@ -11,7 +11,11 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(300, 64, 1000), (130, 12, 7), (70, 37, 133), (300, 64, 1024), (1, 4096, 1000),
-          (513, 100, 129), (128, 16, 128), (257, 4096, 1000), (129, 33, 5), (64, 32, 128)]
+          (513, 100, 129), (128, 16, 128), (257, 4096, 1000), (129, 33, 5), (64, 32, 128),
+          # the paired tensor-core kernel is persistent: more 256 x 256 tiles than SM pairs
+          # (several tiles per pair, accumulators handed over across tile boundaries), a
+          # contraction shorter than one accumulation chunk, ragged last tiles
+          (5000, 64, 1000), (9000, 1024, 1000), (700, 96, 300), (256, 32, 256), (255, 36, 257)]
 
 
 def scores(mod, X, W=None, A=None):
@@ -69,3 +73,69 @@ def test_tensor_core_and_cuda_core_gemm_agree(cuda_lib):
         b.test_set("gemm_simt", 0)
     assert not np.array_equal(outs[0], outs[1])          # two different kernels really ran
     assert np.abs(outs[0] - outs[1]).max() <= 1e-5 * np.abs(outs[1]).max()
+
+
+def test_tensor_core_variants_agree(cuda_lib):
+    """The paired-CTA kernel leaves the truncation of an operand to TF32 to the tensor
+    core; with the head written explicitly (test switch) the result must be the same bit
+    for bit, which is what shows that the hardware truncates.  The one-CTA kernel agrees
+    to float accuracy (its sums run in a different order)."""
+    from libsdca_b200 import binding as b
+    rng = np.random.default_rng(13)
+    X = rng.standard_normal((1000, 2048)).astype(np.float32)
+    W = rng.standard_normal((600, 2048)).astype(np.float32)
+    exact = X.astype(np.float64) @ W.astype(np.float64).T
+    try:
+        base = scores(cuda_lib, X, W=W)
+        b.test_set("gemm_write_hi", 1)
+        explicit = scores(cuda_lib, X, W=W)
+        b.test_set("gemm_write_hi", 0)
+        b.test_set("gemm_single_cta", 1)
+        single = scores(cuda_lib, X, W=W)
+    finally:
+        b.test_set("gemm_write_hi", 0)
+        b.test_set("gemm_single_cta", 0)
+    assert np.array_equal(base, explicit)
+    assert np.abs(base - single).max() <= 1e-5 * np.abs(single).max()
+    mag = np.abs(X).astype(np.float64) @ np.abs(W).astype(np.float64).T
+    eps = np.finfo(np.float32).eps
+    for got in (base, single):
+        assert (np.abs(got - exact) <= (16 + 2 * np.sqrt(2048)) * eps * mag).all()
+
+
+def test_a_wait_that_runs_out_becomes_a_status(cuda_lib):
+    """Every wait inside the tensor-core kernel is bounded.  With the test switch the
+    kernel skips one operand tile and runs with a short limit, so that a wait really runs
+    out: the roles leave their loops, tensor memory is freed, the call reports
+    SDCAB_ERR_TIMEOUT, and the next call on the same context works."""
+    import torch
+    from libsdca_b200 import binding as b
+    rng = np.random.default_rng(5)
+    X = rng.standard_normal((512, 256)).astype(np.float32)
+    W = rng.standard_normal((256, 256)).astype(np.float32)
+    tX, tW = torch.from_numpy(X).cuda(), torch.from_numpy(W).cuda()
+    labels = torch.zeros(512, dtype=torch.int64, device="cuda")
+    p = b.make_problem(tX, labels, W=tW, is_train=False)
+    out = torch.zeros((512, 256), dtype=torch.float32, device="cuda")
+    fn = cuda_lib.lib().sdcab_scores_f32_dev
+    try:
+        b.test_set("gemm_lose_a_tile", 1)
+        rc = fn(C.byref(p), C.c_void_p(out.data_ptr()), None)
+    finally:
+        b.test_set("gemm_lose_a_tile", 0)
+    torch.cuda.synchronize()
+    assert rc == -23, rc
+    assert cuda_lib.lib().sdcab_status_string(rc) == b"device_wait_timeout"
+    # the evaluation reports it through the sums vector's error word
+    A = torch.zeros((512, 256), dtype=torch.float32, device="cuda")
+    try:
+        b.test_set("gemm_lose_a_tile", 1)
+        with pytest.raises(cuda_lib.SdcabError) as e:
+            cuda_lib.evaluate("msvm", tX, labels, A=A, W=tW)
+        assert e.value.status == -23
+    finally:
+        b.test_set("gemm_lose_a_tile", 0)
+    good = scores(cuda_lib, X, W=W)
+    exact = X.astype(np.float64) @ W.astype(np.float64).T
+    mag = np.abs(X).astype(np.float64) @ np.abs(W).astype(np.float64).T
+    assert (np.abs(good - exact) <= (16 + 2 * np.sqrt(256)) * np.finfo(np.float32).eps * mag).all()
