@@ -284,9 +284,14 @@ inline bool tensor_core_gemm_enabled() { return g_test_force_simt == 0; }
 
 inline int scores_tc(const float* X, const float* W, float* out, int M, int N, int K, long long ld,
                      int* tc_err, cudaStream_t stream) {
-  if (g_test_single_cta) return tc::launch(X, W, out, M, N, K, ld, ld, N, tc_err, stream);
-  return tc2::launch(X, W, out, M, N, K, ld, ld, N, tc_err, g_test_write_hi != 0,
-                     g_test_lose_a_tile != 0, stream);
+  if (!g_test_single_cta) {
+    const int rc = tc2::launch(X, W, out, M, N, K, ld, ld, N, tc_err, g_test_write_hi != 0,
+                               g_test_lose_a_tile != 0, stream);
+    // NOT_IMPLEMENTED: the build's register count does not fit the paired kernel's
+    // hand-over of registers; the one-CTA kernel takes the product instead
+    if (rc != SDCAB_ERR_NOT_IMPLEMENTED) return rc;
+  }
+  return tc::launch(X, W, out, M, N, K, ld, ld, N, tc_err, stream);
 }
 inline int scores_tc(const double*, const double*, double*, int, int, int, long long, int*,
                      cudaStream_t) {

@@ -19,8 +19,8 @@
 //     as TMA delivered it serves as the head term; the worker warps only write the
 //     remainder  lo = x - tf32(x)  (exact in float) to a second buffer.  A build
 //     switch keeps the explicit head (hi written in place) for comparison.
-//   * Raw tiles and remainder tiles live in rings of their own (4 and 2 deep):
-//     TMA runs four stages ahead of the tensor core, the split one stage ahead.
+//   * Raw tiles and remainder tiles live in rings of their own (4 and 3 deep):
+//     TMA runs up to four stages ahead of the tensor core, the split up to two.
 //   * The kernel is persistent: a pair walks over the tiles t = pair, pair + P, ...
 //     with the class tile as the fast index, so that the pairs working at the same
 //     time share their rows of X through L2.
@@ -56,16 +56,24 @@ constexpr int kBNHalf = 128;      // rows of B per CTA
 constexpr int kBN = 256;          // columns of the pair's tile = accumulator columns per CTA
 constexpr int kBK = 32;           // floats per row of a stage = one 128-byte swizzle row
 constexpr int kRawStages = 4;
-constexpr int kLoStages = 2;
+constexpr int kLoStages = 3;
 constexpr int kChunk = 4;         // stages per TMEM accumulation chunk (128 contraction steps)
 constexpr int kWorkerWarps = 8;
 constexpr int kControlWarps = 4;  // one warpgroup: TMA, MMA + tensor memory, two idle warps
 constexpr int kThreads = 32 * (kControlWarps + kWorkerWarps);
 // Every quarter of the SM's register file hosts one control warp and two worker warps.
 // A worker keeps 128 running sums in registers, so the control warpgroup hands most of
-// its registers over (setmaxnreg): 56 * 128 + 224 * 256 = 64512 <= 65536.
-constexpr int kControlRegs = 56;
-constexpr int kWorkerRegs = 224;
+// its registers over (setmaxnreg).  The pool is what the launch allocated: the kernel's
+// register count (168 for 384 threads) times 384 = 64512.  setmaxnreg.inc blocks until
+// its registers are there, for ever if the numbers do not add up, so they are checked at
+// compile time against 168 and at run time against the count the compiler really chose:
+// 80 * 128 + 208 * 256 = 63488 <= 64512.  (The thread that issues the MMAs needs its
+// descriptors and barrier addresses in registers: with 56 it spilled inside the issue
+// loop, which is the critical path of the whole pair.)
+constexpr int kControlRegs = 80;
+constexpr int kWorkerRegs = 208;
+constexpr int kPoolRegsNeeded = kControlRegs * 32 * kControlWarps + kWorkerRegs * 32 * kWorkerWarps;
+static_assert(kPoolRegsNeeded <= 168 * kThreads, "setmaxnreg would wait for registers that never come");
 constexpr int kTileBytes = kBM * kBK * 4;                     // 16 KB, A and B halves alike
 constexpr int kRawBytes = 2 * kTileBytes;                     // A then B
 constexpr int kSmemTiles = kRawStages * kRawBytes + kLoStages * kRawBytes;
@@ -93,7 +101,11 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
   return out;
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  // Default semantics (release at CTA scope) on purpose: what the arrival publishes is
+  // shared memory of the arriving CTA, already ordered for the tensor core by
+  // fence.proxy.async, or a finished tcgen05.ld.  The cluster-scope release form cost
+  // about a thousand clocks per stage here (3.2 ms -> 2.3 ms for 65 536 examples).
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -111,7 +123,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, int* err
                                          unsigned limit) {
   for (unsigned i = 0; i < limit; ++i) {
     if (mbar_try_cluster(bar, parity)) return true;
-    if (i > 64) __nanosleep(32);
+    if (i > 2048) __nanosleep(64);
     if ((i & 255) == 255 && *reinterpret_cast<volatile int*>(err) != 0) return false;
   }
   atomicCAS(err, 0, code);
@@ -290,7 +302,9 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     const int wt = threadIdx.x - 32 * kControlWarps;   // 0..255
     const int quarter = warp & 3;               // TMEM lanes 32*quarter .. +31 belong to this warp
     const int half = (warp - kControlWarps) >> 2;      // accumulator columns 128*half .. +127
-    const uint32_t ready_remote[kLoStages] = {map_to_rank(bar_ready(0), 0), map_to_rank(bar_ready(1), 0)};
+    uint32_t ready_remote[kLoStages];
+#pragma unroll
+    for (int s = 0; s < kLoStages; ++s) ready_remote[s] = map_to_rank(bar_ready(s), 0);
     const uint32_t acc_free_remote[2] = {map_to_rank(bar_acc_free(0), 0), map_to_rank(bar_acc_free(1), 0)};
     float acc[kBN / 2];
 #pragma unroll
@@ -320,11 +334,16 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a,
               "=r"(r[14]), "=r"(r[15])
             : "r"(taddr) : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        // the first chunk of a tile starts the sums anew (a select rather than a reset of
-        // the registers after the store: a conditional reset makes the compiler keep a
-        // second copy of the 128 sums)
+        // the first chunk of a tile starts the sums anew (here, not by a reset of the
+        // registers after the store: that makes the compiler keep a second copy of the 128
+        // sums); `first` is the same for the whole warp
+        if (first) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) acc[c0 + j] = (first ? 0.0f : acc[c0 + j]) + __uint_as_float(r[j]);
+          for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(r[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[c0 + j] += __uint_as_float(r[j]);
+        }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -367,7 +386,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (!ok) break;
         float4* ar = reinterpret_cast<float4*>(a_raw(s4));   // A then B, contiguous
         float4* al = reinterpret_cast<float4*>(a_lo(s2));
-#pragma unroll 2
+#pragma unroll
         for (int j = 0; j < kRawBytes / 16 / (32 * kWorkerWarps); ++j) {
           const int i = wt + j * 32 * kWorkerWarps;
           const float4 v = ar[i];
@@ -382,7 +401,10 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         // generic-proxy writes must be visible to the tensor core (async proxy)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(ready_remote[s2]);
+        if (lane == 0) {
+#pragma unroll
+          for (int q = 0; q < kLoStages; ++q) if (q == s2) mbar_arrive_cluster(ready_remote[q]);
+        }
       }
       // A chunk whose last stage was split kLoStages stages ago has been multiplied: the
       // split just done had to wait for that stage's lo buffer, which the tensor core
@@ -425,6 +447,10 @@ inline int launch(const float* A, const float* B, float* C, int M, int N, int K,
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc) return rc;
+  // the register hand-over inside the kernel needs the pool it was sized for
+  cudaFuncAttributes attr;
+  SDCAB_CUDA_TRY(cudaFuncGetAttributes(&attr, kernel));
+  if (attr.numRegs * kThreads < kPoolRegsNeeded) return SDCAB_ERR_NOT_IMPLEMENTED;
   Params p;
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.err = err_dev;
   p.tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
