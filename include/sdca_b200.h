@@ -397,6 +397,106 @@ int sdcab_fit_f64(const sdcab_objective* obj, const sdcab_problem* host_train,
                   const sdcab_fit_criteria* criteria, const int64_t* permutations,
                   sdcab_eval_record* evals, int64_t evals_cap, sdcab_fit_result* result);
 
+/*
+ * The fit with its whole evaluation history and with held-out sets: after every
+ * evaluation of the training set the reference evaluates each test set as well
+ * (solver::evaluate_solution, include/sdca/solver.h:120-132; matsdca_fit takes the
+ * sets as a cell array, src/matlab/mex_solve.cpp:473-501).  All arrays are host
+ * memory owned by the caller; any of them may be NULL.
+ */
+typedef struct sdcab_fit_history {
+  int64_t cap;                 /* evaluations the arrays below have room for               */
+  int64_t num_tests;           /* held-out sets                                             */
+  const sdcab_problem* tests;  /* num_tests problems with is_train = 0: x (features, or the
+                                * kernel columns K_tst = X_trn' X_tst, d = n_train rows),
+                                * n, labels, offsets; d and m as in the training set; a, w,
+                                * w0 are taken from the training problem.  Same kind of
+                                * pointers (device or host) as the training problem.        */
+  sdcab_eval_record* train;    /* cap records of the training set                          */
+  double* train_accuracy;      /* cap x m cumulative top-k accuracies (multiclass)         */
+  int64_t* epoch;              /* cap: the epoch each evaluation was made after            */
+  double* wall_seconds;        /* cap: wall-clock seconds since the start of the fit       */
+  sdcab_eval_record* test;     /* cap x num_tests, evaluation e of set t at e*num_tests+t:
+                                * primal_loss and rank_loss are set (eval_test,
+                                * include/sdca/solver/eval/types.h:127-172)                 */
+  double* test_accuracy;       /* cap x num_tests x m                                      */
+} sdcab_fit_history;
+
+int sdcab_fit_history_f32_dev(const sdcab_objective* obj, const sdcab_problem* train,
+                              const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                              const sdcab_fit_history* history, sdcab_fit_result* result,
+                              void* stream);
+int sdcab_fit_history_f64_dev(const sdcab_objective* obj, const sdcab_problem* train,
+                              const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                              const sdcab_fit_history* history, sdcab_fit_result* result,
+                              void* stream);
+/* Host buffers (training and test sets are copied to the device). */
+int sdcab_fit_history_f32(const sdcab_objective* obj, const sdcab_problem* host_train,
+                          const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                          const sdcab_fit_history* history, sdcab_fit_result* result);
+int sdcab_fit_history_f64(const sdcab_objective* obj, const sdcab_problem* host_train,
+                          const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                          const sdcab_fit_history* history, sdcab_fit_result* result);
+
+/* ------------------------------------------------------------- front end ---- */
+
+/*
+ * matsdca_fit without Matlab (src/matlab/mex_solve.cpp:473-620, 722-800): options in,
+ * model out, host buffers.  Defaults are the reference's: objective msvm_smooth
+ * (mex_solve.cpp:15), c = 1, gamma = 1, k = 1, is_dual = 0, epsilon = 1e-3,
+ * max_epoch = 1000, eval_epoch = 10, no time limits, double precision.
+ */
+typedef struct sdcab_dataset {
+  int64_t n;               /* examples                                               */
+  const void* x;           /* d x n features, or n_train x n Gram matrix columns     */
+  const int64_t* labels;   /* 0-based or 1-based like the reference accepts them
+                            * (data/output.h:169-182); multilabel: concatenated     */
+  const int64_t* offsets;  /* multilabel objectives only: n + 1 offsets              */
+} sdcab_dataset;
+
+typedef struct sdcab_train_options {
+  const char* objective;   /* a name sdcab_objective_from_name accepts; NULL = default */
+  double c, gamma;
+  int64_t k;
+  int32_t is_dual;         /* 1: the data are Gram matrices (kernel input)          */
+  int32_t precision;       /* SDCAB_PRECISION_*                                     */
+  sdcab_fit_criteria criteria;
+  int64_t num_dimensions;  /* d of the features; ignored for Gram matrices          */
+  int64_t num_classes;     /* 0: largest label + 1, as the reference derives it     */
+  const void* W0;          /* optional proximal centre, d x m (features only)       */
+  int32_t warm_start;      /* 1: model.A (and model.W) hold the starting point;
+                            * 0: they start from zero (W from W0 when W0 is given)  */
+  int32_t reserved;
+} sdcab_train_options;
+
+void sdcab_train_options_default(sdcab_train_options* options);
+
+/* The fields of matsdca_fit's model struct (mex_solve.cpp:153-376).  A and W are
+ * caller-provided buffers (m x n and d x m; W may be NULL for Gram input); the
+ * history arrays as in sdcab_fit_history (test sets come from the datasets). */
+typedef struct sdcab_model {
+  void* A;
+  void* W;
+  int64_t num_dimensions, num_examples, num_classes;
+  int32_t is_dual, objective_id;
+  char objective[40];
+  double c, gamma;
+  int64_t k;
+  sdcab_fit_criteria criteria;
+  int32_t status, data_precision, precision, labels_one_based;
+  int64_t epoch;
+  double cpu_time, wall_time, solve_time, eval_time, relative_gap;
+  int64_t num_evals;
+  sdcab_fit_history history;   /* cap and the arrays are set by the caller; tests is
+                                * filled in by the call and not valid afterwards   */
+} sdcab_model;
+
+/* datasets[0] is the training set, the others are evaluated only. */
+int sdcab_train_f32(const sdcab_dataset* datasets, int64_t num_datasets,
+                    const sdcab_train_options* options, sdcab_model* model);
+int sdcab_train_f64(const sdcab_dataset* datasets, int64_t num_datasets,
+                    const sdcab_train_options* options, sdcab_model* model);
+
 /* ------------------------------------------------------------- testing ---- */
 
 /* Switches for the library's own tests; production code never needs them.

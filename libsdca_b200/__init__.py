@@ -27,4 +27,5 @@ from .binding import (  # noqa: F401
     fit_,
     epoch_permutations,
     primal_from_dual,
+    train,
 )

@@ -310,6 +310,69 @@ class FitResult(C.Structure):
                 ("wall_seconds", C.c_double)]
 
 
+class FitHistory(C.Structure):
+    _fields_ = [("cap", C.c_int64), ("num_tests", C.c_int64), ("tests", C.c_void_p),
+                ("train", C.c_void_p), ("train_accuracy", C.c_void_p), ("epoch", C.c_void_p),
+                ("wall_seconds", C.c_void_p), ("test", C.c_void_p), ("test_accuracy", C.c_void_p)]
+
+
+class Dataset(C.Structure):
+    _fields_ = [("n", C.c_int64), ("x", C.c_void_p), ("labels", C.c_void_p), ("offsets", C.c_void_p)]
+
+
+class TrainOptions(C.Structure):
+    _fields_ = [("objective", C.c_char_p), ("c", C.c_double), ("gamma", C.c_double), ("k", C.c_int64),
+                ("is_dual", C.c_int32), ("precision", C.c_int32), ("criteria", FitCriteria),
+                ("num_dimensions", C.c_int64), ("num_classes", C.c_int64), ("W0", C.c_void_p),
+                ("warm_start", C.c_int32), ("reserved", C.c_int32)]
+
+
+class Model(C.Structure):
+    _fields_ = [("A", C.c_void_p), ("W", C.c_void_p), ("num_dimensions", C.c_int64),
+                ("num_examples", C.c_int64), ("num_classes", C.c_int64), ("is_dual", C.c_int32),
+                ("objective_id", C.c_int32), ("objective", C.c_char * 40), ("c", C.c_double),
+                ("gamma", C.c_double), ("k", C.c_int64), ("criteria", FitCriteria),
+                ("status", C.c_int32), ("data_precision", C.c_int32), ("precision", C.c_int32),
+                ("labels_one_based", C.c_int32), ("epoch", C.c_int64), ("cpu_time", C.c_double),
+                ("wall_time", C.c_double), ("solve_time", C.c_double), ("eval_time", C.c_double),
+                ("relative_gap", C.c_double), ("num_evals", C.c_int64), ("history", FitHistory)]
+
+
+class _HistoryBuffers:
+    """Host arrays behind a FitHistory (kept alive with it)."""
+
+    def __init__(self, cap, m, num_tests):
+        self.cap, self.m, self.num_tests = cap, m, num_tests
+        self.train = (EvalRecord * cap)()
+        self.train_accuracy = np.zeros((cap, m))
+        self.epoch = np.zeros(cap, dtype=np.int64)
+        self.wall = np.zeros(cap)
+        self.test = (EvalRecord * max(1, cap * num_tests))()
+        self.test_accuracy = np.zeros((cap, max(1, num_tests), m))
+
+    def fill(self, h):
+        h.cap = self.cap; h.num_tests = self.num_tests
+        h.train = C.cast(self.train, C.c_void_p)
+        h.train_accuracy = self.train_accuracy.ctypes.data
+        h.epoch = self.epoch.ctypes.data
+        h.wall_seconds = self.wall.ctypes.data
+        h.test = C.cast(self.test, C.c_void_p)
+        h.test_accuracy = self.test_accuracy.ctypes.data
+
+    def to_dict(self, num_evals):
+        n = min(num_evals, self.cap)
+        out = dict(
+            train=[{f: getattr(self.train[i], f) for f in RECORD_FIELDS} for i in range(n)],
+            train_accuracy=self.train_accuracy[:n].copy(), epoch=self.epoch[:n].copy(),
+            wall_seconds=self.wall[:n].copy(), tests=[])
+        for t in range(self.num_tests):
+            recs = [self.test[i * self.num_tests + t] for i in range(n)]
+            out["tests"].append(dict(primal_loss=np.array([r.primal_loss for r in recs]),
+                                     rank_loss=np.array([r.rank_loss for r in recs]),
+                                     accuracy=self.test_accuracy[:n, t].copy()))
+        return out
+
+
 FIT_STATUS = ("none", "solving", "solved", "no_progress", "max_epoch", "max_cpu_time",
               "max_wall_time", "failed")
 
@@ -335,7 +398,7 @@ def epoch_permutations(n, num_epochs):
 def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
          precision="double", epsilon=1e-3, max_epoch=1000, eval_epoch=10, eval_on_start=False,
          permutations=None, offsets=None, recompute_primal=False, W0=None,
-         max_cpu_time=0.0, max_wall_time=0.0):
+         max_cpu_time=0.0, max_wall_time=0.0, tests=None):
     """SDCA fit, in place on ``A`` (n x m) and ``W`` (m x d): torch CUDA tensors use the
     device entry point, numpy arrays the host-buffer one (copies inside).
 
@@ -356,6 +419,35 @@ def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
         if perm.size < max_epoch * X.shape[0]:
             raise SdcabError(-1, "fit_: permutations must hold max_epoch * n indices")
     perm_ptr = perm.ctypes.data_as(C.c_void_p) if perm is not None else None
+    if tests is not None:
+        # held-out sets as (X, labels[, offsets]) tuples of the same kind as the training data:
+        # evaluated after every evaluation of the training set
+        m = prob.m
+        bufs = _HistoryBuffers(cap, m, len(tests))
+        tprobs = (Problem * max(1, len(tests)))()
+        keep = []
+        for i, t in enumerate(tests):
+            tp = make_problem(t[0], t[1], A, W, None, t[2] if len(t) > 2 else None, kernel, False)
+            keep.append(tp)
+            tprobs[i] = tp
+        hist = FitHistory()
+        bufs.fill(hist)
+        hist.tests = C.cast(tprobs, C.c_void_p)
+        dev = _is_torch(X)
+        name = "sdcab_fit_history_%s%s" % (_suffix(str(X.dtype) if dev else X.dtype.name), "_dev" if dev else "")
+        args = [C.byref(obj), C.byref(prob), C.byref(crit), perm_ptr, C.byref(hist), C.byref(res)]
+        if dev:
+            args.append(_torch_stream())
+        _check(getattr(lib(), name)(*args), name)
+        out = dict(status=FIT_STATUS[res.status], status_code=res.status, epoch=res.epoch,
+                   num_evals=res.num_evals, solve_seconds=res.solve_seconds,
+                   eval_seconds=res.eval_seconds, cpu_seconds=res.cpu_seconds,
+                   wall_seconds=res.wall_seconds)
+        h = bufs.to_dict(res.num_evals)
+        out["history"] = h["train"]
+        out.update(train_accuracy=h["train_accuracy"], eval_epoch=h["epoch"], eval_wall_seconds=h["wall_seconds"],
+                   tests=h["tests"])
+        return out
     if _is_torch(X):
         fn = getattr(lib(), "sdcab_fit_%s_dev" % _suffix(str(X.dtype)))
         _check(fn(C.byref(obj), C.byref(prob), C.byref(crit), perm_ptr, evals, C.c_int64(cap),
@@ -365,6 +457,65 @@ def fit_(objective, X, labels, A, W=None, kernel=False, c=1.0, gamma=0.0, k=1,
         _check(fn(C.byref(obj), C.byref(prob), C.byref(crit), perm_ptr, evals, C.c_int64(cap),
                   C.byref(res)), "sdcab_fit")
     return fit_result_to_dict(res, evals)
+
+
+def train(data, labels, objective=None, c=1.0, gamma=1.0, k=1, is_dual=False, precision="double",
+          epsilon=1e-3, max_epoch=1000, eval_epoch=10, eval_on_start=False, max_cpu_time=0.0,
+          max_wall_time=0.0, A=None, W=None, W0=None, offsets=None, num_classes=0):
+    """``matsdca_fit(data, labels, opts)`` on numpy arrays (src/matlab/mex_solve.cpp:473-620 of
+    the reference): ``data`` is one (n, d) feature matrix -- or (n, n_train) Gram columns with
+    ``is_dual`` -- or a list of them, the first for training, the others evaluated only;
+    ``labels`` (and ``offsets`` for multilabel objectives) likewise.  Labels may be 0-based or
+    1-based.  ``A`` / ``W`` given: warm start.  Returns the model as a dict."""
+    sets = data if isinstance(data, (list, tuple)) else [data]
+    labs = labels if isinstance(labels, (list, tuple)) else [labels]
+    offs = offsets if isinstance(offsets, (list, tuple)) else [offsets] * len(sets)
+    dtype = sets[0].dtype
+    n = sets[0].shape[0]
+    d = sets[0].shape[1]
+    ds = (Dataset * len(sets))()
+    keep = []
+    for i, (x, l, o) in enumerate(zip(sets, labs, offs)):
+        x = np.ascontiguousarray(x, dtype=dtype); l = np.ascontiguousarray(l, dtype=np.int64)
+        keep += [x, l]
+        ds[i].n = x.shape[0]; ds[i].x = x.ctypes.data; ds[i].labels = l.ctypes.data
+        if o is not None:
+            o = np.ascontiguousarray(o, dtype=np.int64); keep.append(o)
+            ds[i].offsets = o.ctypes.data
+    opts = TrainOptions()
+    lib().sdcab_train_options_default(C.byref(opts))
+    if objective is not None:
+        opts.objective = objective.encode()
+    opts.c = c; opts.gamma = gamma; opts.k = k; opts.is_dual = 1 if is_dual else 0
+    opts.precision = {"double": 0, "single": 1, "float": 1}[precision]
+    opts.criteria = FitCriteria(epsilon, max_epoch, eval_epoch, 1 if eval_on_start else 0, 0,
+                                max_cpu_time, max_wall_time)
+    opts.num_dimensions = d; opts.num_classes = num_classes
+    if W0 is not None:
+        W0 = np.ascontiguousarray(W0, dtype=dtype); opts.W0 = W0.ctypes.data
+    l0 = np.asarray(labs[0])
+    m = num_classes or int(l0.max() - min(1, l0.min()) + 1)
+    opts.warm_start = 1 if A is not None else 0
+    A = np.zeros((n, m), dtype=dtype) if A is None else np.ascontiguousarray(A, dtype=dtype)
+    if not is_dual:
+        W = np.zeros((m, d), dtype=dtype) if W is None else np.ascontiguousarray(W, dtype=dtype)
+    model = Model()
+    model.A = A.ctypes.data
+    model.W = W.ctypes.data if W is not None else None
+    cap = int(max_epoch) + 4
+    bufs = _HistoryBuffers(cap, m, len(sets) - 1)
+    bufs.fill(model.history)
+    fn = getattr(lib(), "sdcab_train_%s" % _suffix(dtype.name))
+    _check(fn(ds, C.c_int64(len(sets)), C.byref(opts), C.byref(model)), "sdcab_train")
+    h = bufs.to_dict(model.num_evals)
+    return dict(A=A, W=W, num_dimensions=model.num_dimensions, num_examples=model.num_examples,
+                num_classes=model.num_classes, is_dual=bool(model.is_dual),
+                objective=model.objective.decode(), objective_id=model.objective_id, c=model.c,
+                k=model.k, gamma=model.gamma, status=FIT_STATUS[model.status], epoch=model.epoch,
+                cpu_time=model.cpu_time, wall_time=model.wall_time, relative_gap=model.relative_gap,
+                labels_one_based=bool(model.labels_one_based), num_evals=model.num_evals,
+                train=h["train"], train_accuracy=h["train_accuracy"], eval_epoch=h["epoch"],
+                tests=h["tests"])
 
 
 def test_set(name, value):

@@ -893,7 +893,8 @@ bool is_permutation(const int64_t* p, long long n, std::vector<unsigned char>& s
 template <typename Data, typename R>
 int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_fit_criteria* crit,
             const int64_t* permutations, sdcab_eval_record* evals, int64_t evals_cap,
-            sdcab_fit_result* result, cudaStream_t user_stream) {
+            sdcab_fit_result* result, cudaStream_t user_stream,
+            const sdcab_fit_history* hist = nullptr) {
   const long long n = train->n, m = train->m;
   DeviceInfo info;
   int rc = get_device_info(&info);
@@ -924,6 +925,16 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
   rc = buf.alloc(&sums_dev, static_cast<size_t>(SDCAB_EVAL_SUMS(m)));
   if (rc) return rc;
 
+  // the reference's stopwatches run while it solves and evaluates (solver.h:81-131):
+  // processor time by std::clock, wall time by a steady clock
+  const std::clock_t cpu_begin = std::clock();
+  const auto wall_begin = std::chrono::steady_clock::now();
+  auto cpu_now = [&]() { return static_cast<double>(std::clock() - cpu_begin) / CLOCKS_PER_SEC; };
+  auto wall_now = [&]() {
+    return std::chrono::duration<double>(std::chrono::steady_clock::now() - wall_begin).count();
+  };
+  int64_t epoch_now = 0;
+
   sdcab_problem ep = *train;
   ep.is_train = 1; ep.a_row_offset = 0; ep.include_primal_regularizer = 1;
   std::vector<double> sums(static_cast<size_t>(SDCAB_EVAL_SUMS(m)));
@@ -950,22 +961,47 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
     SDCAB_CUDA_TRY(cudaEventElapsedTime(&ms, buf.ev[2], buf.ev[3]));
     eval_ms += ms;
     sdcab_eval_record rec;
-    erc = eval_finish(obj, m, sums.data(), &rec, nullptr);
+    const int64_t slot = static_cast<int64_t>(history.size());
+    const bool keep = hist && slot < hist->cap;
+    erc = eval_finish(obj, m, sums.data(), &rec,
+                      (keep && hist->train_accuracy) ? hist->train_accuracy + slot * m : nullptr);
     if (erc) return erc;
     history.push_back(rec);
     if (evals && static_cast<int64_t>(history.size()) <= evals_cap) evals[history.size() - 1] = rec;
+    if (keep) {
+      if (hist->train) hist->train[slot] = rec;
+      if (hist->epoch) hist->epoch[slot] = epoch_now;
+      if (hist->wall_seconds) hist->wall_seconds[slot] = wall_now();
+    }
+    // every held-out set after the training set (solver.h:124-131): scores from the
+    // variables of the training problem, primal loss and accuracy / rank loss only
+    if (hist && hist->tests) {
+      for (int64_t ti = 0; ti < hist->num_tests; ++ti) {
+        sdcab_problem tp = hist->tests[ti];
+        tp.input_kind = train->input_kind; tp.is_train = 0; tp.d = train->d; tp.m = train->m;
+        tp.a = train->a; tp.w = train->w; tp.w0 = nullptr; tp.a_row_offset = 0;
+        tp.include_primal_regularizer = 0;
+        SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[2], s));
+        erc = eval_sums_call<Data>(obj, &tp, sums_dev, s);
+        if (erc) return erc;
+        SDCAB_CUDA_TRY(cudaEventRecord(buf.ev[3], s));
+        SDCAB_CUDA_TRY(cudaMemcpyAsync(sums.data(), sums_dev, sums.size() * sizeof(double),
+                                       cudaMemcpyDeviceToHost, s));
+        SDCAB_CUDA_TRY(cudaStreamSynchronize(s));
+        SDCAB_CUDA_TRY(cudaEventElapsedTime(&ms, buf.ev[2], buf.ev[3]));
+        eval_ms += ms;
+        sdcab_eval_record trec;
+        double* acc = (keep && hist->test_accuracy)
+                          ? hist->test_accuracy + (slot * hist->num_tests + ti) * m : nullptr;
+        erc = eval_finish(obj, m, sums.data(), &trec, acc);
+        if (erc) return erc;
+        if (keep && hist->test) hist->test[slot * hist->num_tests + ti] = trec;
+      }
+    }
     return SDCAB_OK;
   };
   const double eps_floor = std::max(
       static_cast<double>(num<Data>::eps()), static_cast<double>(num<R>::eps()));
-  // the reference's stopwatches run while it solves and evaluates (solver.h:81-131):
-  // processor time by std::clock, wall time by a steady clock
-  const std::clock_t cpu_begin = std::clock();
-  const auto wall_begin = std::chrono::steady_clock::now();
-  auto cpu_now = [&]() { return static_cast<double>(std::clock() - cpu_begin) / CLOCKS_PER_SEC; };
-  auto wall_now = [&]() {
-    return std::chrono::duration<double>(std::chrono::steady_clock::now() - wall_begin).count();
-  };
   auto check = [&](int status, int64_t epoch) {
     const sdcab_eval_record* last = history.empty() ? nullptr : &history.back();
     const sdcab_eval_record* before = history.size() > 1 ? &history[history.size() - 2] : nullptr;
@@ -1018,6 +1054,7 @@ int fit_dev(const sdcab_objective* obj, const sdcab_problem* train, const sdcab_
 
     // end_epoch (solver.h:103-117)
     ++epoch;
+    epoch_now = epoch;
     if (crit->eval_epoch > 0 && epoch % crit->eval_epoch == 0) {
       rc = evaluate(); if (rc) return rc;
       evaluated = true;
@@ -1065,23 +1102,42 @@ int check_fit_args(const sdcab_objective* obj, const sdcab_problem* t, const sdc
   return SDCAB_OK;
 }
 
+int check_history(const sdcab_fit_history* h) {
+  if (!h) return SDCAB_OK;
+  if (h->cap < 0 || h->num_tests < 0) return SDCAB_ERR_ARG_RANGE;
+  if (h->num_tests > 0 && !h->tests) return SDCAB_ERR_ARG;
+  for (int64_t t = 0; t < h->num_tests; ++t) {
+    if (h->tests[t].n <= 0) return SDCAB_ERR_NOT_EMPTY;
+    if (!h->tests[t].x || !h->tests[t].labels) return SDCAB_ERR_ARG;
+  }
+  return SDCAB_OK;
+}
+
 template <typename Data>
 int fit_entry(const sdcab_objective* obj, const sdcab_problem* t, const sdcab_fit_criteria* c,
               const int64_t* perm, sdcab_eval_record* evals, int64_t cap, sdcab_fit_result* res,
-              void* stream) {
+              void* stream, const sdcab_fit_history* hist = nullptr) {
   int rc = check_fit_args(obj, t, c);
   if (rc) return rc;
+  rc = check_history(hist);
+  if (rc) return rc;
+  if (hist && objective_is_multilabel(obj->id))
+    for (int64_t q = 0; q < hist->num_tests; ++q)
+      if (!hist->tests[q].offsets) return SDCAB_ERR_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (obj->precision == SDCAB_PRECISION_FLOAT)
-    return fit_dev<Data, float>(obj, t, c, perm, evals, cap, res, s);
-  return fit_dev<Data, double>(obj, t, c, perm, evals, cap, res, s);
+    return fit_dev<Data, float>(obj, t, c, perm, evals, cap, res, s, hist);
+  return fit_dev<Data, double>(obj, t, c, perm, evals, cap, res, s, hist);
 }
 
 // Host buffers: copy the problem to the device, fit, copy the variables back.
 template <typename Data>
 int fit_host(const sdcab_objective* obj, const sdcab_problem* hp, const sdcab_fit_criteria* c,
-             const int64_t* perm, sdcab_eval_record* evals, int64_t cap, sdcab_fit_result* res) {
+             const int64_t* perm, sdcab_eval_record* evals, int64_t cap, sdcab_fit_result* res,
+             const sdcab_fit_history* hist = nullptr) {
   int rc = check_fit_args(obj, hp, c);
+  if (rc) return rc;
+  rc = check_history(hist);
   if (rc) return rc;
   const long long n = hp->n, m = hp->m, d = hp->d;
   const bool kernel = (hp->input_kind == SDCAB_INPUT_KERNEL);
@@ -1119,11 +1175,130 @@ int fit_host(const sdcab_objective* obj, const sdcab_problem* hp, const sdcab_fi
   }
   sdcab_problem dp = *hp;
   dp.x = dX; dp.a = dA; dp.w = dW; dp.w0 = dW0; dp.labels = dLab; dp.offsets = dOff;
-  rc = fit_entry<Data>(obj, &dp, c, perm, evals, cap, res, nullptr);
+  // held-out sets: checked like the training labels, then copied to the device
+  std::vector<sdcab_problem> dtests;
+  sdcab_fit_history dh;
+  if (hist) {
+    dh = *hist;
+    for (int64_t q = 0; q < hist->num_tests; ++q) {
+      const sdcab_problem& tp = hist->tests[q];
+      if (ml && !tp.offsets) return SDCAB_ERR_ARG;
+      rc = validate_labels(tp.labels, tp.offsets, tp.n, m, ml);
+      if (rc) return rc;
+      const long long tl = ml ? tp.offsets[tp.n] : tp.n;
+      Data* tx = nullptr; int64_t *tlab = nullptr, *toff = nullptr;
+      rc = buf.alloc(&tx, static_cast<size_t>(tp.n) * d); if (rc) return rc;
+      rc = buf.alloc(&tlab, static_cast<size_t>(tl)); if (rc) return rc;
+      SDCAB_CUDA_TRY(cudaMemcpy(tx, tp.x, static_cast<size_t>(tp.n) * d * sizeof(Data), cudaMemcpyHostToDevice));
+      SDCAB_CUDA_TRY(cudaMemcpy(tlab, tp.labels, static_cast<size_t>(tl) * sizeof(int64_t), cudaMemcpyHostToDevice));
+      if (ml) {
+        rc = buf.alloc(&toff, static_cast<size_t>(tp.n + 1)); if (rc) return rc;
+        SDCAB_CUDA_TRY(cudaMemcpy(toff, tp.offsets, static_cast<size_t>(tp.n + 1) * sizeof(int64_t), cudaMemcpyHostToDevice));
+      }
+      sdcab_problem q_dev = tp;
+      q_dev.x = tx; q_dev.labels = tlab; q_dev.offsets = toff;
+      dtests.push_back(q_dev);
+    }
+    dh.tests = dtests.empty() ? nullptr : dtests.data();
+  }
+  rc = fit_entry<Data>(obj, &dp, c, perm, evals, cap, res, nullptr, hist ? &dh : nullptr);
   if (rc) return rc;
   SDCAB_CUDA_TRY(cudaMemcpy(const_cast<void*>(hp->a), dA, a_elems * sizeof(Data), cudaMemcpyDeviceToHost));
   if (!kernel)
     SDCAB_CUDA_TRY(cudaMemcpy(const_cast<void*>(hp->w), dW, w_elems * sizeof(Data), cudaMemcpyDeviceToHost));
+  return SDCAB_OK;
+}
+
+// matsdca_fit without Matlab: datasets + options in, model out.
+template <typename Data>
+int train_host(const sdcab_dataset* sets, int64_t num_sets, const sdcab_train_options* o, sdcab_model* model) {
+  if (!sets || num_sets < 1 || !o || !model) return SDCAB_ERR_ARG;
+  if (!model->A) return SDCAB_ERR_ARG;
+  const sdcab_dataset& trn = sets[0];
+  if (trn.n <= 0 || !trn.x || !trn.labels) return SDCAB_ERR_NOT_EMPTY;
+  sdcab_objective obj;
+  int rc = objective_from_name(o->objective ? o->objective : "msvm_smooth", o->c, o->gamma, o->k, &obj);
+  if (rc) return rc;
+  if (o->precision != SDCAB_PRECISION_DOUBLE && o->precision != SDCAB_PRECISION_FLOAT)
+    return SDCAB_ERR_PRECISION;
+  obj.precision = o->precision;
+  const bool ml = objective_is_multilabel(obj.id);
+  const bool kernel = o->is_dual != 0;
+  const int64_t n = trn.n;
+  const int64_t d = kernel ? n : o->num_dimensions;
+  if (d <= 0) return SDCAB_ERR_NUM_DIM;
+  if (!kernel && !model->W) return SDCAB_ERR_ARG;
+  if (ml && !trn.offsets) return SDCAB_ERR_ARG;
+  // labels: 0-based or 1-based, decided by the smallest training label
+  // (validate_labels, include/sdca/solver/data/output.h:169-182); every set is shifted alike
+  std::vector<std::vector<int64_t>> labels(static_cast<size_t>(num_sets));
+  int64_t shift = 0, max_label = 0;
+  for (int64_t q = 0; q < num_sets; ++q) {
+    const sdcab_dataset& ds = sets[q];
+    if (ds.n <= 0 || !ds.x || !ds.labels) return SDCAB_ERR_NOT_EMPTY;
+    if (ml && !ds.offsets) return SDCAB_ERR_ARG;
+    const int64_t count = ml ? ds.offsets[ds.n] : ds.n;
+    if (count <= 0) return SDCAB_ERR_LABELS_RANGE;
+    int64_t lo = ds.labels[0], hi = ds.labels[0];
+    for (int64_t i = 1; i < count; ++i) { lo = std::min(lo, ds.labels[i]); hi = std::max(hi, ds.labels[i]); }
+    if (q == 0) {
+      if (lo != 0 && lo != 1) return SDCAB_ERR_LABELS_RANGE;
+      shift = lo;
+    }
+    if (lo < shift) return SDCAB_ERR_LABELS_RANGE;
+    max_label = std::max(max_label, hi - shift);
+    labels[static_cast<size_t>(q)].assign(ds.labels, ds.labels + count);
+    for (int64_t& v : labels[static_cast<size_t>(q)]) v -= shift;
+  }
+  const int64_t m = o->num_classes > 0 ? o->num_classes : max_label + 1;
+  if (max_label >= m) return SDCAB_ERR_LABELS_RANGE;
+
+  Data* A = static_cast<Data*>(model->A);
+  Data* W = static_cast<Data*>(model->W);
+  if (!o->warm_start) {
+    std::fill(A, A + static_cast<size_t>(n) * m, Data(0));
+    if (!kernel) {
+      // W = W0 before the first step of a prox-regularised fit (mex_solve.cpp:566-571)
+      if (o->W0) std::memcpy(W, o->W0, static_cast<size_t>(d) * m * sizeof(Data));
+      else std::fill(W, W + static_cast<size_t>(d) * m, Data(0));
+    }
+  }
+  sdcab_problem p = sdcab_problem();
+  p.input_kind = kernel ? SDCAB_INPUT_KERNEL : SDCAB_INPUT_FEATURES;
+  p.is_train = 1; p.d = d; p.n = n; p.m = m;
+  p.x = trn.x; p.a = A; p.w = kernel ? nullptr : W; p.w0 = kernel ? nullptr : o->W0;
+  p.labels = labels[0].data(); p.offsets = trn.offsets; p.include_primal_regularizer = 1;
+  std::vector<sdcab_problem> tests;
+  for (int64_t q = 1; q < num_sets; ++q) {
+    sdcab_problem tp = sdcab_problem();
+    tp.input_kind = p.input_kind; tp.d = d; tp.n = sets[q].n; tp.m = m;
+    tp.x = sets[q].x; tp.labels = labels[static_cast<size_t>(q)].data(); tp.offsets = sets[q].offsets;
+    tests.push_back(tp);
+  }
+  sdcab_fit_history h = model->history;
+  h.num_tests = num_sets - 1;
+  h.tests = tests.empty() ? nullptr : tests.data();
+  sdcab_fit_result res = sdcab_fit_result();
+  rc = fit_host<Data>(&obj, &p, &o->criteria, nullptr, nullptr, 0, &res, &h);
+  if (rc) return rc;
+  // the model (mex_solve.cpp:153-376)
+  model->num_dimensions = d; model->num_examples = n; model->num_classes = m;
+  model->is_dual = kernel ? 1 : 0; model->objective_id = obj.id;
+  std::snprintf(model->objective, sizeof(model->objective), "%s", o->objective ? o->objective : "msvm_smooth");
+  model->c = obj.c; model->gamma = obj.gamma; model->k = obj.k;
+  model->criteria = o->criteria;
+  model->status = res.status;
+  model->data_precision = sizeof(Data) == 4 ? SDCAB_PRECISION_FLOAT : SDCAB_PRECISION_DOUBLE;
+  model->precision = obj.precision;
+  model->labels_one_based = static_cast<int32_t>(shift);
+  model->epoch = res.epoch;
+  model->cpu_time = res.cpu_seconds; model->wall_time = res.wall_seconds;
+  model->solve_time = res.solve_seconds; model->eval_time = res.eval_seconds;
+  model->num_evals = res.num_evals;
+  model->history.num_tests = num_sets - 1;
+  model->history.tests = nullptr;
+  const int64_t last = std::min(res.num_evals, h.cap) - 1;
+  model->relative_gap = (h.train && last >= 0) ? h.train[last].relative_gap : 0.0;
   return SDCAB_OK;
 }
 
@@ -1151,6 +1326,46 @@ int sdcab_fit_f64_dev(const sdcab_objective* obj, const sdcab_problem* train,
                       sdcab_eval_record* evals, int64_t evals_cap, sdcab_fit_result* result,
                       void* stream) {
   return sdcab::fit_entry<double>(obj, train, criteria, permutations, evals, evals_cap, result, stream);
+}
+
+int sdcab_fit_history_f32_dev(const sdcab_objective* obj, const sdcab_problem* train,
+                              const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                              const sdcab_fit_history* history, sdcab_fit_result* result, void* stream) {
+  return sdcab::fit_entry<float>(obj, train, criteria, permutations, nullptr, 0, result, stream, history);
+}
+int sdcab_fit_history_f64_dev(const sdcab_objective* obj, const sdcab_problem* train,
+                              const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                              const sdcab_fit_history* history, sdcab_fit_result* result, void* stream) {
+  return sdcab::fit_entry<double>(obj, train, criteria, permutations, nullptr, 0, result, stream, history);
+}
+int sdcab_fit_history_f32(const sdcab_objective* obj, const sdcab_problem* host_train,
+                          const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                          const sdcab_fit_history* history, sdcab_fit_result* result) {
+  return sdcab::fit_host<float>(obj, host_train, criteria, permutations, nullptr, 0, result, history);
+}
+int sdcab_fit_history_f64(const sdcab_objective* obj, const sdcab_problem* host_train,
+                          const sdcab_fit_criteria* criteria, const int64_t* permutations,
+                          const sdcab_fit_history* history, sdcab_fit_result* result) {
+  return sdcab::fit_host<double>(obj, host_train, criteria, permutations, nullptr, 0, result, history);
+}
+
+void sdcab_train_options_default(sdcab_train_options* o) {
+  if (!o) return;
+  std::memset(o, 0, sizeof(*o));
+  o->objective = nullptr; o->c = 1; o->gamma = 1; o->k = 1;
+  o->is_dual = 0; o->precision = SDCAB_PRECISION_DOUBLE;
+  // stopping_criteria of the reference (include/sdca/solver/solverdef.h:50-57)
+  o->criteria.epsilon = 1e-3; o->criteria.max_epoch = 1000; o->criteria.eval_epoch = 10;
+  o->criteria.eval_on_start = 0; o->criteria.recompute_primal = 0;
+  o->criteria.max_cpu_time = 0; o->criteria.max_wall_time = 0;
+}
+int sdcab_train_f32(const sdcab_dataset* datasets, int64_t num_datasets,
+                    const sdcab_train_options* options, sdcab_model* model) {
+  return sdcab::train_host<float>(datasets, num_datasets, options, model);
+}
+int sdcab_train_f64(const sdcab_dataset* datasets, int64_t num_datasets,
+                    const sdcab_train_options* options, sdcab_model* model) {
+  return sdcab::train_host<double>(datasets, num_datasets, options, model);
 }
 
 int sdcab_fit_f32(const sdcab_objective* obj, const sdcab_problem* host_train,

@@ -392,6 +392,50 @@ int run_eval(const eval_args& a, Objective<Data, Result> obj, double* out, doubl
   return 0;
 }
 
+// Held-out sets of the next fit (solver_context::add_test, context.h:87-91): set with
+// sdca_ref_set_tests before sdca_ref_fit, cleared by the fit.  out receives, per
+// evaluation e, {primal_loss, rank_loss} at out[2 * e ..]; acc the cumulative top-k
+// accuracies (m per evaluation, multiclass).
+struct ref_test_set {
+  int64_t n;
+  const void* X;
+  const int64_t* labels;
+  const int64_t* offsets;
+  double* out;
+  double* acc;
+};
+static std::vector<ref_test_set> g_tests;
+static int64_t g_tests_cap = 0;
+
+inline sdca::multiclass_output make_test_out(const ref_test_set& t, int64_t m, sdca::multiclass_output*) {
+  std::vector<sdca::size_type> v(t.labels, t.labels + t.n);
+  return sdca::multiclass_output(static_cast<sdca::size_type>(m), v);
+}
+inline sdca::multilabel_output make_test_out(const ref_test_set& t, int64_t m, sdca::multilabel_output*) {
+  std::vector<sdca::size_type> u(t.offsets, t.offsets + t.n + 1);
+  std::vector<sdca::size_type> v(t.labels, t.labels + t.offsets[t.n]);
+  return sdca::multilabel_output(static_cast<sdca::size_type>(m), v, u);
+}
+template <typename Data>
+sdca::feature_input<Data> make_test_in(const eval_args& a, const ref_test_set& t, sdca::feature_input<Data>*) {
+  return sdca::make_input_feature(static_cast<sdca::size_type>(a.d), static_cast<sdca::size_type>(t.n),
+                                  static_cast<const Data*>(t.X));
+}
+template <typename Data>
+sdca::kernel_input<Data> make_test_in(const eval_args& a, const ref_test_set& t, sdca::kernel_input<Data>*) {
+  return sdca::make_input_kernel(static_cast<sdca::size_type>(a.d), static_cast<sdca::size_type>(t.n),
+                                 static_cast<const Data*>(t.X));
+}
+template <typename Result>
+void store_test_eval(const sdca::eval_test<Result, sdca::multiclass_output>& e, double* out, double* acc, int64_t m) {
+  out[0] = static_cast<double>(e.primal_loss); out[1] = 0;
+  if (acc) for (int64_t j = 0; j < m && j < static_cast<int64_t>(e.accuracy.size()); ++j) acc[j] = static_cast<double>(e.accuracy[j]);
+}
+template <typename Result>
+void store_test_eval(const sdca::eval_test<Result, sdca::multilabel_output>& e, double* out, double*, int64_t) {
+  out[0] = static_cast<double>(e.primal_loss); out[1] = static_cast<double>(e.rank_loss);
+}
+
 // Fit: solver::solve with the given stopping criteria.  Returns the history of
 // evaluations (7 doubles per evaluation) and the final status / epoch.
 template <typename Data, typename Result, template <typename> class Input,
@@ -405,8 +449,17 @@ int run_fit(const eval_args& a, Objective<Data, Result> obj, double* hist,
   ctx.criteria.max_epoch = static_cast<sdca::size_type>(a.max_epoch);
   ctx.criteria.eval_epoch = static_cast<sdca::size_type>(a.eval_epoch);
   ctx.criteria.eval_on_start = a.eval_on_start != 0;
+  for (const ref_test_set& t : g_tests)
+    ctx.add_test(make_test_in<Data>(a, t, (Input<Data>*)nullptr), make_test_out(t, a.m, (Output*)nullptr));
   auto solver = sdca::make_solver(ctx);
   solver.solve();
+  for (std::size_t q = 0; q < g_tests.size(); ++q) {
+    const auto& evs = ctx.test[q].evals;
+    for (std::size_t e = 0; e < evs.size() && static_cast<int64_t>(e) < g_tests_cap; ++e)
+      store_test_eval<Result>(evs[e], g_tests[q].out + 2 * e,
+                              g_tests[q].acc ? g_tests[q].acc + a.m * static_cast<int64_t>(e) : nullptr, a.m);
+  }
+  g_tests.clear();
   int64_t ne = static_cast<int64_t>(ctx.train.evals.size());
   *num_evals = ne;
   for (int64_t i = 0; i < ne && i < hist_cap; ++i) {
@@ -529,6 +582,11 @@ int sdca_ref_eval(const eval_args* a, int dtype, int result, double* out, double
     return -4;
   }
   return -2;
+}
+
+void sdca_ref_set_tests(const ref_test_set* sets, int count, int64_t cap) {
+  g_tests.assign(sets, sets + count);
+  g_tests_cap = cap;
 }
 
 int sdca_ref_fit(const eval_args* a, int dtype, int result, double* hist,

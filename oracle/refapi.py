@@ -54,6 +54,11 @@ class EvalArgs(C.Structure):
                 ("eval_epoch", C.c_int64), ("eval_on_start", C.c_int)]
 
 
+class RefTestSet(C.Structure):
+    _fields_ = [("n", C.c_int64), ("X", C.c_void_p), ("labels", C.c_void_p), ("offsets", C.c_void_p),
+                ("out", C.c_void_p), ("acc", C.c_void_p)]
+
+
 def _dtype_code(dt):
     dt = np.dtype(dt)
     if dt == np.float32:
@@ -151,8 +156,22 @@ class _Backend:
         return rec
 
     def fit(self, objective, X, A, labels, epsilon=1e-3, max_epoch=1000, eval_epoch=10,
-            eval_on_start=False, result="double", **kw):
+            eval_on_start=False, result="double", tests=None, **kw):
+        """``tests``: held-out sets as (X, labels[, offsets]) tuples (reference back end only);
+        the result then has ``tests``: per set a dict of primal_loss, rank_loss (one entry per
+        evaluation) and accuracy (evaluations x m)."""
         a, m = self._eval_args(objective, X, A, labels, **kw)
+        test_out = []
+        if tests:
+            cap_t = max_epoch + 4
+            sets = (RefTestSet * len(tests))()
+            for i, t in enumerate(tests):
+                out = np.zeros((cap_t, 2)); acc = np.zeros((cap_t, m))
+                sets[i].n = t[0].shape[0]; sets[i].X = t[0].ctypes.data; sets[i].labels = t[1].ctypes.data
+                sets[i].offsets = t[2].ctypes.data if len(t) > 2 and t[2] is not None else None
+                sets[i].out = out.ctypes.data; sets[i].acc = acc.ctypes.data
+                test_out.append((out, acc))
+            self._fn("set_tests")(sets, len(tests), C.c_int64(cap_t))
         a.epsilon = epsilon; a.max_epoch = max_epoch; a.eval_epoch = eval_epoch
         a.eval_on_start = 1 if eval_on_start else 0
         cap = max_epoch + 4
@@ -164,8 +183,11 @@ class _Backend:
                              C.byref(st), _ptr(acc))
         if rc != 0:
             raise RuntimeError("%sfit -> %d" % (self.prefix, rc))
-        return dict(history=hist[:ne.value].copy(), epoch=ep.value, status=st.value,
-                    accuracy=acc)
+        res = dict(history=hist[:ne.value].copy(), epoch=ep.value, status=st.value, accuracy=acc)
+        if tests:
+            res["tests"] = [dict(primal_loss=o[:ne.value, 0].copy(), rank_loss=o[:ne.value, 1].copy(),
+                                 accuracy=ac[:ne.value].copy()) for o, ac in test_out]
+        return res
 
     def epoch_permutations(self, n, num_epochs):
         perm = np.zeros((num_epochs, n), dtype=np.int64)
