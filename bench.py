@@ -402,12 +402,19 @@ def gap_measure(args, rank, world, dist, torch, sd):
     W = sd.primal_from_dual(X, A)
     torch.cuda.synchronize()
     t_primal = time.perf_counter() - t_primal
-    if dist is not None:
-        dist.all_reduce(W)
     torch.cuda.synchronize()
     ws_bytes = sd.lib().sdcab_eval_workspace_bytes
     ws_bytes.restype = C.c_size_t
     workspace = torch.empty(ws_bytes(C.c_int64(n), C.c_int64(m), C.c_int64(4)), dtype=torch.uint8, device="cuda")
+    # the library's own communicator (NCCL behind the C ABI): rank 0 makes the id, the
+    # process group that torchrun set up only carries it to the other ranks
+    comm = None
+    if dist is not None:
+        ident = [b.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ident, src=0)
+        comm = b.Comm.create(world, rank, ident[0])
+        comm.allreduce_(W)                  # the d x m sum of the sharded rebuild W = X A'
+        torch.cuda.synchronize()
     reps = max(5, min(args.steps, 10))
     warm = max(3, min(args.warmup, 5))
     results = {}
@@ -417,9 +424,10 @@ def gap_measure(args, rank, world, dist, torch, sd):
         sums = torch.zeros(8 + m, dtype=torch.float64, device="cuda")
 
         def one_eval():
-            sd.eval_sums_(obj, prob, sums, "f32", workspace, workspace.numel())
-            if dist is not None:
-                dist.all_reduce(sums)
+            if comm is not None:
+                comm.eval_sums_(obj, prob, sums, "f32", workspace, workspace.numel())
+            else:
+                sd.eval_sums_(obj, prob, sums, "f32", workspace, workspace.numel())
 
         for _ in range(warm):
             one_eval()
@@ -464,9 +472,9 @@ def gap_measure(args, rank, world, dist, torch, sd):
             raise sd.SdcabError(rc, "sdcab_eval_f32")
         terms = np.array([rec.primal_loss, rec.dual_loss, rec.primal_regularizer, rec.dual_regularizer,
                           acc[0] * n], dtype=np.float64)
-        if dist is not None:
+        if comm is not None:
             t = torch.from_numpy(terms).cuda()
-            dist.all_reduce(t)
+            comm.allreduce_(t)
             terms = t.cpu().numpy()
         return terms
 
@@ -541,12 +549,16 @@ def gap_measure(args, rank, world, dist, torch, sd):
                        "%d examples in total, float32" % (d, m, n * world),
            "examples_per_gpu": n, "n_gpus": world,
            "scaling": "strong" if args.gap_examples <= 0 else "weak",
-           "collective": "one all_reduce(sum) of %d doubles per evaluation, inside the timed region" % (8 + m),
+           "collective": "one ncclAllReduce(sum) of %d doubles per evaluation through the library's "
+                         "communicator (sdcab_eval_sums_sharded_f32_dev), inside the timed region" % (8 + m),
            "timing": "CUDA events around each evaluation, median of %d, max over ranks" % reps,
            "seconds_per_eval": first["seconds_per_eval"],
            "results": results, "roofline": gap_roofline(first["tflops"] / world),
            "e2e": e2e, "cpu_baseline": cpu, "parity_on_sample": parity,
            "setup_primal_from_dual": {"seconds": t_primal, "tflops": 2.0 * d * m * n / t_primal / 1e12}}
+    if comm is not None:
+        torch.cuda.synchronize()
+        comm.destroy()
     del X, A, W, workspace
     torch.cuda.empty_cache()
     return out

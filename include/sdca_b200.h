@@ -48,7 +48,8 @@ typedef enum sdcab_status {
   SDCAB_ERR_CUDA = -20,
   SDCAB_ERR_NO_DEVICE = -21,
   SDCAB_ERR_TOO_LARGE = -22,
-  SDCAB_ERR_TIMEOUT = -23        /* a bounded wait inside a kernel ran out */
+  SDCAB_ERR_TIMEOUT = -23,       /* a bounded wait inside a kernel ran out */
+  SDCAB_ERR_NCCL = -24           /* NCCL missing or a collective failed: sdcab_comm_last_error() */
 } sdcab_status;
 
 const char* sdcab_status_string(int status);
@@ -263,6 +264,43 @@ int sdcab_eval_sums_fixed_scratch_f64_dev(const sdcab_objective* obj, const sdca
                                           double* sums_dev, void* stream);
 size_t sdcab_eval_fixed_scratch_bytes(void);
 const char* sdcab_eval_fixed_scratch_error(void);
+
+/*
+ * The ranks of a sharded evaluation.  Examples are independent
+ * (include/sdca/solver/eval.h:36-47), so each rank evaluates its shard into its own
+ * sums vector and ONE all-reduce (sum, 8 + m doubles) gives every rank the sums of
+ * the whole set; sdcab_eval_finish then runs on every rank.  The reference is a
+ * single-process library and has no counterpart.  NCCL is bound at run time; a
+ * NULL communicator stands for a single shard everywhere below.
+ *   one process per GPU:  rank 0 calls sdcab_comm_unique_id and hands the
+ *       SDCAB_COMM_ID_BYTES bytes to the other ranks by any means (a file, MPI, a
+ *       socket); every rank then calls sdcab_comm_create with its device current;
+ *   one process, several GPUs:  sdcab_comm_create_local fills `out[0 .. ngpus)`
+ *       (devices = NULL means 0 .. ngpus - 1); collectives of the local ranks
+ *       must then be issued from separate host threads or inside
+ *       ncclGroupStart / ncclGroupEnd.
+ * The primal regulariser is counted on the rank whose problem has
+ * include_primal_regularizer set.
+ */
+typedef struct sdcab_comm sdcab_comm;
+#define SDCAB_COMM_ID_BYTES 128
+int sdcab_comm_unique_id(void* id_out);
+int sdcab_comm_create(sdcab_comm** out, int nranks, int rank, const void* id);
+int sdcab_comm_create_local(sdcab_comm** out, int ngpus, const int* devices);
+int sdcab_comm_destroy(sdcab_comm* comm);
+int sdcab_comm_rank(const sdcab_comm* comm);
+int sdcab_comm_size(const sdcab_comm* comm);
+const char* sdcab_comm_last_error(void);
+/* In-place sums over the ranks on `stream` (asynchronous, like the kernels). */
+int sdcab_comm_allreduce_f64(sdcab_comm* comm, double* buf_dev, int64_t count, void* stream);
+int sdcab_comm_allreduce_f32(sdcab_comm* comm, float* buf_dev, int64_t count, void* stream);
+/* sdcab_eval_sums_*_dev on this rank's shard followed by the all-reduce of the sums. */
+int sdcab_eval_sums_sharded_f32_dev(const sdcab_objective* obj, const sdcab_problem* p,
+                                    double* sums_dev, void* workspace_dev, size_t workspace_bytes,
+                                    sdcab_comm* comm, void* stream);
+int sdcab_eval_sums_sharded_f64_dev(const sdcab_objective* obj, const sdcab_problem* p,
+                                    double* sums_dev, void* workspace_dev, size_t workspace_bytes,
+                                    sdcab_comm* comm, void* stream);
 
 /* Turns summed-up sums (host memory) into the record: applies the objective's
  * coefficient, forms primal / dual, normalises the accuracy histogram into

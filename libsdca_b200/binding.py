@@ -518,6 +518,55 @@ def train(data, labels, objective=None, c=1.0, gamma=1.0, k=1, is_dual=False, pr
                 tests=h["tests"])
 
 
+class Comm:
+    """The ranks of a sharded evaluation (``sdcab_comm``): NCCL behind the C ABI."""
+
+    ID_BYTES = 128
+
+    def __init__(self, handle):
+        self.handle = handle
+
+    @staticmethod
+    def unique_id():
+        buf = C.create_string_buffer(Comm.ID_BYTES)
+        _check_comm(lib().sdcab_comm_unique_id(buf), "sdcab_comm_unique_id")
+        return buf.raw
+
+    @staticmethod
+    def create(nranks, rank, unique_id):
+        h = C.c_void_p()
+        _check_comm(lib().sdcab_comm_create(C.byref(h), int(nranks), int(rank), unique_id), "sdcab_comm_create")
+        return Comm(h)
+
+    def allreduce_(self, t):
+        """In-place sum of a float32 / float64 torch CUDA tensor over the ranks."""
+        fn = getattr(lib(), "sdcab_comm_allreduce_%s" % _suffix(str(t.dtype)))
+        _check_comm(fn(self.handle, C.c_void_p(t.data_ptr()), C.c_int64(t.numel()), _torch_stream()),
+                    "sdcab_comm_allreduce")
+        return t
+
+    def eval_sums_(self, objective, problem, sums, dtype_suffix, workspace=None, workspace_bytes=0):
+        """This rank's shard evaluated and the sums added over the ranks."""
+        fn = getattr(lib(), "sdcab_eval_sums_sharded_%s_dev" % dtype_suffix)
+        _check_comm(fn(C.byref(objective), C.byref(problem), C.c_void_p(sums.data_ptr()),
+                       C.c_void_p(workspace.data_ptr()) if workspace is not None else None,
+                       C.c_size_t(workspace_bytes), self.handle, _torch_stream()),
+                    "sdcab_eval_sums_sharded_dev")
+        return sums
+
+    def destroy(self):
+        if self.handle:
+            lib().sdcab_comm_destroy(self.handle)
+            self.handle = None
+
+
+def _check_comm(rc, where):
+    if rc == -24:
+        lib().sdcab_comm_last_error.restype = C.c_char_p
+        raise SdcabError(rc, where + ": " + lib().sdcab_comm_last_error().decode())
+    _check(rc, where)
+
+
 def test_set(name, value):
     """Switches for the library's own tests (``sdcab_test_set``)."""
     _check(lib().sdcab_test_set(name.encode(), C.c_int64(int(value))), "sdcab_test_set(%s)" % name)

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libsdca_b200.so")
 OBJ_DIR = os.path.join(HERE, "build")
-SOURCES = ["api.cu", "prox.cu", "eval.cu", "fit.cu", "primal.cu"]
+SOURCES = ["api.cu", "prox.cu", "eval.cu", "fit.cu", "primal.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr"]
 
@@ -55,7 +55,7 @@ def build(force=False, verbose=False):
     with open(os.path.join(OBJ_DIR, "ptxas.log"), "w") as f:
         for k, v in logs.items():
             f.write("==== %s\n%s\n" % (k, v))
-    cmd = [nvcc, "-shared", "-o", OUT] + objs + ["-lcudart"]
+    cmd = [nvcc, "-shared", "-o", OUT] + objs + ["-lcudart", "-ldl"]
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout)

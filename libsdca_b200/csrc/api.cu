@@ -136,6 +136,7 @@ const char* sdcab_status_string(int status) {
     case SDCAB_ERR_NO_DEVICE: return "no_cuda_device";
     case SDCAB_ERR_TOO_LARGE: return "too_large";
     case SDCAB_ERR_TIMEOUT: return "device_wait_timeout";
+    case SDCAB_ERR_NCCL: return "nccl_error";
   }
   return "unknown";
 }

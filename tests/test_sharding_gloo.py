@@ -2,7 +2,7 @@
 each rank produces the sums of its shard, one all-reduce adds them, and
 eval_finish on the reduced vector equals the unsharded record.  The per-shard
 sums come from the host-lane build of the loss code (no GPU here); the recipe
-is the one bench.py and INTEGRATION.md describe for NCCL."""
+is the one the benchmark uses with NCCL."""
 import os
 import socket
 import sys
