@@ -70,7 +70,12 @@ typedef struct sdcab_prox_opts {
   double lo, hi, rhs, rho, alpha;
   int64_t k, p;
   int32_t precision;
-  int32_t reserved;
+  int32_t accurate_math;   /* 1: recompute t exactly from the final sets after variable
+                            * fixing, as the reference does when it is compiled with
+                            * SDCA_ACCURATE_MATH (include/sdca/prox/knapsack_eq.h:87-106);
+                            * concerns knapsack_eq / _le / _le_biased and topk_simplex
+                            * (+ biased), which end in that routine; 0 = the reference's
+                            * default build */
 } sdcab_prox_opts;
 
 void sdcab_prox_opts_default(sdcab_prox_opts* opts);

@@ -37,7 +37,7 @@ class SdcabError(RuntimeError):
 class ProxOpts(C.Structure):
     _fields_ = [("lo", C.c_double), ("hi", C.c_double), ("rhs", C.c_double),
                 ("rho", C.c_double), ("alpha", C.c_double), ("k", C.c_int64),
-                ("p", C.c_int64), ("precision", C.c_int32), ("reserved", C.c_int32)]
+                ("p", C.c_int64), ("precision", C.c_int32), ("accurate_math", C.c_int32)]
 
 
 class Thresholds(C.Structure):
@@ -80,12 +80,13 @@ def _check(rc, where):
         raise SdcabError(rc, where)
 
 
-def make_opts(lo=0.0, hi=1.0, rhs=1.0, rho=1.0, alpha=1.0, k=1, p=1, precision="double"):
+def make_opts(lo=0.0, hi=1.0, rhs=1.0, rho=1.0, alpha=1.0, k=1, p=1, precision="double",
+              accurate_math=False):
     prec = {"double": 0, "single": 1, "float": 1}.get(precision)
     if prec is None:
         # "long double" exists in the reference's front end but has no device type
         raise SdcabError(-8, "precision=%r" % (precision,))
-    return ProxOpts(lo, hi, rhs, rho, alpha, int(k), int(p), prec, 0)
+    return ProxOpts(lo, hi, rhs, rho, alpha, int(k), int(p), prec, 1 if accurate_math else 0)
 
 
 def _is_torch(x):

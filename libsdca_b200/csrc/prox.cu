@@ -178,7 +178,9 @@ int dispatch_prox(int prox, const Data* a, Data* out, int m, long long n, const 
                   sdcab_thresholds* thr_out, int apply, cudaStream_t stream) {
   if (prox == kTwoSimplexSort)
     return launch_two_simplex_sort<Data, R>(a, out, m, n, q, thr_out, apply, stream);
-  if (apply && !thr_out) {
+  // the register-row kernels solve on compacted candidates and have no exact
+  // recomputation step: the accurate-math variant takes the general kernel
+  if (apply && !thr_out && !q.accurate) {
     int rc = try_entropic_rows<R>(prox, a, out, m, n, q, stream);
     if (rc != kNoFastPath) return rc;
     rc = launch_fast_rows<Data, R>(prox, a, out, m, n, q, stream);
@@ -229,6 +231,7 @@ int prox_dev(const char* name, const Data* a, Data* out, long long m, long long 
   ProxParams q;
   q.lo = o->lo; q.hi = o->hi; q.rhs = o->rhs; q.rho = o->rho; q.alpha = o->alpha;
   q.k = static_cast<int>(o->k); q.p = static_cast<int>(o->p);
+  q.accurate = o->accurate_math ? 1 : 0;
   if (o->precision == SDCAB_PRECISION_FLOAT)
     return dispatch_prox<Data, float>(prox, a, out, static_cast<int>(m), n, q, thr_out, apply, stream);
   return dispatch_prox<Data, double>(prox, a, out, static_cast<int>(m), n, q, thr_out, apply, stream);
@@ -301,7 +304,7 @@ extern "C" {
 void sdcab_prox_opts_default(sdcab_prox_opts* o) {
   if (!o) return;
   o->lo = 0; o->hi = 1; o->rhs = 1; o->rho = 1; o->alpha = 1;
-  o->k = 1; o->p = 1; o->precision = SDCAB_PRECISION_DOUBLE; o->reserved = 0;
+  o->k = 1; o->p = 1; o->precision = SDCAB_PRECISION_DOUBLE; o->accurate_math = 0;
 }
 
 int sdcab_prox_f32_dev(const char* prox, float* a, int64_t m, int64_t n,

@@ -31,6 +31,7 @@ enum MapId { kMapIdentity = 0, kMapExp, kMapLambert, kMapScaledLambert };
 struct ProxParams {
   double lo, hi, rhs, rho, alpha;
   int k, p;
+  int accurate;   // exact recomputation of t after variable fixing (SDCA_ACCURATE_MATH)
 };
 
 SDCAB_HD MapId prox_map(int prox) {
@@ -47,11 +48,11 @@ SDCAB_D Thr<R> compute_thresholds(int prox, const Row& row, const ProxParams& q)
   const R lo = static_cast<R>(q.lo), hi = static_cast<R>(q.hi);
   const R rhs = static_cast<R>(q.rhs), rho = static_cast<R>(q.rho);
   switch (prox) {
-    case kKnapsackEq: return thr_knapsack_eq<R>(row, lo, hi, rhs);
-    case kKnapsackLe: return thr_knapsack_le<R>(row, lo, hi, rhs);
-    case kKnapsackLeBiased: return thr_knapsack_le_biased<R>(row, lo, hi, rhs, rho);
-    case kTopkSimplex: return thr_topk_simplex<R>(row, q.k, rhs, R(0));
-    case kTopkSimplexBiased: return thr_topk_simplex<R>(row, q.k, rhs, rho);
+    case kKnapsackEq: return thr_knapsack_eq<R>(row, lo, hi, rhs, q.accurate != 0);
+    case kKnapsackLe: return thr_knapsack_le<R>(row, lo, hi, rhs, q.accurate != 0);
+    case kKnapsackLeBiased: return thr_knapsack_le_biased<R>(row, lo, hi, rhs, rho, q.accurate != 0);
+    case kTopkSimplex: return thr_topk_simplex<R>(row, q.k, rhs, R(0), q.accurate != 0);
+    case kTopkSimplexBiased: return thr_topk_simplex<R>(row, q.k, rhs, rho, q.accurate != 0);
     case kTopkCone: return thr_topk_cone<R>(row, q.k, R(0));
     case kTopkConeBiased: return thr_topk_cone<R>(row, q.k, rho);
     case kEntropy: return thr_entropy<R>(row, hi, rhs);

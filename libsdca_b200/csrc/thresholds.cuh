@@ -137,8 +137,39 @@ SDCAB_D bool take_next(const Row& row, Taken<R>& tk, R& val) {
 // Same iteration as include/sdca/prox/knapsack_eq.h:25-109 (Kiwiel's variable
 // fixing): the free entries always form a value interval (lb, ub], so fixing a
 // tail moves one end of the interval instead of partitioning the data.
+// The exact recomputation of t that the reference makes when it is compiled with
+// SDCA_ACCURATE_MATH (include/sdca/prox/knapsack_eq.h:87-106): from the final sets,
+// t = (sum of the middle entries - rhs + hi |U| + lo |L|) / |M|, kept between
+// max(L) - lo and min(U) - hi; their midpoint when M is empty.
 template <typename R, typename Row>
-SDCAB_D Thr<R> thr_knapsack_eq(const Row& row, R lo, R hi, R rhs) {
+SDCAB_D Thr<R> knapsack_recompute_t(const Row& row, Thr<R> thr, R rhs) {
+  const int m = row.size();
+  R sum_M = 0, max_L = -num<R>::inf(), min_U = num<R>::inf();
+  int nU = 0, nM = 0;
+  row.for_each([&](typename Row::data_type xd, int) {
+    const R x = static_cast<R>(xd);
+    if (x > thr.cutU) { ++nU; min_U = min_(min_U, x); }
+    else if (x > thr.cutM) { ++nM; sum_M += x; }
+    else max_L = max_(max_L, x);
+  });
+  sum_M = warp_sum(sum_M); max_L = warp_max(max_L); min_U = -warp_max(-min_U);
+  nU = warp_sum(nU); nM = warp_sum(nM);
+  const int nL = m - nU - nM;
+  const R t_lo = (nL > 0) ? max_L - thr.lo : -num<R>::max();
+  const R t_hi = (nU > 0) ? min_U - thr.hi : num<R>::max();
+  R t;
+  if (nM > 0) {
+    t = (sum_M - rhs + thr.hi * static_cast<R>(nU) + thr.lo * static_cast<R>(nL)) / static_cast<R>(nM);
+    t = max_(t_lo, min_(t, t_hi));
+  } else {
+    t = R(0.5) * (t_lo + t_hi);
+  }
+  thr.t = t;
+  return thr;
+}
+
+template <typename R, typename Row>
+SDCAB_D Thr<R> thr_knapsack_eq(const Row& row, R lo, R hi, R rhs, bool accurate = false) {
   const int m = row.size();
   const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
   const R total = row_sum<R>(row);
@@ -173,20 +204,23 @@ SDCAB_D Thr<R> thr_knapsack_eq(const Row& row, R lo, R hi, R rhs) {
       tt = static_cast<R>(mfree) * t - sum_lo + s_lo;
       mfree -= n_lo;
     } else {
-      return make_thr(t, lo, hi, nU_fixed + n_hi, mfree - n_hi - n_lo,
-                      min_(ub, thi), max_(lb, tlo));
+      const Thr<R> thr = make_thr(t, lo, hi, nU_fixed + n_hi, mfree - n_hi - n_lo,
+                                  min_(ub, thi), max_(lb, tlo));
+      return accurate ? knapsack_recompute_t<R>(row, thr, rhs) : thr;
     }
     if (mfree > 0) {
       t = tt / static_cast<R>(mfree);
     } else {
-      return make_thr(t, lo, hi, nU_fixed, 0, ub, ub);
+      // everything is fixed: the entries above ub sit at hi, the others at lo
+      const Thr<R> thr = make_thr(t, lo, hi, nU_fixed, 0, ub, ub);
+      return accurate ? knapsack_recompute_t<R>(row, thr, rhs) : thr;
     }
   }
 }
 
 // <1,x> <= rhs                   (include/sdca/prox/knapsack_le.h:17-44)
 template <typename R, typename Row>
-SDCAB_D Thr<R> thr_knapsack_le(const Row& row, R lo, R hi, R rhs) {
+SDCAB_D Thr<R> thr_knapsack_le(const Row& row, R lo, R hi, R rhs, bool accurate = false) {
   const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
   int n_hi = 0, n_mid = 0;
   R sum_mid = 0;
@@ -198,7 +232,7 @@ SDCAB_D Thr<R> thr_knapsack_le(const Row& row, R lo, R hi, R rhs) {
   n_hi = warp_sum(n_hi); n_mid = warp_sum(n_mid); sum_mid = warp_sum(sum_mid);
   const int n_lo = row.size() - n_hi - n_mid;
   const R s = sum_mid + hi * static_cast<R>(n_hi) + lo * static_cast<R>(n_lo);
-  if (s > rhs + eps) return thr_knapsack_eq<R>(row, lo, hi, rhs);
+  if (s > rhs + eps) return thr_knapsack_eq<R>(row, lo, hi, rhs, accurate);
   return make_thr(R(0), lo, hi, n_hi, n_mid, hi, lo);
 }
 
@@ -245,10 +279,10 @@ SDCAB_D Thr<R> thr_knapsack_le_biased_root(const Row& row, R lo, R hi, R rhs, R 
 // (include/sdca/prox/knapsack_le_biased.h:106-129; the sorted double loop of
 //  :10-86 is replaced by the one-dimensional root search above)
 template <typename R, typename Row>
-SDCAB_D Thr<R> thr_knapsack_le_biased(const Row& row, R lo, R hi, R rhs, R rho) {
-  if (rho == 0) return thr_knapsack_le<R>(row, lo, hi, rhs);
+SDCAB_D Thr<R> thr_knapsack_le_biased(const Row& row, R lo, R hi, R rhs, R rho, bool accurate = false) {
+  if (rho == 0) return thr_knapsack_le<R>(row, lo, hi, rhs, accurate);
   const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
-  Thr<R> eq = thr_knapsack_eq<R>(row, lo, hi, rhs);
+  Thr<R> eq = thr_knapsack_eq<R>(row, lo, hi, rhs, accurate);
   if (eq.t >= rho * rhs - eps) return eq;
   return thr_knapsack_le_biased_root<R>(row, lo, hi, rhs, rho, eq.t);
 }
@@ -364,7 +398,7 @@ SDCAB_D Thr<R> thr_topk_cone(const Row& row, int k, R rho) {
 // min 0.5(<x,x> + rho<1,x>^2) - <a,x>,  <1,x> <= rhs,  0 <= x_i <= <1,x>/k
 // (include/sdca/prox/topk_simplex.h:9-68, topk_simplex_biased.h:9-71)
 template <typename R, typename Row>
-SDCAB_D Thr<R> thr_topk_simplex(const Row& row, int k, R rhs, R rho) {
+SDCAB_D Thr<R> thr_topk_simplex(const Row& row, int k, R rhs, R rho, bool accurate = false) {
   const R K = static_cast<R>(k), lo = 0;
   const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
   const R rho_k2 = rho * K * K;
@@ -372,10 +406,10 @@ SDCAB_D Thr<R> thr_topk_simplex(const Row& row, int k, R rhs, R rho) {
   const Projection proj = topk_special_cases<R>(row, k, K + rho_k2, thr);
   if (proj == kProjZero) return thr;
   if (proj == kProjConstant) {
-    if (K * thr.hi > rhs + eps) return thr_knapsack_eq<R>(row, lo, rhs / K, rhs);
+    if (K * thr.hi > rhs + eps) return thr_knapsack_eq<R>(row, lo, rhs / K, rhs, accurate);
     return thr;
   }
-  Thr<R> eq = thr_knapsack_eq<R>(row, lo, rhs / K, rhs);
+  Thr<R> eq = thr_knapsack_eq<R>(row, lo, rhs / K, rhs, accurate);
   bool lt;
   if (eq.nU == 0) {
     lt = eq.t < rho * rhs - eps;

@@ -6,8 +6,10 @@ Two libraries are produced:
   built; needs only gcc).
 * ``oracle/_ref/libsdca_ref.so`` -- ``ref_shim.cpp`` compiled against the
   reference's own, unmodified header tree.  Built only where that tree is
-  present (``SDCA_REFERENCE_DIR``, or the default of ``REF_DIR`` below); elsewhere the
-  prebuilt file that travelled with the repository is used as it is.
+  present (``SDCA_REFERENCE_DIR``, or a ``reference`` folder beside this repository);
+  elsewhere the prebuilt file that travelled with the repository is used as it is.
+  A second build of the same shim with ``-DSDCA_ACCURATE_MATH`` goes to
+  ``oracle/_ref/libsdca_ref_accurate.so``.
 
 The reference flags follow its default (non ``SDCA_ACCURATE_MATH``) build, but
 without ``-Ofast``/``-ffast-math`` so that results do not depend on the
@@ -20,8 +22,13 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DIR = os.environ.get("SDCA_REFERENCE_DIR", "/root/reference")
+# the reference's source tree: named by the environment, else looked for beside this
+# repository (../reference); where neither exists the prebuilt library is used
+REF_DIR = os.environ.get("SDCA_REFERENCE_DIR") or os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 REF_SO = os.path.join(HERE, "_ref", "libsdca_ref.so")
+# the same shim against the same headers with SDCA_ACCURATE_MATH defined: the reference's
+# optional exact recomputation of t (prox/knapsack_eq.h:87-106) and of W (eval/core.h:148-182)
+REF_ACCURATE_SO = os.path.join(HERE, "_ref", "libsdca_ref_accurate.so")
 ORACLE_SO = os.path.join(HERE, "libsdca_oracle.so")
 
 
@@ -57,7 +64,7 @@ def build_reference(force=False):
     blas = os.path.join(HERE, "cblas_seq.c")
     if not os.path.isdir(inc):
         return REF_SO if os.path.exists(REF_SO) else None
-    if not force and _newer(REF_SO, [shim, blas]):
+    if not force and _newer(REF_SO, [shim, blas]) and _newer(REF_ACCURATE_SO, [shim, blas]):
         return REF_SO
     os.makedirs(os.path.dirname(REF_SO), exist_ok=True)
     obj = os.path.join(HERE, "_ref", "cblas_seq.o")
@@ -65,6 +72,9 @@ def build_reference(force=False):
     _run(["g++", "-std=c++14", "-O2", "-fPIC", "-shared", "-include", "limits",
           "-DBLAS_DEFAULT_LOCAL_HEADER", "-I", inc, shim, obj, "-o", REF_SO,
           "-lpthread", "-ldl"])
+    _run(["g++", "-std=c++14", "-O2", "-fPIC", "-shared", "-include", "limits",
+          "-DBLAS_DEFAULT_LOCAL_HEADER", "-DSDCA_ACCURATE_MATH", "-I", inc, shim, obj, "-o",
+          REF_ACCURATE_SO, "-lpthread", "-ldl"])
     return REF_SO
 
 

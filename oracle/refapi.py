@@ -211,6 +211,11 @@ class Reference(_Backend):
         return self.lib.sdca_ref_use_blas(path.encode() if path else None, int(num_threads))
 
 
+class ReferenceAccurate(Reference):
+    """The same headers compiled with SDCA_ACCURATE_MATH."""
+    path = os.path.join(HERE, "_ref", "libsdca_ref_accurate.so")
+
+
 class Restatement(_Backend):
     prefix = "sdca_oracle_"
     path = os.path.join(HERE, "libsdca_oracle.so")
@@ -223,6 +228,12 @@ def reference():
     if "ref" not in _cache:
         _cache["ref"] = Reference()
     return _cache["ref"]
+
+
+def reference_accurate():
+    if "acc" not in _cache:
+        _cache["acc"] = ReferenceAccurate()
+    return _cache["acc"]
 
 
 def restatement():

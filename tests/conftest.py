@@ -23,6 +23,16 @@ def ref():
 
 
 @pytest.fixture(scope="session")
+def ref_accurate():
+    """The reference compiled with SDCA_ACCURATE_MATH (exact recomputation of t)."""
+    from oracle import build_oracle, refapi
+    build_oracle.build_reference()
+    if not os.path.exists(refapi.ReferenceAccurate.path):
+        pytest.skip("oracle/_ref/libsdca_ref_accurate.so is not built and the reference tree is absent")
+    return refapi.reference_accurate()
+
+
+@pytest.fixture(scope="session")
 def hostsim():
     from tests.hostsim import build as hb
     return hb.load()

@@ -78,7 +78,7 @@ extern "C" int sdcab_hostsim_prox(const char* name, int dtype, void* a, int64_t 
                                   sdcab_thresholds* thr, int apply) {
   int prox = sdcab::prox_id_from_name(name);
   if (prox < 0) return SDCAB_ERR_PROX;
-  sdcab::ProxParams q{o->lo, o->hi, o->rhs, o->rho, o->alpha, (int)o->k, (int)o->p};
+  sdcab::ProxParams q{o->lo, o->hi, o->rhs, o->rho, o->alpha, (int)o->k, (int)o->p, o->accurate_math ? 1 : 0};
   const bool f = (o->precision == SDCAB_PRECISION_FLOAT);
   if (dtype == 0) return f ? run<float, float>(prox, (float*)a, m, n, q, thr, apply)
                            : run<float, double>(prox, (float*)a, m, n, q, thr, apply);

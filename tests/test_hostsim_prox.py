@@ -55,3 +55,32 @@ def test_lambert(ref, hostsim):
         y, _ = hostsim.run("lambert_w_exp", x)
         y_ref = ref.prox("lambert_w_exp", x)
         assert np.array_equal(y, y_ref)
+
+
+ACCURATE = ["knapsack_eq", "knapsack_le", "knapsack_le_biased", "topk_simplex", "topk_simplex_biased"]
+
+
+@pytest.mark.parametrize("name", ACCURATE)
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_accurate_math_matches_the_accurate_build(ref, ref_accurate, hostsim, name, dtype):
+    """opts.accurate_math recomputes t from the final sets like the reference built with
+    SDCA_ACCURATE_MATH (prox/knapsack_eq.h:87-106); compared with that build, and the
+    recomputation really changes some thresholds against the default build."""
+    rng = np.random.default_rng(stable_seed("accurate", name, str(dtype)))
+    changed = 0
+    for kind in ("normal", "pos", "neg", "mixed", "ties"):
+        for m in (2, 3, 5, 33, 200):
+            a = regime(rng, 24, m, dtype, kind)
+            kw = random_opts(rng, name, m)
+            x_ref = ref_accurate.prox(name, a, **kw)
+            x, thr = hostsim.run(name, a, accurate_math=True, **kw)
+            tol = tolerance(dtype, "double", m)
+            assert scaled_error(x, x_ref, a).max() <= tol, (name, kind, m, kw)
+            t_acc = ref_accurate.thresholds(name, a, **kw)["t"]
+            t_def = ref.thresholds(name, a, **kw)["t"]
+            changed += int((t_acc != t_def).sum())
+            same = np.abs(thr["t"] - t_acc) <= tol * np.maximum(1, np.abs(t_acc))
+            degenerate = ref_accurate.thresholds(name, a, **kw)["num_mid"] == 0
+            # (the top-k operators report other thresholds for their special cases)
+            assert name.startswith("topk") or (same | degenerate).all(), (name, kind, m, kw)
+    assert changed > 0

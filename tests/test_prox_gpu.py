@@ -189,3 +189,19 @@ def test_edge_shapes(ref, cuda_lib):
         assert scaled_error(x, ref.prox("knapsack", a), a).max() <= 1e-5
         x = run_dev(cuda_lib, "topk_cone", a, k=1)
         assert scaled_error(x, ref.prox("topk_cone", a, k=1), a).max() <= 1e-5
+
+
+@pytest.mark.parametrize("name", ["knapsack_eq", "knapsack_le", "knapsack_le_biased", "topk_simplex",
+                                  "topk_simplex_biased"])
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_accurate_math_matches_the_accurate_build(ref_accurate, cuda_lib, name, dtype):
+    """opts.accurate_math = 1: the exact recomputation of t of the reference's
+    SDCA_ACCURATE_MATH build (prox/knapsack_eq.h:87-106), against that build."""
+    rng = np.random.default_rng(stable_seed("accurate-gpu", name, str(dtype)))
+    for kind in ("normal", "pos", "neg", "mixed", "ties"):
+        for m in (2, 5, 33, 100, 200, 1000, 1025):
+            a = regime(rng, 37, m, dtype, kind)
+            kw = random_opts(rng, name, m)
+            x_ref = ref_accurate.prox(name, a, **kw)
+            x = run_dev(cuda_lib, name, a, accurate_math=True, **kw)
+            assert scaled_error(x, x_ref, a).max() <= tolerance(dtype, "double", m), (name, kind, m, kw)
