@@ -87,6 +87,13 @@ void sdcab_prox_opts_default(sdcab_prox_opts* opts);
 typedef struct sdcab_thresholds {
   double t, lo, hi;
   int32_t num_hi, num_mid;
+  int32_t status;    /* 0: solved.  bit 0: a bounded search ended without an admissible
+                      * answer and the all-zero default stands in, which is what the
+                      * reference returns silently (prox/topk_cone.h:131,
+                      * knapsack_le_biased.h:85).  bit 1: a threshold is not finite
+                      * (NaN or infinite entries in the vector; the reference asserts,
+                      * proxdef.h:112) */
+  int32_t reserved;
 } sdcab_thresholds;
 
 /*

@@ -42,11 +42,12 @@ class ProxOpts(C.Structure):
 
 class Thresholds(C.Structure):
     _fields_ = [("t", C.c_double), ("lo", C.c_double), ("hi", C.c_double),
-                ("num_hi", C.c_int32), ("num_mid", C.c_int32)]
+                ("num_hi", C.c_int32), ("num_mid", C.c_int32), ("status", C.c_int32),
+                ("reserved", C.c_int32)]
 
 
 THR_DTYPE = np.dtype([("t", "<f8"), ("lo", "<f8"), ("hi", "<f8"),
-                      ("num_hi", "<i4"), ("num_mid", "<i4")])
+                      ("num_hi", "<i4"), ("num_mid", "<i4"), ("status", "<i4"), ("reserved", "<i4")])
 
 _lib = None
 

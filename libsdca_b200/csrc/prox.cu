@@ -44,9 +44,12 @@ prox_rows_kernel(const Data* a, Data* out, int m, long long n, ProxParams q,
       ThrPair<R> pr = thr_two_simplex<R>(ra, rb, static_cast<R>(q.rhs));
       if (thr_out && lane == 0) {
         sdcab_thresholds o;
+        o.reserved = 0;
         o.t = pr.a.t; o.lo = pr.a.lo; o.hi = pr.a.hi; o.num_hi = pr.a.nU; o.num_mid = pr.a.nM;
+        o.status = thr_status(pr.a);
         thr_out[2 * row] = o;
         o.t = pr.b.t; o.lo = pr.b.lo; o.hi = pr.b.hi; o.num_hi = pr.b.nU; o.num_mid = pr.b.nM;
+        o.status = thr_status(pr.b);
         thr_out[2 * row + 1] = o;
       }
       if (apply) {
@@ -59,6 +62,7 @@ prox_rows_kernel(const Data* a, Data* out, int m, long long n, ProxParams q,
       if (thr_out && lane == 0) {
         sdcab_thresholds o;
         o.t = thr.t; o.lo = thr.lo; o.hi = thr.hi; o.num_hi = thr.nU; o.num_mid = thr.nM;
+        o.status = thr_status(thr); o.reserved = 0;
         thr_out[row] = o;
       }
       if (apply) {

@@ -65,6 +65,12 @@ SDCAB_D Thr<R> compute_thresholds(int prox, const Row& row, const ProxParams& q)
   return make_thr(R(0), R(0), R(0), 0, 0, R(0), R(0));
 }
 
+// Status of a row as the thresholds entry points report it.
+template <typename R>
+SDCAB_HD int thr_status(const Thr<R>& t) {
+  return t.status | ((finite_(t.t) && finite_(t.hi) && finite_(t.lo)) ? 0 : kThrNotFinite);
+}
+
 // The clip of proxdef.h:176-177 with std::max / std::min operand order.
 template <typename Data>
 SDCAB_HD Data clip_(Data v, Data lo, Data hi) {

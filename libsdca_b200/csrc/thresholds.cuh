@@ -30,12 +30,16 @@ struct Thr {
   R t, lo, hi;
   int nU, nM;
   R cutU, cutM;
+  int status;   // 0: solved; kThrUnsettled: a bounded search ended without an admissible
+                // answer and the all-zero default stands in (as in the reference)
 };
+enum { kThrSolved = 0, kThrUnsettled = 1, kThrNotFinite = 2 };
 
 template <typename R>
 SDCAB_HD Thr<R> make_thr(R t, R lo, R hi, int nU, int nM, R cutU, R cutM) {
   Thr<R> r;
   r.t = t; r.lo = lo; r.hi = hi; r.nU = nU; r.nM = nM; r.cutU = cutU; r.cutM = cutM;
+  r.status = kThrSolved;
   return r;
 }
 
@@ -271,7 +275,11 @@ SDCAB_D Thr<R> thr_knapsack_le_biased_root(const Row& row, R lo, R hi, R rhs, R 
     }
     t = tn;
   }
-  if (!(t <= rho * rhs + eps)) return make_thr(R(0), R(0), R(0), 0, 0, R(0), R(0));
+  if (!(t <= rho * rhs + eps)) {
+    Thr<R> none = make_thr(R(0), R(0), R(0), 0, 0, R(0), R(0));
+    none.status = kThrUnsettled;
+    return none;
+  }
   return make_thr(t, lo, hi, nU, nM, hi + t, lo + t);
 }
 
@@ -382,7 +390,9 @@ SDCAB_D Thr<R> thr_topk_cone_search(const Row& row, int k, R rho) {
     if (!has_next) break;
     tk = nx; min_U = s_u; sum_U += s_u;
   }
-  return make_thr(R(0), R(0), R(0), 0, 0, num<R>::inf(), num<R>::inf());
+  Thr<R> none = make_thr(R(0), R(0), R(0), 0, 0, num<R>::inf(), num<R>::inf());
+  none.status = kThrUnsettled;
+  return none;
 }
 
 // (include/sdca/prox/topk_cone.h:144-157, topk_cone_biased.h:124-139)

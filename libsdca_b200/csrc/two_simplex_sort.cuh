@@ -116,9 +116,9 @@ two_simplex_sort_kernel(const Data* a, Data* out, int m, long long n, ProxParams
     tb = __shfl_sync(0xffffffffu, tb, 0);
     if (thr_out && lane == 0) {
       sdcab_thresholds o;
-      o.lo = 0; o.hi = q.rhs; o.num_hi = 0;
-      o.t = ta; o.num_mid = r; thr_out[2 * row] = o;
-      o.t = tb; o.num_mid = s; thr_out[2 * row + 1] = o;
+      o.lo = 0; o.hi = q.rhs; o.num_hi = 0; o.reserved = 0;
+      o.t = ta; o.num_mid = r; o.status = finite_(ta) ? kThrSolved : kThrNotFinite; thr_out[2 * row] = o;
+      o.t = tb; o.num_mid = s; o.status = finite_(tb) ? kThrSolved : kThrNotFinite; thr_out[2 * row + 1] = o;
     }
     if (apply) {
       const Thr<R> tha = make_thr(ta, R(0), static_cast<R>(q.rhs), 0, 0, R(0), R(0));

@@ -31,8 +31,8 @@ int run(int prox, Data* a, int64_t m, int64_t n, const sdcab::ProxParams& q,
       StridedRow<Data> ra(x, q.p), rb(x + q.p, static_cast<int>(m) - q.p);
       ThrPair<R> pr = thr_two_simplex<R>(ra, rb, static_cast<R>(q.rhs));
       if (thr) {
-        thr[2 * r] = {double(pr.a.t), double(pr.a.lo), double(pr.a.hi), pr.a.nU, pr.a.nM};
-        thr[2 * r + 1] = {double(pr.b.t), double(pr.b.lo), double(pr.b.hi), pr.b.nU, pr.b.nM};
+        thr[2 * r] = {double(pr.a.t), double(pr.a.lo), double(pr.a.hi), pr.a.nU, pr.a.nM, thr_status(pr.a), 0};
+        thr[2 * r + 1] = {double(pr.b.t), double(pr.b.lo), double(pr.b.hi), pr.b.nU, pr.b.nM, thr_status(pr.b), 0};
       }
       if (apply) {
         Applier<Data> fa(pr.a, kMapIdentity, 1.0), fb(pr.b, kMapIdentity, 1.0);
@@ -49,8 +49,8 @@ int run(int prox, Data* a, int64_t m, int64_t n, const sdcab::ProxParams& q,
       R ta, tb; int rr, ss;
       two_simplex_sort_walk<R, Data>(sa.data(), na, sb.data(), nb, static_cast<R>(q.rhs), ta, tb, rr, ss);
       if (thr) {
-        thr[2 * r] = {double(ta), 0.0, q.rhs, 0, rr};
-        thr[2 * r + 1] = {double(tb), 0.0, q.rhs, 0, ss};
+        thr[2 * r] = {double(ta), 0.0, q.rhs, 0, rr, finite_(ta) ? 0 : 2, 0};
+        thr[2 * r + 1] = {double(tb), 0.0, q.rhs, 0, ss, finite_(tb) ? 0 : 2, 0};
       }
       if (apply) {
         Applier<Data> fa(make_thr(ta, R(0), static_cast<R>(q.rhs), 0, 0, R(0), R(0)), kMapIdentity, 1.0);
@@ -62,7 +62,7 @@ int run(int prox, Data* a, int64_t m, int64_t n, const sdcab::ProxParams& q,
     }
     StridedRow<Data> row(x, static_cast<int>(m));
     Thr<R> t = compute_thresholds<R>(prox, row, q);
-    if (thr) thr[r] = {double(t.t), double(t.lo), double(t.hi), t.nU, t.nM};
+    if (thr) thr[r] = {double(t.t), double(t.lo), double(t.hi), t.nU, t.nM, thr_status(t), 0};
     if (apply) {
       Applier<Data> f(t, prox_map(prox), q.alpha);
       for (int64_t i = 0; i < m; ++i) x[i] = f(x[i]);

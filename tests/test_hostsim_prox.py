@@ -84,3 +84,31 @@ def test_accurate_math_matches_the_accurate_build(ref, ref_accurate, hostsim, na
             # (the top-k operators report other thresholds for their special cases)
             assert name.startswith("topk") or (same | degenerate).all(), (name, kind, m, kw)
     assert changed > 0
+
+
+@pytest.mark.parametrize("name", PROX_SINGLE + ["two_simplex", "two_simplex_sort"])
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_nan_and_infinite_rows_end_with_a_defined_status(hostsim, name, dtype):
+    """Rows with NaN or infinite entries: every search is bounded, so the call returns, and
+    the thresholds entry point flags each such row (status bit 1: a threshold is not finite,
+    or bit 0: the search ended on its default) or reports finite thresholds.  Clean rows in
+    the same batch are unaffected.  (The reference asserts on such input, proxdef.h:112.)"""
+    rng = np.random.default_rng(stable_seed("nonfinite", name, str(dtype)))
+    for m in (2, 5, 33, 200):
+        base = regime(rng, 12, m, dtype, "normal")
+        kw = random_opts(rng, name, m)
+        clean, thr_clean = hostsim.run(name, base, **kw)
+        bad = base.copy()
+        bad[1, 0] = np.nan
+        bad[3, m // 2] = np.inf
+        bad[5, m - 1] = -np.inf
+        bad[7, :] = np.nan
+        bad[9, 0] = np.inf; bad[9, m - 1] = -np.inf
+        out, thr = hostsim.run(name, bad, **kw)          # returns: bounded termination
+        per_row = 2 if name.startswith("two_simplex") else 1
+        status = thr["status"].reshape(-1, per_row)
+        assert set(np.unique(status)) <= {0, 1, 2, 3}
+        finite_thr = (np.isfinite(thr["t"]) & np.isfinite(thr["hi"])).reshape(-1, per_row)
+        assert ((status & 2) != 0).all(axis=1)[~finite_thr.all(axis=1)].all()
+        for r in (0, 2, 4, 6, 8, 10, 11):
+            assert np.array_equal(out[r], clean[r]) and (status[r] == thr_clean["status"].reshape(-1, per_row)[r]).all()
