@@ -108,7 +108,8 @@ def test_nan_and_infinite_rows_end_with_a_defined_status(hostsim, name, dtype):
         per_row = 2 if name.startswith("two_simplex") else 1
         status = thr["status"].reshape(-1, per_row)
         assert set(np.unique(status)) <= {0, 1, 2, 3}
-        finite_thr = (np.isfinite(thr["t"]) & np.isfinite(thr["hi"])).reshape(-1, per_row)
-        assert ((status & 2) != 0).all(axis=1)[~finite_thr.all(axis=1)].all()
+        finite_thr = np.isfinite(thr["t"]) & np.isfinite(thr["hi"]) & np.isfinite(thr["lo"])
+        assert ((thr["status"] & 2) != 0)[~finite_thr].all()       # every non-finite record is flagged
+        assert ((thr["status"] & 2) == 0)[finite_thr].all()
         for r in (0, 2, 4, 6, 8, 10, 11):
             assert np.array_equal(out[r], clean[r]) and (status[r] == thr_clean["status"].reshape(-1, per_row)[r]).all()
