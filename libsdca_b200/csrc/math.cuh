@@ -25,6 +25,20 @@ SDCAB_HD T householder5(T w, T y) {
                  (f11 * (T(24) * f11 + T(36) * f0y) + f00y * (T(14) * y + f0 + T(8)));
 }
 
+#if defined(__CUDA_ARCH__)
+// The same step for float data on the device with the quotient formed by the fast
+// division (reciprocal approximation and a multiply, 2 ulp): the quotient is the
+// correction term of a fifth-order step, a few per cent of w at most, so its last bits
+// do not reach the result, and an IEEE division costs as much as the rest of the step.
+__device__ __forceinline__ float householder5_fast(float w, float y) {
+  const float f0 = w - y, f1 = 1.0f + y;
+  const float f11 = f1 * f1, f0y = f0 * y;
+  const float f00y = f0 * f0y;
+  return w - __fdividef(4.0f * f0 * (6.0f * f1 * (f11 + f0y) + f00y),
+                        f11 * (24.0f * f11 + 36.0f * f0y) + f00y * (14.0f * y + f0 + 8.0f));
+}
+#endif
+
 // (1 + x/1024)^1024 by ten squarings   (reference: math/lambert.h:53-62)
 template <typename T>
 SDCAB_HD T exp_crude(T x) {
@@ -47,11 +61,19 @@ SDCAB_HD float lambert_w_exp(float x) {
   const bool upper = x > -1.0f;                 // (-1, +inf)
   const bool tail_lo = !(x > -18.0f);           // (-inf, -18]
   const bool tail_hi = x > 8.0f;                // (8, +inf)
+#if defined(__CUDA_ARCH__)
+  const float seed = upper ? householder5_fast(x, 1.0f) : exp_crude(x);
+#else
   const float seed = upper ? householder5(x, 1.0f) : exp_crude(x);
+#endif
   const float e = exp_(tail_lo ? x : x - seed);
   const float w_in = tail_hi ? x - log_(x) : seed;
   const float y_in = tail_hi ? x : e;
+#if defined(__CUDA_ARCH__)
+  const float stepped = householder5_fast(w_in, y_in);
+#else
   const float stepped = householder5(w_in, y_in);
+#endif
   if (tail_lo) return (x > -104.0f) ? e : 0.0f;
   if (tail_hi && !(x <= 536870912.0f)) return x;
   return stepped;
