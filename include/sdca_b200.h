@@ -389,7 +389,10 @@ typedef struct sdcab_fit_result {
  * sdca_blas_gemm(D, M, N, X, D, A, M, W, NoTrans, Trans[, 1, 1])), W = [W0 +] X A'.
  * x: d x n column major (features), a: m x n column major (dual variables),
  * w0: d x m column major or NULL, w: d x m column major (written).  All device
- * pointers; the sum over the examples runs in a fixed order.
+ * pointers; the sum over the examples runs in a fixed order.  Float data of 2048
+ * examples and more runs on the tensor cores (3xTF32, float accuracy); that form
+ * synchronises the stream before it returns and reports a wait that ran out inside
+ * the kernel as SDCAB_ERR_TIMEOUT.
  */
 int sdcab_primal_from_dual_f32_dev(const float* x, const float* a, const float* w0, float* w,
                                    int64_t d, int64_t m, int64_t n, void* stream);
@@ -562,6 +565,7 @@ int sdcab_train_f64(const sdcab_dataset* datasets, int64_t num_datasets,
  *   "gemm_write_hi", 0|1   1: the paired kernel stores the TF32 head of every
  *                      operand explicitly instead of leaving the truncation to the
  *                      tensor core
+ *   "primal_simt", 0|1   1: sdcab_primal_from_dual_f32_dev on the CUDA cores
  * Returns SDCAB_ERR_ARG for an unknown name.  Not thread safe. */
 int sdcab_test_set(const char* name, int64_t value);
 

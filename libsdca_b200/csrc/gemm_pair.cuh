@@ -30,6 +30,17 @@
 //     finished chunk into float registers (rounded additions) while the next chunk
 //     is being multiplied, across tile boundaries.
 //
+// The same kernel serves the product with the contraction index as the SLOW index of
+// both operands (template flag kMN): W = A' X, primal variables from dual variables
+// (include/sdca/solver/eval/core.h:164-174 of the reference), where example i holds m
+// contiguous dual variables and d contiguous features.  The operand tiles are then
+// "MN-major": TMA brings boxes of 32 contiguous floats x 32 examples, a stage is four such
+// boxes per operand (written with the 32-byte-atom form of the 128-byte swizzle, the
+// only MN-major layout the tensor core takes for 32-bit operands), the shared-memory
+// descriptors name the stride between the boxes, and one MMA consumes a group of 8
+// examples (1024 bytes further per step).  The split into
+// head and remainder is elementwise, so it does not care.
+//
 // Roles per CTA (12 warps): warp 0 lane 0 issues TMA; warp 1 owns tensor memory
 // and, in the leader CTA (cluster rank 0), lane 0 issues every tcgen05.mma of the
 // pair; warps 2-3 only give up their registers; warps 4-11 split and drain.  Hand-overs go through mbarriers; the workers
@@ -76,6 +87,7 @@ constexpr int kPoolRegsNeeded = kControlRegs * 32 * kControlWarps + kWorkerRegs 
 static_assert(kPoolRegsNeeded <= 168 * kThreads, "setmaxnreg would wait for registers that never come");
 constexpr int kTileBytes = kBM * kBK * 4;                     // 16 KB, A and B halves alike
 constexpr int kRawBytes = 2 * kTileBytes;                     // A then B
+constexpr int kBoxBytes = 32 * kBK * 4;                       // MN-major: 32 floats x 32 examples
 constexpr int kSmemTiles = kRawStages * kRawBytes + kLoStages * kRawBytes;
 constexpr int kNumBarriers = 2 * kRawStages + 2 * kLoStages + 5;
 static_assert(kNumBarriers * 8 <= 256, "barrier area");
@@ -147,8 +159,26 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
       ::"r"(bar), "h"(mask) : "memory");
 }
 
+// MN-major operand.  For 32-bit operands the tensor core takes MN-major tiles in one
+// layout only, the 128-byte swizzle with 32-byte atoms: rows of 32 contiguous floats
+// along M (or N), 4 rows (contraction steps) per 512-byte swizzle atom, the 32-byte
+// pieces of a row exchanged among themselves by the row's index (TMA's
+// SWIZZLE_128B_ATOM_32B writes exactly this).  The next 32 floats along M / N lie
+// `box_bytes` further (leading byte offset), the next 4 contraction steps 512 bytes
+// further (stride byte offset); descriptor version 1, layout type 1.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t box_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>((box_bytes >> 4) & 0x3FFF) << 16;   // leading byte offset
+  d |= static_cast<uint64_t>(512 >> 4) << 32;                    // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                           // version
+  d |= static_cast<uint64_t>(1) << 61;                           // SWIZZLE_128B_BASE32B
+  return d;
+}
+
 struct Params {
   float* C;
+  const float* C0;           // optional addend with the layout of C (W0), or null
   long long ldc;
   int M, N, K;
   int tiles_m, tiles_n;      // 256 x 256 tiles
@@ -157,7 +187,7 @@ struct Params {
   int lose_tile;             // test switch: the leader's TMA skips this stage (-1: none)
 };
 
-template <bool kWriteHi>
+template <bool kWriteHi, bool kMN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b, Params p) {
@@ -233,8 +263,17 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           if (!ok) break;
           if (it == p.lose_tile && rank == 0) continue;   // test switch: this stage never lands
           mbar_expect_tx(bar_full(s), kRawBytes);
-          tma_load_2d(smem_u32(a_raw(s)), &map_a, kt * kBK, m0, bar_full(s));
-          tma_load_2d(smem_u32(b_raw(s)), &map_b, kt * kBK, n0, bar_full(s));
+          if (kMN) {
+            // four boxes of 32 floats x 32 examples per operand
+#pragma unroll
+            for (int c = 0; c < kBM / 32; ++c) {
+              tma_load_2d(smem_u32(a_raw(s)) + c * kBoxBytes, &map_a, m0 + 32 * c, kt * kBK, bar_full(s));
+              tma_load_2d(smem_u32(b_raw(s)) + c * kBoxBytes, &map_b, n0 + 32 * c, kt * kBK, bar_full(s));
+            }
+          } else {
+            tma_load_2d(smem_u32(a_raw(s)), &map_a, kt * kBK, m0, bar_full(s));
+            tma_load_2d(smem_u32(b_raw(s)), &map_b, kt * kBK, n0, bar_full(s));
+          }
 #pragma unroll
           for (int q = 0; q < kRawStages; ++q) if (q == s) last_issue[q] = it;
         }
@@ -251,6 +290,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     if (lane == 0 && rank == 0) {
       // instruction descriptor: D = F32, A = B = TF32, both K-major, N = 256, M = 256 (pair)
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) |
+                             (kMN ? ((1u << 15) | (1u << 16)) : 0u) |      // both operands MN-major
                              (static_cast<uint32_t>(kBN >> 3) << 17) |
                              (static_cast<uint32_t>((2 * kBM) >> 4) << 24);
       int it = 0, ch = 0;
@@ -271,13 +311,15 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(b * kBN);
-          const uint64_t da_hi = smem_desc_sw128(smem_u32(a_raw(s4)));
-          const uint64_t db_hi = smem_desc_sw128(smem_u32(b_raw(s4)));
-          const uint64_t da_lo = smem_desc_sw128(smem_u32(a_lo(s2)));
-          const uint64_t db_lo = smem_desc_sw128(smem_u32(b_lo(s2)));
+          const uint64_t da_hi = kMN ? smem_desc_mn_sw128(smem_u32(a_raw(s4)), kBoxBytes) : smem_desc_sw128(smem_u32(a_raw(s4)));
+          const uint64_t db_hi = kMN ? smem_desc_mn_sw128(smem_u32(b_raw(s4)), kBoxBytes) : smem_desc_sw128(smem_u32(b_raw(s4)));
+          const uint64_t da_lo = kMN ? smem_desc_mn_sw128(smem_u32(a_lo(s2)), kBoxBytes) : smem_desc_sw128(smem_u32(a_lo(s2)));
+          const uint64_t db_lo = kMN ? smem_desc_mn_sw128(smem_u32(b_lo(s2)), kBoxBytes) : smem_desc_sw128(smem_u32(b_lo(s2)));
 #pragma unroll
           for (int ks = 0; ks < kBK / 8; ++ks) {
-            const uint64_t off = static_cast<uint64_t>(ks * 32 >> 4);  // 8 floats = 32 bytes
+            // one MMA takes 8 contraction steps: 32 bytes along a K-major row, or the next
+            // group of 8 rows (1024 bytes) of an MN-major box
+            const uint64_t off = static_cast<uint64_t>((kMN ? ks * 1024 : ks * 32) >> 4);
             // small terms first, the large product last
             mma_tf32_pair(tmem_d, da_lo + off, db_hi + off, idesc, !(chunk_first && ks == 0));
             mma_tf32_pair(tmem_d, da_hi + off, db_lo + off, idesc, 1);
@@ -355,14 +397,21 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
         if (row < p.M) {
           float* dst = p.C + static_cast<long long>(row) * p.ldc + col0;
-          if (vec_ok && col0 + kBN / 2 <= p.N) {
+          const float* add = p.C0 ? p.C0 + static_cast<long long>(row) * p.ldc + col0 : nullptr;
+          if (vec_ok && col0 + kBN / 2 <= p.N && (!add || (reinterpret_cast<uintptr_t>(p.C0) & 15) == 0)) {
 #pragma unroll
-            for (int j = 0; j < kBN / 2; j += 4)
-              *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            for (int j = 0; j < kBN / 2; j += 4) {
+              float4 o = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+              if (add) {
+                const float4 w0 = *reinterpret_cast<const float4*>(add + j);
+                o.x += w0.x; o.y += w0.y; o.z += w0.z; o.w += w0.w;
+              }
+              *reinterpret_cast<float4*>(dst + j) = o;
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < kBN / 2; ++j)
-              if (col0 + j < p.N) dst[j] = acc[j];
+              if (col0 + j < p.N) dst[j] = add ? acc[j] + add[j] : acc[j];
           }
         }
       }
@@ -440,7 +489,7 @@ inline int launch(const float* A, const float* B, float* C, int M, int N, int K,
   CUtensorMap map_a, map_b;
   if (!tc::make_map(&map_a, A, M, K, lda, kBM) || !tc::make_map(&map_b, B, N, K, ldb, kBNHalf))
     return SDCAB_ERR_CUDA;
-  auto kernel = write_hi ? gemm_tf32x3_pair_kernel<true> : gemm_tf32x3_pair_kernel<false>;
+  auto kernel = write_hi ? gemm_tf32x3_pair_kernel<true, false> : gemm_tf32x3_pair_kernel<false, false>;
   // the opt-in to large dynamic shared memory is a property of the function on each
   // device, so it is set on every launch (a cheap host-side call)
   SDCAB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
@@ -452,12 +501,61 @@ inline int launch(const float* A, const float* B, float* C, int M, int N, int K,
   SDCAB_CUDA_TRY(cudaFuncGetAttributes(&attr, kernel));
   if (attr.numRegs * kThreads < kPoolRegsNeeded) return SDCAB_ERR_NOT_IMPLEMENTED;
   Params p;
-  p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.err = err_dev;
+  p.C = C; p.C0 = nullptr; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.err = err_dev;
   p.tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
   p.tiles_n = (N + kBN - 1) / kBN;
   p.spin_limit = lose_a_tile ? kSpinLimitShort : kSpinLimit;
   p.lose_tile = lose_a_tile ? 1 : -1;
   // one pair of CTAs per pair of SMs, or fewer when there are fewer tiles
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  int pairs = std::max(1, info.sm_count / 2);
+  if (tiles < pairs) pairs = static_cast<int>(tiles);
+  kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  SDCAB_CUDA_TRY(cudaGetLastError());
+  return SDCAB_OK;
+}
+
+// box = 32 contiguous floats x 32 rows of a rows x cols matrix (row stride ld floats)
+inline bool make_map_mn(CUtensorMap* map, const float* base, long long rows, long long cols, long long ld) {
+  tc::EncodeTiledFn fn = tc::encode_tiled();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * sizeof(float)};
+  cuuint32_t box[2] = {32, static_cast<cuuint32_t>(kBK)};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Whether the MN-major form can take C = A' B (+ C0): TMA's alignment rules.
+inline bool usable_mn(const float* A, const float* B, const float* C0, long long lda, long long ldb) {
+  return ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 &&
+         (lda % 4) == 0 && (ldb % 4) == 0 && tc::encode_tiled() != nullptr &&
+         (!C0 || (reinterpret_cast<uintptr_t>(C0) & 3) == 0);
+}
+
+// C (M x N, ldc) = A' B [+ C0] with A: K x M (row stride lda), B: K x N (row stride ldb):
+// the contraction index is the slow index of both operands.  err_dev as in launch().
+inline int launch_mn(const float* A, const float* B, const float* C0, float* C, int M, int N, long long K,
+                     long long lda, long long ldb, long long ldc, int* err_dev, cudaStream_t stream) {
+  if (K > 0x7fffffffLL - kBK) return SDCAB_ERR_TOO_LARGE;
+  CUtensorMap map_a, map_b;
+  if (!make_map_mn(&map_a, A, K, M, lda) || !make_map_mn(&map_b, B, K, N, ldb)) return SDCAB_ERR_CUDA;
+  auto kernel = gemm_tf32x3_pair_kernel<false, true>;
+  SDCAB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  DeviceInfo info;
+  int rc = get_device_info(&info);
+  if (rc) return rc;
+  cudaFuncAttributes attr;
+  SDCAB_CUDA_TRY(cudaFuncGetAttributes(&attr, kernel));
+  if (attr.numRegs * kThreads < kPoolRegsNeeded) return SDCAB_ERR_NOT_IMPLEMENTED;
+  Params p;
+  p.C = C; p.C0 = C0; p.ldc = ldc; p.M = M; p.N = N; p.K = static_cast<int>(K); p.err = err_dev;
+  p.tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
+  p.tiles_n = (N + kBN - 1) / kBN;
+  p.spin_limit = kSpinLimit;
+  p.lose_tile = -1;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   int pairs = std::max(1, info.sm_count / 2);
   if (tiles < pairs) pairs = static_cast<int>(tiles);

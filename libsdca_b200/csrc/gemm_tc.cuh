@@ -119,7 +119,8 @@ struct Params {
   int* err;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+// (internal linkage: the header is included by more than one translation unit)
+static __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a,
                    const __grid_constant__ CUtensorMap map_b, Params p) {
   extern __shared__ unsigned char smem_dyn[];

@@ -67,7 +67,13 @@ SDCAB_HD float lambert_w_exp(float x) {
   const float seed = upper ? householder5(x, 1.0f) : exp_crude(x);
 #endif
   const float e = exp_(tail_lo ? x : x - seed);
+#if defined(__CUDA_ARCH__)
+  // x > 8: the seed x - log(x) feeds one fifth-order step; the fast logarithm's absolute
+  // error of 2e-7 on a seed of 6 and more is far below what that step removes
+  const float w_in = tail_hi ? x - __logf(x) : seed;
+#else
   const float w_in = tail_hi ? x - log_(x) : seed;
+#endif
   const float y_in = tail_hi ? x : e;
 #if defined(__CUDA_ARCH__)
   const float stepped = householder5_fast(w_in, y_in);

@@ -6,11 +6,17 @@
 // of A and BK rows of X, loaded as they lie in memory, and every thread adds
 // a[j] * x[i] for its TJ x TI block of W.  FMA in the data type, like the BLAS
 // gemm the reference calls (include/sdca/solver/eval/core.h:164-174).
+//
+// Float data of more than a few thousand examples goes to the tensor cores instead:
+// the paired-CTA 3xTF32 kernel of gemm_pair.cuh in its MN-major form, one pair of CTAs
+// per 256 x 256 tile of W walking over all examples in order (a fixed summation order,
+// so the result is the same from run to run).
 #include <algorithm>
 #include <cstdint>
 
 #include "../../include/sdca_b200.h"
 #include "common_host.h"
+#include "gemm_pair.cuh"
 #include "primal.h"
 
 namespace sdcab {
@@ -96,6 +102,35 @@ __global__ void primal_reduce_kernel(const T* __restrict__ slices, const T* __re
   }
 }
 
+static int g_primal_force_simt = 0;
+void primal_test_force_simt(int on) { g_primal_force_simt = on ? 1 : 0; }
+
+// The tensor-core form; kNotTaken when the operands do not qualify.
+constexpr int kNotTaken = 1;
+inline int primal_tc(const float* x, const float* a, const float* w0, float* w, long long d, long long m,
+                     long long n, cudaStream_t stream) {
+  if (g_primal_force_simt || n < 2048 || d > 0x7fffffffLL || m > 0x7fffffffLL) return kNotTaken;
+  if (!tc2::usable_mn(a, x, w0, m, d) || (d % 4) != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0)
+    return kNotTaken;
+  void* err = nullptr;
+  int rc = workspace_reserve(5, 256, &err);
+  if (rc) return rc;
+  SDCAB_CUDA_TRY(cudaMemsetAsync(err, 0, sizeof(int), stream));
+  rc = tc2::launch_mn(a, x, w0, w, static_cast<int>(m), static_cast<int>(d), n, m, d, d,
+                      static_cast<int*>(err), stream);
+  if (rc == SDCAB_ERR_NOT_IMPLEMENTED) return kNotTaken;
+  if (rc) return rc;
+  // a wait that ran out inside the kernel becomes this call's status
+  int host_err = 0;
+  SDCAB_CUDA_TRY(cudaMemcpyAsync(&host_err, err, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  SDCAB_CUDA_TRY(cudaStreamSynchronize(stream));
+  return host_err ? SDCAB_ERR_TIMEOUT : SDCAB_OK;
+}
+inline int primal_tc(const double*, const double*, const double*, double*, long long, long long, long long,
+                     cudaStream_t) {
+  return kNotTaken;
+}
+
 template <typename Data>
 int primal_from_dual_dev(const Data* x, const Data* a, const Data* w0, Data* w, long long d,
                          long long m, long long n, cudaStream_t stream) {
@@ -104,6 +139,8 @@ int primal_from_dual_dev(const Data* x, const Data* a, const Data* w0, Data* w, 
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc) return rc;
+  rc = primal_tc(x, a, w0, w, d, m, n, stream);
+  if (rc != kNotTaken) return rc;
   const long long tiles_i = (d + kPrimalBI - 1) / kPrimalBI, tiles_j = (m + kPrimalBJ - 1) / kPrimalBJ;
   if (tiles_i > 0x7fffffffLL || tiles_j > 65535) return SDCAB_ERR_TOO_LARGE;
   // few tiles: slices of examples fill the device

@@ -15,4 +15,7 @@ template <typename Data>
 int primal_from_dual_dev(const Data* x, const Data* a, const Data* w0, Data* w, long long d,
                          long long m, long long n, cudaStream_t stream);
 
+// test switch: 1 keeps float data on the CUDA-core kernel
+void primal_test_force_simt(int on);
+
 }  // namespace sdcab

@@ -207,7 +207,11 @@ def test_primal_from_dual_matches_matrix_product(cuda_lib, dtype):
     launch that splits the examples into slices, with and without W0."""
     import torch
     rng = np.random.default_rng(stable_seed("primal-from-dual", str(dtype)))
-    for d, m, n in ((5, 3, 7), (128, 100, 1000), (300, 70, 4097), (4100, 10, 33), (1, 1, 1)):
+    # the last three are shapes the tensor-core form takes for float data (2048 examples and
+    # more, m and d multiples of four): ragged 256 x 256 tiles, more tiles than SM pairs'
+    # first round, a contraction that is not a multiple of the stage
+    for d, m, n in ((5, 3, 7), (128, 100, 1000), (300, 70, 4097), (4100, 10, 33), (1, 1, 1),
+                    (256, 100, 5000), (520, 1000, 3001), (4096, 12, 2048)):
         X = rng.standard_normal((n, d)).astype(dtype)
         A = rng.standard_normal((n, m)).astype(dtype)
         W0 = rng.standard_normal((m, d)).astype(dtype)
@@ -221,6 +225,16 @@ def test_primal_from_dual_matches_matrix_product(cuda_lib, dtype):
         # the same call twice gives the same bits (fixed summation order)
         again = cuda_lib.primal_from_dual(dev(X), dev(A), W0=dev(W0)).cpu().numpy()
         assert np.array_equal(W, again)
+        if dtype == np.float32 and n >= 2048 and m % 4 == 0 and d % 4 == 0:
+            # the CUDA-core kernel (test switch) is a different kernel with the same answer
+            from libsdca_b200 import binding as b
+            try:
+                b.test_set("primal_simt", 1)
+                simt = cuda_lib.primal_from_dual(dev(X), dev(A), W0=dev(W0)).cpu().numpy()
+            finally:
+                b.test_set("primal_simt", 0)
+            assert not np.array_equal(W, simt)
+            assert (np.abs(W - simt) <= 2 * tol * np.sqrt(n) * (scale + np.abs(W0))).all(), (d, m, n, "simt")
 
 
 @pytest.mark.parametrize("dtype", [np.float64, np.float32])
