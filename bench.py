@@ -276,7 +276,13 @@ def other_prox_config(args, rank, world, local_rank):
         "cpu_baseline": cpu, "gpu_launches": len(per_op) * max(args.steps, 10)}))
 
 
-def gap_roofline(tflops):
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_tf32x3_pair_kernel launch over a chunk of
+# 65 536 examples (ncu --set full): 1.360 GB + 0.250 GB; the algorithmic bytes of that chunk are
+# 65 536 x (4096 + 1000) x 4 B + 16.4 MB of W = 1.352 GB.  Traffic grows with the examples.
+NCU_DRAM_BYTES_PER_EXAMPLE_GAP = (1.360e9 + 0.250e9) / 65536
+
+
+def gap_roofline(tflops, examples=None):
     """The score GEMM runs on tcgen05 as 3xTF32: three tensor-core products per
     useful multiply-add, TF32 at half the bf16 rate, so the useful-flop ceiling is
     a sixth of the measured bf16 GEMM throughput."""
@@ -292,8 +298,12 @@ def gap_roofline(tflops):
     if peak is None:
         peak = 1590.0 / 6.0
     return {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s (useful fp32 flop; 3xTF32)",
-            "frac": tflops / peak, "traffic": None, "peak_kind": kind,
-            "kernel": "gemm_tf32x3_kernel (tcgen05, TMA) + eval_loss_kernel"}
+            "frac": tflops / peak,
+            "traffic": examples * NCU_DRAM_BYTES_PER_EXAMPLE_GAP if examples else None,
+            "traffic_note": "dram read + write bytes of the score GEMM for one evaluation on one GPU, scaled by "
+                            "examples from the ncu capture of a 65 536-example chunk",
+            "peak_kind": kind,
+            "kernel": "gemm_tf32x3_pair_kernel (tcgen05 cta_group::2, TMA) + eval_loss_kernel"}
 
 
 GAP = dict(d=4096, m=1000, k=5, c=1.0, n_total=1048576)
@@ -553,7 +563,7 @@ def gap_measure(args, rank, world, dist, torch, sd):
                          "communicator (sdcab_eval_sums_sharded_f32_dev), inside the timed region" % (8 + m),
            "timing": "CUDA events around each evaluation, median of %d, max over ranks" % reps,
            "seconds_per_eval": first["seconds_per_eval"],
-           "results": results, "roofline": gap_roofline(first["tflops"] / world),
+           "results": results, "roofline": gap_roofline(first["tflops"] / world, n),
            "e2e": e2e, "cpu_baseline": cpu, "parity_on_sample": parity,
            "setup_primal_from_dual": {"seconds": t_primal, "tflops": 2.0 * d * m * n / t_primal / 1e12}}
     if comm is not None:
@@ -655,7 +665,7 @@ def fit_config(args, rank, world, local_rank):
         "roofline": {"bound": "latency (a chain of N dependent steps per epoch)",
                      "achieved": 1e6 * r["solve_seconds"] / epochs / n, "peak": None,
                      "unit": "us/step", "frac": None, "traffic": None,
-                     "kernel": "fit_chain_kernel + gemm_kernel<double,64,64,8,4,4>"},
+                     "kernel": "fit_chain_kernel + gemm_kernel<double,64,128,8,8,4> (mma.sync f64)"},
         "gpu_launches": int(3 * ((n + 63) // 64) * r["epoch"] + 6 * r["num_evals"]),
         "clocks": clocks,
     }
