@@ -566,6 +566,9 @@ int sdcab_train_f64(const sdcab_dataset* datasets, int64_t num_datasets,
  *                      operand explicitly instead of leaving the truncation to the
  *                      tensor core
  *   "primal_simt", 0|1   1: sdcab_primal_from_dual_f32_dev on the CUDA cores
+ *   "gemm_f64_tile", 0..3   tile of the double-precision score products: 0 by
+ *                      shape, 1 the 128-column block tile, 2 / 3 the pipelined
+ *                      104-column tile with 64 / 128 rows per block
  * Returns SDCAB_ERR_ARG for an unknown name.  Not thread safe. */
 int sdcab_test_set(const char* name, int64_t value);
 

@@ -116,6 +116,13 @@ static int workspace_release_all() {
 
 }  // namespace sdcab
 
+namespace sdcab {
+// tile choice of the double-precision products (declared in gemm_blocked.cuh; tests only)
+static int g_gemm_f64_tile_mode = 0;
+int gemm_f64_tile_mode() { return g_gemm_f64_tile_mode; }
+void set_gemm_f64_tile_mode(int mode) { g_gemm_f64_tile_mode = mode; }
+}  // namespace sdcab
+
 extern "C" {
 
 const char* sdcab_status_string(int status) {

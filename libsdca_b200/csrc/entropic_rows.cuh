@@ -50,19 +50,67 @@ struct GroupResult {
   bool full;
 };
 
-// Moves the largest of cand[u .. total) to position u (one step of a selection
-// sort): phase B orders only as many candidates as its search over U visits, and
-// does so on one lane per row, where phase A would sort all of them on a warp.
-__device__ __forceinline__ float select_next(float* cand, int u, int total) {
-  float best = cand[u];
-  int where = u;
-  for (int j = u + 1; j < total; ++j) {
-    const float c = cand[j];
-    if (c > best) { best = c; where = j; }
+// The k largest entries of a row held NV vectors per lane, in descending order, one per
+// lane (lane r gets the r-th largest, lanes >= k get -inf; k <= 32).  Every lane orders
+// its own entries with a sorting network; then k rounds pop the largest head: one
+// redux.sync.max over the heads, and the first lane that holds it moves its list up.
+// Repeated values are popped one per round, as a sort of the whole row would list them.
+__device__ __forceinline__ void order_pair(float& a, float& b) {
+  const float hi = fmaxf(a, b), lo = fminf(a, b);
+  a = hi; b = lo;
+}
+template <int N>
+__device__ __forceinline__ void sort_desc_in_lane(float (&h)[N]) {
+  if constexpr (N == 8) {
+    // the 19-exchange network for eight inputs
+    order_pair(h[0], h[1]); order_pair(h[2], h[3]); order_pair(h[4], h[5]); order_pair(h[6], h[7]);
+    order_pair(h[0], h[2]); order_pair(h[1], h[3]); order_pair(h[4], h[6]); order_pair(h[5], h[7]);
+    order_pair(h[1], h[2]); order_pair(h[5], h[6]); order_pair(h[0], h[4]); order_pair(h[3], h[7]);
+    order_pair(h[1], h[5]); order_pair(h[2], h[6]);
+    order_pair(h[1], h[4]); order_pair(h[3], h[6]);
+    order_pair(h[2], h[4]); order_pair(h[3], h[5]);
+    order_pair(h[3], h[4]);
+  } else {
+    // bitonic network, N a power of two
+#pragma unroll
+    for (int k = 2; k <= N; k <<= 1) {
+#pragma unroll
+      for (int j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          const int l = i ^ j;
+          if (l > i) {
+            if ((i & k) == 0) order_pair(h[i], h[l]);
+            else order_pair(h[l], h[i]);
+          }
+        }
+      }
+    }
   }
-  cand[where] = cand[u];
-  cand[u] = best;
-  return best;
+}
+template <int NV>
+__device__ __forceinline__ float largest_k_of_row(const RegRow<float, NV>& row, int k, int lane) {
+  constexpr int N = NV * 4;
+  float h[N];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const float* e = reinterpret_cast<const float*>(&row.v[j]);   // vectors past the end hold -inf
+#pragma unroll
+    for (int c = 0; c < 4; ++c) h[j * 4 + c] = e[c];
+  }
+  sort_desc_in_lane<N>(h);
+  float mine = -num<float>::inf();
+  for (int r = 0; r < k; ++r) {
+    const float top = warp_max_fast(h[0]);
+    const unsigned hit = __ballot_sync(kFullMask, h[0] == top);
+    if (lane == r) mine = top;
+    if (lane == __ffs(hit) - 1) {
+#pragma unroll
+      for (int j = 0; j + 1 < N; ++j) h[j] = h[j + 1];
+      h[N - 1] = -num<float>::inf();
+    }
+  }
+  return mine;
 }
 
 // Phase B of the top-k entropy projection for one row: the same closed forms as
@@ -84,19 +132,20 @@ __device__ __forceinline__ GroupResult<R> grouped_topk_entropy(R S, float mxf, i
     out.hi = R(1);
     return out;
   }
-  if (total > 32 || total <= k) {
+  // a row with a NaN has a NaN sum; its candidates are not ordered: the general routine
+  if (total <= k || !(S == S)) {
     out.full = true;
     return out;
   }
-  const int last = min(k - 1, total - 1);
-  const float top = select_next(cand, 0, total);
+  const int last = k - 1;
+  const float top = cand[0];
   R pe_prev = static_cast<R>(exp_(top - mxf));       // sum of the exponentials of U
   R s_prev = static_cast<R>(top);                    // smallest entry of U
   R sum_U = s_prev;
   R zs = 0, log_zs = 0, cur_max = 0;
   int ustar = last;
   for (int u = 1; u <= last; ++u) {
-    const float sf = select_next(cand, u, total);
+    const float sf = cand[u];
     const R s = static_cast<R>(sf);
     const R rest = S - pe_prev;                      // relative to the old maximum
     // a rest that is a small fraction of the whole sum has lost too many digits
@@ -127,19 +176,14 @@ __device__ __forceinline__ GroupResult<R> grouped_topk_entropy(R S, float mxf, i
 
 template <typename R, int PROX, int NV>
 __global__ void __launch_bounds__(kFastThreads, SDCAB_GROUP_MIN_BLOCKS)
-entropic_grouped_kernel(const float* __restrict__ a, float* __restrict__ out, int m, long long n,
+entropic_grouped_kernel(const float* a, float* out, int m, long long n,
                         ProxParams q, int m_pad, int group) {
   constexpr bool kTopkForm = (PROX == kTopkEntropy);
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ float slots_all[kFastThreads / 32][32];
-  __shared__ int counters[kFastThreads / 32];
   __shared__ GroupScratch<R, kTopkForm> sc;
   __shared__ R log_of[33];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps_per_block = kFastThreads / 32;
-  float* slots = slots_all[warp];
-  int* counter = &counters[warp];
-  if (lane == 0) *counter = 0;
   if (threadIdx.x < 33) log_of[threadIdx.x] = threadIdx.x ? log_(static_cast<R>(threadIdx.x)) : R(0);
   __syncthreads();
   float* stage = reinterpret_cast<float*>(smem_raw) + static_cast<size_t>(warp) * m_pad;
@@ -166,12 +210,9 @@ entropic_grouped_kernel(const float* __restrict__ a, float* __restrict__ out, in
       row_max_and_expsum<R, NV>(row, mxf, lm, S);
       int total = 0;
       if (kTopkForm && k > 1 && !(S > certain)) {
-        // the entries that can be among the k + 1 largest, for phase B
-        const float tau = kth_largest_of_lanes(lm, k, lane);
-        const float cut = (tau > -num<float>::inf()) ? nextafterf(tau, -num<float>::inf()) : tau;
-        LaneRow<float> cand;
-        total = compact_candidates(row, cut, slots, counter, lane, cand);
-        if (total <= 32) sc.cand[kTopkForm ? i : 0][lane] = cand.x;
+        // the k largest entries in descending order, for phase B
+        sc.cand[kTopkForm ? i : 0][lane] = largest_k_of_row<NV>(row, k, lane);
+        total = k + 1;
       }
       if (lane == 0) {
         sc.sum_or_t[i] = S;

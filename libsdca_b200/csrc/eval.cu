@@ -666,6 +666,11 @@ int sdcab_test_set(const char* name, int64_t value) {
   if (std::strcmp(name, "gemm_lose_a_tile") == 0) { sdcab::g_test_lose_a_tile = value ? 1 : 0; return SDCAB_OK; }
   if (std::strcmp(name, "gemm_single_cta") == 0) { sdcab::g_test_single_cta = value ? 1 : 0; return SDCAB_OK; }
   if (std::strcmp(name, "gemm_write_hi") == 0) { sdcab::g_test_write_hi = value ? 1 : 0; return SDCAB_OK; }
+  if (std::strcmp(name, "gemm_f64_tile") == 0) {
+    if (value < 0 || value > 3) return SDCAB_ERR_ARG_RANGE;
+    sdcab::set_gemm_f64_tile_mode(static_cast<int>(value));
+    return SDCAB_OK;
+  }
   if (std::strcmp(name, "primal_simt") == 0) { sdcab::primal_test_force_simt(value ? 1 : 0); return SDCAB_OK; }
   return SDCAB_ERR_ARG;
 }

@@ -732,7 +732,7 @@ __device__ __noinline__ Thr<R> full_row_thresholds(const Data* buf, int m, const
 
 template <typename Data, typename R, int PROX, int NV>
 __global__ void __launch_bounds__(kFastThreads, FastMinBlocks<Data, R, PROX>::value)
-fast_rows_kernel(const Data* __restrict__ a, Data* __restrict__ out, int m, long long n,
+fast_rows_kernel(const Data* a, Data* out, int m, long long n,
                  ProxParams q, int m_pad) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ Data slots_all[kFastThreads / 32][32];

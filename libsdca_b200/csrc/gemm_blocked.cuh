@@ -5,6 +5,7 @@
 #pragma once
 
 #include <cstdint>
+#include <type_traits>
 
 #include "common_host.h"
 
@@ -305,11 +306,38 @@ struct GemmExtras {
   int skip_owner = -1;
 };
 
+// Tile choice for doubles (tests only, sdcab_test_set "gemm_f64_tile"): 0 = by shape,
+// 1 = the block tile of gemm_kernel, 2 / 3 = the pipelined 104-column tile with 64 / 128 rows.
+int gemm_f64_tile_mode();
+void set_gemm_f64_tile_mode(int mode);
+
+}  // namespace sdcab
+
+#include "gemm_f64_pipe.cuh"
+
+namespace sdcab {
+
 template <typename T, typename G>
 int launch_gemm_tile(const T* A, const T* B, T* C, int M, int N, int K, long long lda,
                      long long ldb, long long ldc, bool b_kmajor, cudaStream_t stream,
                      const GemmExtras& x) {
   constexpr int V = 16 / sizeof(T);
+  if constexpr (std::is_same<T, double>::value && G::MMA) {
+    // few classes: the 104-column tile wastes a twenty-fifth of the tensor-core work at
+    // m = 100 where the 128-column tile wastes a fifth
+    const int mode = gemm_f64_tile_mode();
+    const bool narrow = (mode == 0) ? (N <= 104 || (N > 128 && (N + 103) / 104 * 104 <= (N + 127) / 128 * 128))
+                                    : mode >= 2;
+    if (narrow) {
+      // 128 rows per block halve the reads of the second operand's tile, which pays when that
+      // tile is the wide one (column index contiguous) and the rows fill the GPU at one block
+      // per SM: 25.3 against 23.7 TFLOP/s at 50 000 x 100 x 50 000; with the contraction index
+      // contiguous in both operands 64 rows and three blocks per SM are faster (27.0 / 25.7)
+      const bool tall = (mode == 0) ? (!b_kmajor && M >= 128 * 148) : mode == 3;
+      if (tall) return f64pipe::launch<128, 13>(A, B, C, M, N, K, lda, ldb, ldc, b_kmajor, stream, x);
+      return f64pipe::launch<64, 13>(A, B, C, M, N, K, lda, ldb, ldc, b_kmajor, stream, x);
+    }
+  }
   auto aligned = [&](const void* p, long long ld) {
     return ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && ld % V == 0) ? 1 : 0;
   };

@@ -75,6 +75,36 @@ def test_tensor_core_and_cuda_core_gemm_agree(cuda_lib):
     assert np.abs(outs[0] - outs[1]).max() <= 1e-5 * np.abs(outs[1]).max()
 
 
+def test_double_precision_tiles_agree(cuda_lib):
+    """The three tiles of the double-precision product (the 128-column block tile, the
+    pipelined 104-column tile with 64 and with 128 rows per block) on shapes with ragged
+    edges in every direction, odd leading dimensions (8-byte copies) and both operand
+    forms: each within the dot-product bound of the exact result, and the forced tiles
+    really are different kernels from one another where the shape lets them differ."""
+    from libsdca_b200 import binding as b
+    rng = np.random.default_rng(17)
+    shapes = [(333, 50, 100), (130, 17, 7), (64, 16, 104), (700, 129, 105), (257, 1000, 99),
+              (19000, 40, 100), (45, 3, 3)]
+    eps = np.finfo(np.float64).eps
+    try:
+        for n, d, m in shapes:
+            X = rng.standard_normal((n, d))
+            W = rng.standard_normal((m, d))
+            A = rng.standard_normal((d, m))
+            for kw, exact, mag in ((dict(W=W), X @ W.T, np.abs(X) @ np.abs(W).T),
+                                   (dict(A=A), X @ A, np.abs(X) @ np.abs(A))):
+                outs = []
+                for mode in (1, 2, 3, 0):
+                    b.test_set("gemm_f64_tile", mode)
+                    outs.append(scores(cuda_lib, X, **kw))
+                    assert (np.abs(outs[-1] - exact) <= (16 + 2 * np.sqrt(d)) * eps * mag + 1e-300).all(), \
+                        (n, d, m, mode)
+                # the two pipelined tiles add the same terms in the same order
+                assert np.array_equal(outs[1], outs[2]), (n, d, m)
+    finally:
+        b.test_set("gemm_f64_tile", 0)
+
+
 def test_tensor_core_variants_agree(cuda_lib):
     """The paired-CTA kernel leaves the truncation of an operand to TF32 to the tensor
     core; with the head written explicitly (test switch) the result must be the same bit
