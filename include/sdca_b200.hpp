@@ -133,6 +133,14 @@ inline void prox_two_simplex(std::ptrdiff_t dim, std::ptrdiff_t p, Data* first, 
   sdcab_prox_opts o = detail::defaults(); o.p = p; o.rhs = rhs;
   detail::run<Result>("two_simplex", dim, first, last, o);
 }
+// include/sdca/prox/two_simplex_sort.h:177-189 (dim, p, first, last, aux, rhs): the sort-based
+// routine, a different function from two_simplex where a block ends up empty
+template <typename Result = double, typename Data>
+inline void prox_two_simplex_sort(std::ptrdiff_t dim, std::ptrdiff_t p, Data* first, Data* last, Data*,
+                                  Result rhs = 1) {
+  sdcab_prox_opts o = detail::defaults(); o.p = p; o.rhs = rhs;
+  detail::run<Result>("two_simplex_sort", dim, first, last, o);
+}
 // apply(dim, first, last, lambert_w_exp_map<Data>()): include/sdca/prox/proxdef.h:386-400
 template <typename Data>
 inline void apply_lambert_w_exp(std::ptrdiff_t dim, Data* first, Data* last) {

@@ -333,7 +333,14 @@ int launch_gemm_tile(const T* A, const T* B, T* C, int M, int N, int K, long lon
       // tile is the wide one (column index contiguous) and the rows fill the GPU at one block
       // per SM: 25.3 against 23.7 TFLOP/s at 50 000 x 100 x 50 000; with the contraction index
       // contiguous in both operands 64 rows and three blocks per SM are faster (27.0 / 25.7)
-      const bool tall = (mode == 0) ? (!b_kmajor && M >= 128 * 148) : mode == 3;
+      // ... unless the 128-row blocks fill the GPU's last wave worse: compare the rows the
+      // busiest SM works through (ncu: 160 such blocks on 148 SMs ran at 44 % of elapsed cycles
+      // with the FP64 tensor pipe active, 81 % while an SM had a block)
+      DeviceInfo info;
+      const int sms = (get_device_info(&info) == SDCAB_OK && info.sm_count > 0) ? info.sm_count : 148;
+      const long long load_tall = ((M + 127) / 128 + sms - 1) / sms * 128LL;
+      const long long load_short = ((M + 63) / 64 + sms - 1) / sms * 64LL;
+      const bool tall = (mode == 0) ? (!b_kmajor && 100 * load_tall <= 107 * load_short) : mode == 3;
       if (tall) return f64pipe::launch<128, 13>(A, B, C, M, N, K, lda, ldb, ldc, b_kmajor, stream, x);
       return f64pipe::launch<64, 13>(A, B, C, M, N, K, lda, ldb, ldc, b_kmajor, stream, x);
     }

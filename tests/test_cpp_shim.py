@@ -50,11 +50,13 @@ int main(int argc, char** argv) {
     sdca::b200::prox_topk_cone<float>(mp, a2.data(), a2.data() + a2.size(), aux.data(), 3);
     write_all((dir + "/out_topk_cone.bin").c_str(), a2);
     std::vector<double> b = read_all<double>((dir + "/rows_f64.bin").c_str());
-    std::vector<double> b2 = b, b3 = b;
+    std::vector<double> b2 = b, b3 = b, b4 = b;
     sdca::b200::prox_knapsack_eq(mp, b.data(), b.data() + b.size(), b.data());
     write_all((dir + "/out_knapsack_eq.bin").c_str(), b);
     sdca::b200::prox_two_simplex(mp, 3, b2.data(), b2.data() + b2.size(), b2.data(), 1.0);
     write_all((dir + "/out_two_simplex.bin").c_str(), b2);
+    sdca::b200::prox_two_simplex_sort(mp, 3, b4.data(), b4.data() + b4.size(), b4.data(), 1.0);
+    write_all((dir + "/out_two_simplex_sort.bin").c_str(), b4);
     sdca::b200::apply_lambert_w_exp(mp, b3.data(), b3.data() + b3.size());
     write_all((dir + "/out_lambert.bin").c_str(), b3);
 
@@ -149,6 +151,7 @@ def test_shim_program_matches_reference(ref, cuda_lib):
             "topk_cone": load("out_topk_cone", np.float32).reshape(rows, mp),
             "knapsack_eq": load("out_knapsack_eq", np.float64).reshape(rows, mp),
             "two_simplex": load("out_two_simplex", np.float64).reshape(rows, mp),
+            "two_simplex_sort": load("out_two_simplex_sort", np.float64).reshape(rows, mp),
             "lambert": load("out_lambert", np.float64).reshape(rows, mp),
         }
         out_eval = load("out_eval", np.float64)
@@ -160,6 +163,12 @@ def test_shim_program_matches_reference(ref, cuda_lib):
     scale64 = np.maximum(1, np.abs(rows64).max(axis=1, keepdims=True))
     assert (np.abs(got["knapsack_eq"] - ref.prox("knapsack_eq", rows64)) <= 1e-12 * scale64).all()
     assert (np.abs(got["two_simplex"] - ref.prox("two_simplex", rows64, p=3, rhs=1.0)) <= 1e-12 * scale64).all()
+    # rows on which the reference's sort-based walk stays inside its arrays
+    from tests.util import two_simplex_sort_defined
+    ok = two_simplex_sort_defined(ref, rows64, p=3, rhs=1.0)
+    assert ok.sum() >= rows // 2
+    want_s = ref.prox("two_simplex_sort", rows64[ok], p=3, rhs=1.0)
+    assert (np.abs(got["two_simplex_sort"][ok] - want_s) <= 1e-12 * scale64[ok]).all()
     want_l = ref.lambert_w_exp(rows64)
     assert (np.abs(got["lambert"] - want_l) <= 1e-12 * np.maximum(1, np.abs(want_l))).all()
     r = ref.evaluate("l2_topk_hinge_smooth", X, A, labels, W=W, c=1.0, gamma=1.0, k=1)
