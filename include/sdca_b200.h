@@ -566,6 +566,8 @@ int sdcab_train_f64(const sdcab_dataset* datasets, int64_t num_datasets,
  *                      operand explicitly instead of leaving the truncation to the
  *                      tensor core
  *   "primal_simt", 0|1   1: sdcab_primal_from_dual_f32_dev on the CUDA cores
+ *   "loss_general", 0|1   1: the general loss kernel (score rows in shared memory)
+ *                      where the register-row kernel of the top-k hinge losses applies
  *   "gemm_f64_tile", 0..3   tile of the double-precision score products: 0 by
  *                      shape, 1 the 128-column block tile, 2 / 3 the pipelined
  *                      104-column tile with 64 / 128 rows per block

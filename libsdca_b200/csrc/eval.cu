@@ -18,6 +18,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 #include <vector>
 
 #include "common_host.h"
@@ -121,6 +122,10 @@ eval_loss_kernel(LossArgs g, const Data* __restrict__ scores, const Data* __rest
   for (int i = threadIdx.x; i < kHistLocal && i < m; i += kLossThreads)
     if (local_hist[i]) atomicAdd(&hist[i], static_cast<unsigned long long>(local_hist[i]));
 }
+
+}  // namespace sdcab
+#include "loss_rows.cuh"
+namespace sdcab {
 
 // sums[0..4] += block partials.  One block of 256 threads: thread t adds the
 // partials of blocks t, t + 256, ... in order, then a fixed tree combines the
@@ -236,6 +241,7 @@ static int g_test_force_simt = 0;
 static int g_test_lose_a_tile = 0;
 static int g_test_single_cta = 0;   // the one-CTA tensor-core kernel instead of the paired one
 static int g_test_write_hi = 0;     // the paired kernel writes the TF32 head explicitly
+static int g_test_loss_general = 0; // the general loss kernel where the register-row one applies
 
 // Chunks are bounded so that the product's grid (one row of thread blocks per 128
 // examples in grid.y for the CUDA-core kernel) stays inside the launch limits.
@@ -384,8 +390,19 @@ int eval_sums_dev(const sdcab_objective* obj, const sdcab_problem* p, double* su
     const int blocks = static_cast<int>(std::max<long long>(
         1, std::min<long long>(L.max_blocks, (count + warps - 1) / warps)));
     const Data* A = static_cast<const Data*>(p->a);
-    if (fl) kf<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
-    else kd<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+    bool launched = false;
+    if constexpr (std::is_same<Data, float>::value) {
+      if (!g_test_loss_general && loss_rows_usable(g, scores, A)) {
+        rc = fl ? launch_loss_rows<float>(g, scores, A, partials, hist, blocks, info.smem_optin, stream)
+                : launch_loss_rows<double>(g, scores, A, partials, hist, blocks, info.smem_optin, stream);
+        if (rc) return rc;
+        launched = true;
+      }
+    }
+    if (!launched) {
+      if (fl) kf<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+      else kd<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+    }
     combine_partials_kernel<<<1, 256, 0, stream>>>(partials, blocks, sums);
   }
   hist_to_sums_kernel<<<std::max(1, static_cast<int>((m + 255) / 256)), 256, 0, stream>>>(
@@ -639,8 +656,19 @@ int eval_sums_fixed_scratch(const sdcab_objective* obj, const sdcab_problem* p, 
     const int blocks = static_cast<int>(std::max<long long>(
         1, std::min<long long>(max_blocks, (count + warps - 1) / warps)));
     const Data* A = static_cast<const Data*>(p->a);
-    if (fl) kf<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
-    else kd<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+    bool launched = false;
+    if constexpr (std::is_same<Data, float>::value) {
+      if (!g_test_loss_general && loss_rows_usable(g, scores, A)) {
+        rc = fl ? launch_loss_rows<float>(g, scores, A, partials, hist, blocks, info.smem_optin, stream)
+                : launch_loss_rows<double>(g, scores, A, partials, hist, blocks, info.smem_optin, stream);
+        if (rc) return rc;
+        launched = true;
+      }
+    }
+    if (!launched) {
+      if (fl) kf<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+      else kd<<<blocks, kLossThreads, smem, stream>>>(g, scores, A, partials, hist);
+    }
     combine_partials_kernel<<<1, 256, 0, stream>>>(partials, blocks, sums);
   }
   hist_to_sums_kernel<<<std::max(1, static_cast<int>((m + 255) / 256)), 256, 0, stream>>>(
@@ -666,6 +694,7 @@ int sdcab_test_set(const char* name, int64_t value) {
   if (std::strcmp(name, "gemm_lose_a_tile") == 0) { sdcab::g_test_lose_a_tile = value ? 1 : 0; return SDCAB_OK; }
   if (std::strcmp(name, "gemm_single_cta") == 0) { sdcab::g_test_single_cta = value ? 1 : 0; return SDCAB_OK; }
   if (std::strcmp(name, "gemm_write_hi") == 0) { sdcab::g_test_write_hi = value ? 1 : 0; return SDCAB_OK; }
+  if (std::strcmp(name, "loss_general") == 0) { sdcab::g_test_loss_general = value ? 1 : 0; return SDCAB_OK; }
   if (std::strcmp(name, "gemm_f64_tile") == 0) {
     if (value < 0 || value > 3) return SDCAB_ERR_ARG_RANGE;
     sdcab::set_gemm_f64_tile_mode(static_cast<int>(value));

@@ -232,7 +232,7 @@ __device__ __forceinline__ double round_down(float v, double) { return static_ca
 // divide by small counts, and a multiplication by the tabulated reciprocal (one
 // rounding more than the division, far inside every tolerance) is a single
 // instruction where the division is a routine of thirty.
-__constant__ double kReciprocal[33] = {
+static __constant__ double kReciprocal[33] = {
     0.0, 1.0, 1.0 / 2, 1.0 / 3, 1.0 / 4, 1.0 / 5, 1.0 / 6, 1.0 / 7, 1.0 / 8, 1.0 / 9, 1.0 / 10,
     1.0 / 11, 1.0 / 12, 1.0 / 13, 1.0 / 14, 1.0 / 15, 1.0 / 16, 1.0 / 17, 1.0 / 18, 1.0 / 19, 1.0 / 20,
     1.0 / 21, 1.0 / 22, 1.0 / 23, 1.0 / 24, 1.0 / 25, 1.0 / 26, 1.0 / 27, 1.0 / 28, 1.0 / 29, 1.0 / 30,

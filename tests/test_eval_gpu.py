@@ -234,3 +234,38 @@ def test_host_forms_reject_bad_labels(cuda_lib):
         with pytest.raises(cuda_lib.SdcabError) as e:
             cuda_lib.evaluate("mlsvm", X, l2, A=A, W=W, offsets=o2)
         assert e.value.status == -5, mutate
+
+
+@pytest.mark.parametrize("objective", ["l2_hinge_topk", "l2_topk_hinge", "l2_hinge_topk_smooth"])
+def test_register_row_loss_kernel_matches_reference_and_general_kernel(ref, cuda_lib, objective):
+    """Float features with 64 to 1024 classes in whole 16-byte vectors take the loss
+    kernel that keeps the score row in registers.  It must agree with the reference term
+    by term, and with the library's general loss kernel (test switch) to rounding; the two
+    are different kernels, so at least one shape must differ in the last bits."""
+    from libsdca_b200 import binding as b
+    rng = np.random.default_rng(stable_seed("loss-rows", objective))
+    differ = False
+    try:
+        for n, d, m, k, gamma in ((257, 32, 64, 1, 1.0), (130, 48, 100, 3, 0.3), (200, 40, 260, 8, 2.0),
+                                  (300, 64, 1000, 5, 1.0), (90, 64, 1024, 5, 0.05), (64, 32, 516, 2, 10.0)):
+            X, labels, _ = random_problem(rng, n, d, m, np.float32, False)
+            A = np.zeros((n, m), dtype=np.float32); W = np.zeros((m, d), dtype=np.float32)
+            kw = dict(c=1.5, gamma=gamma, k=k)
+            ref.fit(objective, X, A, labels, W=W, max_epoch=2, eval_epoch=10, **kw)
+            r = ref.evaluate(objective, X, A.copy(), labels, W=W, **kw)
+            reg_tol = float_sum_tol(np.float32, m * d)
+            for precision in ("double", "single"):
+                b.test_set("loss_general", 0)
+                g = gpu_eval(cuda_lib, objective, X, labels, A=A, W=W, precision=precision, **kw)
+                b.test_set("loss_general", 1)
+                q = gpu_eval(cuda_lib, objective, X, labels, A=A, W=W, precision=precision, **kw)
+                tol = 1e-5 if precision == "double" else 1e-4
+                compare(g, r, tol, (objective, n, d, m, precision, "register rows"), reg_tol)
+                compare(g, q, 1e-9 if precision == "double" else 1e-4,
+                        (objective, n, d, m, precision, "against the general kernel"))
+                assert np.array_equal(g["accuracy"], q["accuracy"])
+                differ = differ or g["primal_loss"] != q["primal_loss"] or g["dual_loss"] != q["dual_loss"]
+    finally:
+        b.test_set("loss_general", 0)
+    if objective == "l2_hinge_topk_smooth":
+        assert differ
