@@ -45,6 +45,22 @@ PROX_CONFIGS = {
             ops=(("topk_entropy", dict(k=1)), ("topk_entropy", dict(k=10)),
                  ("entropy", dict(hi=1.0, rhs=1.0)), ("lambert_w_exp", dict())),
             name="config 3: top-k entropy k=1,10, entropy, Lambert W(exp x), 1048576 x 200 float32"),
+    # Sweeps over the operators of matsdca_prox that the five configurations do not time
+    # (include/sdca/prox/*.h): not configurations of the benchmark definition, same shapes and
+    # generators as configs 2 and 3 so that the figures sit beside theirs.
+    6: dict(rows=131072, m=1000, dtype="float32", gen="topk_rows",
+            ops=(("knapsack", dict()), ("knapsack_le", dict()), ("knapsack_le_biased", dict(rho=1.0)),
+                 ("topk_simplex", dict(k=K_TOP)), ("topk_simplex_biased", dict(k=K_TOP, rho=1.0)),
+                 ("topk_cone", dict(k=K_TOP)), ("topk_cone_biased", dict(k=K_TOP, rho=1.0)),
+                 ("two_simplex", dict(p=500)), ("two_simplex_sort", dict(p=500))),
+            cpu_rows=16384, no_cpu=("two_simplex_sort",),
+            name="operator sweep, Euclidean projections: 131072 x 1000 float32, N(0,1) with ties"),
+    7: dict(rows=262144, m=200, dtype="float32", gen="entropy_rows",
+            ops=(("entropy", dict(hi=1.0, rhs=1.0)), ("topk_entropy", dict(k=K_TOP)),
+                 ("entropy_norm", dict(hi=1.0, rhs=1.0)),
+                 ("topk_entropy_biased", dict(k=K_TOP, alpha=1.0))),
+            cpu_rows=16384, no_cpu=(),
+            name="operator sweep, entropic projections: 262144 x 200 float32, N(0,4)"),
 }
 
 
@@ -250,9 +266,13 @@ def other_prox_config(args, rank, world, local_rank):
     cpu = None
     if not args.no_cpu_baseline and refapi.have_reference():
         threads = max(1, min(os.cpu_count() or 1, 64))
-        sample = host[: min(rows, 65536)]
+        sample = host[: min(rows, cfg.get("cpu_rows", 65536))]
         cpu = {}
         for name, kw in cfg["ops"]:
+            if name in cfg.get("no_cpu", ()):
+                # the reference's sort-based walk reads past its arrays on some rows
+                # (prox/two_simplex_sort.h:84-97): not run on unchecked rows
+                continue
             t0 = time.perf_counter()
             refapi.reference().prox(name, sample, nthreads=threads, **kw)
             label = name + ("(k=%d)" % kw["k"] if "k" in kw else "")
@@ -719,7 +739,7 @@ def main():
     ap.add_argument("--max-epoch", type=int, default=100, help="config 5: epoch limit")
     ap.add_argument("--cpu-fit-examples", type=int, default=4000,
                     help="config 5: size of the problem the reference's solver is timed on")
-    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5, 6, 7],
                     help="benchmark configuration; 2 (default) is the headline")
     ap.add_argument("--no-gap", action="store_true",
                     help="leave the duality-gap evaluation (config 4) out of the default line")

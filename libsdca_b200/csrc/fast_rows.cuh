@@ -26,13 +26,24 @@ constexpr int kFastThreads = 128;
 // projections read the row a second time for the final map instead (see the
 // kernel), so their search runs in 64-72 registers and eight (seven for the
 // simplex with double thresholds) blocks fit; measured fastest at these values.
-template <typename Data, typename R, int PROX> struct FastMinBlocks {
+// The knapsack family (knapsack_eq / _le / _le_biased) does the same once a lane holds four
+// vectors or more; with two vectors per lane (config 1's 100 doubles) keeping the row was
+// measured faster.
+template <int PROX, int NV> struct KnapsackStaged {
+  static constexpr bool value = (PROX == kKnapsackEq || PROX == kKnapsackLe || PROX == kKnapsackLeBiased) &&
+                                NV >= 4;
+};
+template <typename Data, typename R, int PROX, int NV> struct FastMinBlocks {
   static constexpr bool kTopk = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased ||
                                  PROX == kTopkCone || PROX == kTopkConeBiased);
   static constexpr bool kSimplex = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased);
   static constexpr bool kDouble = sizeof(R) == 8;
   static constexpr bool kEntropic = sizeof(Data) == 4 && (PROX == kTopkEntropy || PROX == kEntropy);
-  static constexpr int value = kTopk ? ((kDouble && kSimplex) ? 7 : 8) : (kEntropic ? 8 : (kDouble ? 5 : 6));
+  static constexpr bool kKnapStaged = KnapsackStaged<PROX, NV>::value;
+  // the simplex projection of short rows (config 1's 100 doubles) fits eight blocks as well
+  static constexpr bool kShortSimplex = (PROX == kKnapsackEq) && NV == 2;
+  static constexpr int value = kTopk ? ((kDouble && kSimplex) ? 7 : 8)
+                                     : ((kEntropic || kKnapStaged || kShortSimplex) ? 8 : (kDouble ? 5 : 6));
 };
 
 template <typename Data> struct VecOf;
@@ -565,10 +576,29 @@ __device__ __forceinline__ FastStatus fast_knapsack_eq(const RegRow<Data, NV>& r
   Data lm = -num<Data>::inf();
   row.for_each([&](Data x, int) { lm = max_(lm, x); });
   // a lower bound of the maximum through the one-instruction float reduction
-  const float below = warp_max_fast(round_down(lm, float()));
+  float cur = round_down(lm, float());
+  const float below = warp_max_fast(cur);
   if (!(below > -num<float>::inf())) return kFastNeedsFullRow;
   const R below_r = static_cast<R>(below);
-  const Data cut = round_down(below_r - rhs - (abs_(below_r) + rhs) * num<R>::eps() * 4, Data());
+  // t is the largest of the t_j, and any j entries of the row bound the sum of its j largest
+  // from below: the largest lane maxima (each an entry of its own) give t >= (their sum - rhs) / j.
+  // For long rows that cut is far tighter than max - rhs (N(0,1), m = 1000: about 4 candidates
+  // instead of 30, which would overflow the 32 slots on a quarter of the rows).
+  R bound = below_r - rhs;
+  if (NV >= 4) {
+    R sum = below_r;
+    float top = below;
+#pragma unroll
+    for (int j = 2; j <= 4; ++j) {
+      const unsigned hit = __ballot_sync(kFullMask, cur == top);
+      if (lane == __ffs(hit) - 1) cur = -num<float>::inf();
+      top = warp_max_fast(cur);
+      if (!(top > -num<float>::inf())) break;
+      sum += static_cast<R>(top);
+      bound = max_(bound, over_count(sum - rhs, j));
+    }
+  }
+  const Data cut = round_down(bound - (abs_(below_r) + rhs) * num<R>::eps() * 8, Data());
   LaneRow<Data> cand;
   const int total = compact_candidates(row, cut, slots, counter, lane, cand);
   if (total > 32 || total < 1) return kFastNeedsFullRow;
@@ -593,6 +623,45 @@ __device__ __forceinline__ FastStatus fast_knapsack_eq(const RegRow<Data, NV>& r
   if (__any_sync(kFullMask, mine && v - t > hi)) return kFastNeedsFullRow;
   thr = make_thr(t, R(0), hi, 0, size, hi + t, t);
   return kFastDone;
+}
+
+// knapsack_le with lo = 0 (include/sdca/prox/knapsack_le.h:17-44): the sum of the row clipped
+// to [0, hi] decides between t = 0 and the equality-constrained projection.
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ FastStatus fast_knapsack_le(const RegRow<Data, NV>& row, R hi, R rhs,
+                                                       Data* slots, int* counter, int lane,
+                                                       Thr<R>& thr) {
+  const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
+  int n_hi = 0, n_mid = 0;
+  R sum_mid = 0;
+  row.for_each([&](Data xd, int) {
+    const R x = static_cast<R>(xd);
+    if (x >= hi) ++n_hi;
+    else if (x > R(0)) { ++n_mid; sum_mid += x; }
+  });
+  n_hi = warp_sum(n_hi); n_mid = warp_sum(n_mid); sum_mid = warp_sum(sum_mid);
+  const R s = sum_mid + hi * static_cast<R>(n_hi);
+  if (s > rhs + eps) return fast_knapsack_eq<R>(row, hi, rhs, slots, counter, lane, thr);
+  thr = make_thr(R(0), R(0), hi, n_hi, n_mid, hi, R(0));
+  return kFastDone;
+}
+
+// The three knapsack operators with lo = 0 on a register row.  knapsack_le_biased
+// (include/sdca/prox/knapsack_le_biased.h:89-129): rho = 0 is knapsack_le; otherwise the
+// equality-constrained projection is the answer when its t >= rho * rhs, and the search over
+// (U, M) -- the general routine -- is needed only below that.
+template <typename R, int PROX, typename Data, int NV>
+__device__ __forceinline__ FastStatus fast_knapsack_family(const RegRow<Data, NV>& row,
+                                                           const ProxParams& q, Data* slots,
+                                                           int* counter, int lane, Thr<R>& thr) {
+  if (!(q.lo == 0 && q.hi > 0 && q.rhs > 0) || q.accurate) return kFastNeedsFullRow;
+  const R hi = static_cast<R>(q.hi), rhs = static_cast<R>(q.rhs);
+  if (PROX == kKnapsackEq) return fast_knapsack_eq<R>(row, hi, rhs, slots, counter, lane, thr);
+  if (PROX == kKnapsackLe || q.rho == 0) return fast_knapsack_le<R>(row, hi, rhs, slots, counter, lane, thr);
+  const R rho = static_cast<R>(q.rho);
+  if (fast_knapsack_eq<R>(row, hi, rhs, slots, counter, lane, thr) != kFastDone) return kFastNeedsFullRow;
+  const R eps = num<R>::eps() * max_(R(1), abs_(rhs));
+  return (thr.t >= rho * rhs - eps) ? kFastDone : kFastNeedsFullRow;
 }
 
 // ---- entropic projections of float rows --------------------------------------
@@ -731,7 +800,7 @@ __device__ __noinline__ Thr<R> full_row_thresholds(const Data* buf, int m, const
 }
 
 template <typename Data, typename R, int PROX, int NV>
-__global__ void __launch_bounds__(kFastThreads, FastMinBlocks<Data, R, PROX>::value)
+__global__ void __launch_bounds__(kFastThreads, FastMinBlocks<Data, R, PROX, NV>::value)
 fast_rows_kernel(const Data* a, Data* out, int m, long long n,
                  ProxParams q, int m_pad) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -748,8 +817,9 @@ fast_rows_kernel(const Data* a, Data* out, int m, long long n,
   constexpr bool kTopk = (PROX == kTopkSimplex || PROX == kTopkSimplexBiased ||
                           PROX == kTopkCone || PROX == kTopkConeBiased);
   // operators with a fast path that can decline a row
-  constexpr bool kStaged = kTopk || (std::is_same<Data, float>::value &&
-                                     (PROX == kTopkEntropy || PROX == kEntropy));
+  constexpr bool kKnap = (PROX == kKnapsackEq || PROX == kKnapsackLe || PROX == kKnapsackLeBiased);
+  constexpr bool kStaged = kTopk || KnapsackStaged<PROX, NV>::value ||
+                           (std::is_same<Data, float>::value && (PROX == kTopkEntropy || PROX == kEntropy));
   const R rho_used = (PROX == kTopkSimplexBiased || PROX == kTopkConeBiased) ? static_cast<R>(q.rho) : R(0);
   const TopkConsts<R> tc(q.k > 0 ? q.k : 1, static_cast<R>(q.rhs), rho_used);
   for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + warp; r < n;
@@ -768,6 +838,7 @@ fast_rows_kernel(const Data* a, Data* out, int m, long long n,
     } else if (PROX == kTopkCone || PROX == kTopkConeBiased) {
       st = fast_topk_cone<R>(row, q.k, rho_used, tc, slots, counter, sorted_all[warp], lane, thr);
     }
+    if (kKnap && kStaged) st = fast_knapsack_family<R, PROX>(row, q, slots, counter, lane, thr);
     if (std::is_same<Data, float>::value && PROX == kTopkEntropy) {
       st = fast_topk_entropy<R, NV>(reinterpret_cast<const RegRow<float, NV>&>(row), q.k,
                                     reinterpret_cast<float*>(slots), counter, lane, thr);
@@ -785,9 +856,7 @@ fast_rows_kernel(const Data* a, Data* out, int m, long long n,
       }
     } else {
       bool done = false;
-      if (PROX == kKnapsackEq && q.lo == 0 && q.hi > 0 && q.rhs > 0)
-        done = fast_knapsack_eq<R>(row, static_cast<R>(q.hi), static_cast<R>(q.rhs), slots, counter,
-                                   lane, thr) == kFastDone;
+      if (kKnap) done = fast_knapsack_family<R, PROX>(row, q, slots, counter, lane, thr) == kFastDone;
       if (!done) thr = compute_thresholds<R>(PROX, row, q);
     }
     Applier<Data> f(thr, prox_map(PROX), q.alpha);
@@ -813,7 +882,8 @@ int launch_fast(const Data* a, Data* out, int m, long long n, const ProxParams& 
                           PROX == kTopkCone || PROX == kTopkConeBiased) ||
                          (std::is_same<Data, float>::value && (PROX == kTopkEntropy || PROX == kEntropy));
   const int m_pad = (m + 15) & ~15;
-  const size_t smem = kTopk ? static_cast<size_t>(kFastThreads / 32) * m_pad * sizeof(Data) : 0;
+  const size_t smem = (kTopk || KnapsackStaged<PROX, NV>::value)
+                          ? static_cast<size_t>(kFastThreads / 32) * m_pad * sizeof(Data) : 0;
   int per_sm = 0;
   SDCAB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFastThreads, smem));
   if (per_sm < 1) per_sm = 1;
@@ -852,6 +922,7 @@ int launch_fast_rows(int prox, const Data* a, Data* out, int m, long long n,
     case kTopkConeBiased: return launch_fast_nv<Data, R, kTopkConeBiased>(a, out, m, n, q, stream);
     case kKnapsackEq: return launch_fast_nv<Data, R, kKnapsackEq>(a, out, m, n, q, stream);
     case kKnapsackLe: return launch_fast_nv<Data, R, kKnapsackLe>(a, out, m, n, q, stream);
+    case kKnapsackLeBiased: return launch_fast_nv<Data, R, kKnapsackLeBiased>(a, out, m, n, q, stream);
     case kEntropy: return launch_fast_nv<Data, R, kEntropy>(a, out, m, n, q, stream);
     case kTopkEntropy: return launch_fast_nv<Data, R, kTopkEntropy>(a, out, m, n, q, stream);
     default: break;
