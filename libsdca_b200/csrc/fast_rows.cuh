@@ -559,6 +559,141 @@ __device__ __forceinline__ FastStatus fast_topk_cone(const RegRow<Data, NV>& row
   return kFastNeedsFullRow;
 }
 
+// Top-k cone with rho > 0 (include/sdca/prox/topk_cone_biased.h:8-113).  For a set U of the
+// u largest entries the pair (M, t) is the root of
+//     F_u(t) = up * sum_{i not in U} (a_i - t)_+  -  (k - u)^2 t  -  (k - u) sum_U,   up = u + rho k^2,
+// decreasing in t, and the search accepts the first u whose (t, hi) passes the reference's
+// inequalities.  With rho > 0 every root is well above the bulk of the row, so the search
+// needs only the entries above a cut below all the roots.  Such a cut comes from a few
+// entries of the row: with v_1 >= v_2 >= ... the J largest lane maxima (each an entry of its
+// own), at most u of them lie in U and sum_U <= u v_1, hence
+//     F_u(t) >= up * sum_{i = u+1..J} (v_i - t)_+  -  (k - u)^2 t  -  (k - u) u v_1,
+// whose root L_u bounds the root of F_u from below; lane u solves its own L_u.  The entries
+// above min_u L_u (and at least the k + 1 largest) are compacted and sorted, and lane u then
+// runs the Newton iteration of the general routine on the sorted candidates -- a count and a
+// prefix-sum look-up per step instead of a pass over the row -- followed by the acceptance
+// test; the smallest u that passes wins, as in the sequential search.
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ FastStatus fast_topk_cone_biased(const RegRow<Data, NV>& row, int k, R rho,
+                                                            const TopkConsts<R>& tc, Data* slots,
+                                                            int* counter, R* sorted, int lane,
+                                                            Thr<R>& thr) {
+  const int m = row.size();
+  if (k > 8 || m <= 32 || !(rho > 0)) return kFastNeedsFullRow;
+  const R K = tc.K, rho_k2 = tc.rho_k2;
+  const R eps = 16 * num<R>::eps();
+  const int J = k + 4;
+  // the J largest lane maxima, in descending order, into shared memory
+  {
+    Data lmd = -num<Data>::inf();
+    row.for_each([&](Data x, int) { lmd = max_(lmd, x); });
+    float cur = round_down(lmd, float());
+    float top = warp_max_fast(cur);
+    if (!(top > -num<float>::inf())) return kFastNeedsFullRow;
+    for (int j = 0; j < J; ++j) {
+      if (lane == 0) sorted[j] = static_cast<R>(top);
+      const unsigned hit = __ballot_sync(kFullMask, cur == top);
+      if (lane == __ffs(hit) - 1) cur = -num<float>::inf();
+      top = warp_max_fast(cur);
+    }
+    __syncwarp();
+  }
+  // lane u < k: the root L_u of the lower bound of F_u
+  R bound = num<R>::inf();
+  const R v1 = sorted[0];
+  if (lane < k) {
+    const int u = lane;
+    const R kmu = K - static_cast<R>(u), up = static_cast<R>(u) + rho_k2;
+    const R fixed = kmu * static_cast<R>(u) * v1;
+    int cnt = 0; R sum = 0;
+    for (int i = u; i < J; ++i) {
+      const R v = sorted[i];
+      if (v > -num<R>::inf()) { ++cnt; sum += v; }
+    }
+    R t = (up * sum - fixed) / (kmu * kmu + up * static_cast<R>(cnt));
+    // the values above t are a prefix of v_{u+1}, v_{u+2}, ...: drop from the end
+    while (cnt > 0 && !(sorted[u + cnt - 1] > t)) {
+      sum -= sorted[u + cnt - 1];
+      --cnt;
+      t = (up * sum - fixed) / (kmu * kmu + up * static_cast<R>(cnt));
+    }
+    bound = t;
+  }
+  // the k + 1 largest entries have to be candidates as well
+  if (lane == k) bound = sorted[k];
+  bound = warp_min(bound);
+  __syncwarp();
+  if (!(bound > -num<R>::inf())) return kFastNeedsFullRow;
+  const Data cut = round_down(bound - (abs_(bound) + abs_(v1) + R(1)) * eps, Data());
+  LaneRow<Data> cand;
+  const int total = compact_candidates(row, cut, slots, counter, lane, cand);
+  if (total > 32 || total <= k) return kFastNeedsFullRow;
+  const Sorted<R> c = sort_candidates<R>(cand, total, lane);
+  if (sorted_special_cases<R>(c, m, k, tc.inv_div, thr) != kProjGeneral) return kFastDone;
+  R* sm_s = sorted;
+  R* sm_P = sorted + 32;
+  sm_s[lane] = c.s;
+  sm_P[lane] = c.P;
+  __syncwarp();
+  const int n = total;
+  bool pass = false;
+  R t_u = 0, hi_u = 0, minU_u = num<R>::inf();
+  int j_u = 0;
+  if (lane <= k) {
+    const int u = lane;
+    const R kmu = K - static_cast<R>(u), up = static_cast<R>(u) + rho_k2;
+    const R sum_U = (u > 0) ? sm_P[u - 1] : R(0);
+    const R min_U = (u > 0) ? sm_s[u - 1] : num<R>::inf();
+    const R s_u = sm_s[u];                 // the largest entry outside U (n > k >= u)
+    int j; R sum_M;
+    bool valid = true;
+    if (u == k) {
+      if (up > 0) { j = 1; sum_M = s_u; } else { j = 0; sum_M = 0; valid = false; }
+    } else {
+      // Newton steps from the left, starting on the piece of the cut
+      j = n - u; sum_M = sm_P[n - 1] - sum_U;
+      for (int it = 0; it <= 32; ++it) {
+        const R D = kmu * kmu + up * static_cast<R>(j);
+        const R t = (up * sum_M - kmu * sum_U) / D;
+        // candidates outside U that exceed t: a prefix of s_u, s_{u+1}, ...
+        int g = u;
+        while (g < n && sm_s[g] > t) ++g;
+        const int cj = g - u;
+        if (cj == j) break;
+        j = cj;
+        sum_M = (g > 0 ? sm_P[g - 1] : R(0)) - sum_U;
+      }
+    }
+    if (valid) {
+      const R D = kmu * kmu + up * static_cast<R>(j);
+      const R t = (up * sum_M - kmu * sum_U) / D;
+      const R hi = (static_cast<R>(j) * sum_U + kmu * sum_M) / D;
+      const R tt = hi + t;
+      const R max_M = (j > 0) ? s_u : -num<R>::inf();
+      if (max_M - eps <= tt && tt <= min_U + eps) {
+        bool ok = true;
+        if (u == k) ok = (t <= s_u + eps);
+        else if (j == 0) ok = (s_u - eps <= t);
+        pass = ok;
+      }
+      t_u = t; hi_u = hi; minU_u = min_U; j_u = j;
+    }
+  }
+  __syncwarp();
+  const unsigned found = __ballot_sync(kFullMask, pass);
+  if (found == 0u) return kFastNeedsFullRow;
+  const int w = __ffs(found) - 1;
+  const R t = __shfl_sync(kFullMask, t_u, w);
+  const R hi = __shfl_sync(kFullMask, hi_u, w);
+  const R min_U = __shfl_sync(kFullMask, minU_u, w);
+  const int j = __shfl_sync(kFullMask, j_u, w);
+  // all of M has to be among the candidates: the cut lies below every root by construction,
+  // and a root that reaches down to the cut is left to the general search
+  if (!(t > static_cast<R>(cut))) return kFastNeedsFullRow;
+  thr = make_thr(t, R(0), hi, w, j, min_U, (j > 0) ? t : min_U);
+  return kFastDone;
+}
+
 // ---- knapsack with lo = 0 (the simplex of include/sdca/prox/knapsack_eq.h) -----
 // When no entry reaches the upper bound, the solution has t >= max - rhs (the
 // largest entry alone contributes max - t <= rhs), so the support lies among the
@@ -836,7 +971,9 @@ fast_rows_kernel(const Data* a, Data* out, int m, long long n,
       st = fast_topk_simplex<R>(row, q.k, static_cast<R>(q.rhs), rho_used, tc, slots, counter,
                                 sorted_all[warp], lane, thr);
     } else if (PROX == kTopkCone || PROX == kTopkConeBiased) {
-      st = fast_topk_cone<R>(row, q.k, rho_used, tc, slots, counter, sorted_all[warp], lane, thr);
+      st = (PROX == kTopkConeBiased && rho_used > 0)
+               ? fast_topk_cone_biased<R>(row, q.k, rho_used, tc, slots, counter, sorted_all[warp], lane, thr)
+               : fast_topk_cone<R>(row, q.k, rho_used, tc, slots, counter, sorted_all[warp], lane, thr);
     }
     if (kKnap && kStaged) st = fast_knapsack_family<R, PROX>(row, q, slots, counter, lane, thr);
     if (std::is_same<Data, float>::value && PROX == kTopkEntropy) {

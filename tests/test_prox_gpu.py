@@ -79,6 +79,41 @@ def test_simplex_candidate_path_matches_reference(ref, cuda_lib, dtype, precisio
                 assert ok, (m, kw, err)
 
 
+@pytest.mark.parametrize("dtype,precision", [(np.float64, "double"), (np.float32, "double"),
+                                              (np.float32, "float")])
+def test_knapsack_family_and_biased_cone_candidate_paths(ref, cuda_lib, dtype, precision):
+    """Long rows of knapsack_eq / _le / _le_biased (cut from the largest lane maxima, the
+    clipped-sum test, the t >= rho * rhs test) and of the biased top-k cone (lane u solving
+    the size-u search on the sorted candidates) against the reference, on rows that take the
+    candidate paths and on rows that must fall back (bunched values, ties, tiny rho)."""
+    from libsdca_b200 import synth
+    rng = np.random.default_rng(stable_seed("candidate-paths", str(dtype), precision))
+    for m in (64, 200, 1000):
+        a = np.concatenate([regime(rng, 200, m, dtype, kind)
+                            for kind in ("normal", "pos", "neg", "mixed", "ties")] +
+                           [synth.topk_rows(rows=600, m=m, seed=int(rng.integers(1 << 30))).astype(dtype),
+                            (3 * synth.topk_rows(rows=200, m=m, seed=int(rng.integers(1 << 30)))).astype(dtype)])
+        cases = [("knapsack_le", dict(lo=0.0, hi=1.0, rhs=1.0)), ("knapsack_le", dict(lo=0.0, hi=0.3, rhs=2.0)),
+                 ("knapsack_le", dict(lo=0.0, hi=1.0, rhs=1e4)),
+                 ("knapsack_le_biased", dict(lo=0.0, hi=1.0, rhs=1.0, rho=1.0)),
+                 ("knapsack_le_biased", dict(lo=0.0, hi=1.0, rhs=1.0, rho=5.0)),
+                 ("knapsack_le_biased", dict(lo=0.0, hi=0.5, rhs=3.0, rho=0.0)),
+                 ("knapsack_eq", dict(lo=0.0, hi=1.0, rhs=1.0)), ("knapsack_eq", dict(lo=0.0, hi=10.0, rhs=4.0))]
+        for k in (1, 3, 5, 8):
+            for rho in (1e-6, 0.05, 1.0, 7.0):
+                cases.append(("topk_cone_biased", dict(k=k, rho=rho)))
+        for name, kw in cases:
+            x = run_dev(cuda_lib, name, a, precision=precision, **kw)
+            x_ref = ref.prox(name, a, result=precision, **kw)
+            tol = tolerance(dtype, precision, m)
+            if precision == "double":
+                err = scaled_error(x, x_ref, a).max()
+                assert err <= tol, (name, m, kw, err)
+            else:
+                ok, err = float_precision_ok(x, x_ref, ref.prox(name, a, result="double", **kw), a, tol)
+                assert ok, (name, m, kw, err)
+
+
 @pytest.mark.parametrize("name,kw", [("topk_simplex", dict(k=5, rhs=1.0)), ("topk_cone", dict(k=5))])
 @pytest.mark.parametrize("precision", ["double", "float"])
 def test_config2_topk_f32_with_ties(ref, cuda_lib, name, kw, precision):
