@@ -43,7 +43,8 @@ template <typename Data, typename R, int PROX, int NV> struct FastMinBlocks {
   // the simplex projection of short rows (config 1's 100 doubles) fits eight blocks as well
   static constexpr bool kShortSimplex = (PROX == kKnapsackEq) && NV == 2;
   static constexpr int value = kTopk ? ((kDouble && kSimplex) ? 7 : 8)
-                                     : ((kEntropic || kKnapStaged || kShortSimplex) ? 8 : (kDouble ? 5 : 6));
+                                     : ((kEntropic || kKnapStaged || kShortSimplex || PROX == kTwoSimplex)
+                                            ? 8 : (kDouble ? 5 : 6));
 };
 
 template <typename Data> struct VecOf;
@@ -103,6 +104,23 @@ struct RegRow {
         const Data* e = reinterpret_cast<const Data*>(&v[j]);
 #pragma unroll
         for (int c = 0; c < VN; ++c) f(e[c], base + c);
+      }
+    }
+  }
+
+  // like store, the map also gets the entry's index
+  template <typename F>
+  __device__ __forceinline__ void store_indexed(Data* __restrict__ g, int lane, F&& f) const {
+    Vec* gv = reinterpret_cast<Vec*>(g);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int vi = j * 32 + lane;
+      if (vi * VN < m) {
+        Vec o = v[j];
+        Data* e = reinterpret_cast<Data*>(&o);
+#pragma unroll
+        for (int c = 0; c < VN; ++c) e[c] = f(e[c], vi * VN + c);
+        __stcs(gv + vi, o);
       }
     }
   }
@@ -799,6 +817,43 @@ __device__ __forceinline__ FastStatus fast_knapsack_family(const RegRow<Data, NV
   return (thr.t >= rho * rhs - eps) ? kFastDone : kFastNeedsFullRow;
 }
 
+// two_simplex (include/sdca/prox/two_simplex.h:18-119): the first phase projects each block
+// onto the simplex of radius rhs on its own (:36-61) and is the answer when the two thresholds
+// satisfy t + s >= -eps; that is the candidate path of fast_knapsack_eq run on each block with
+// the other block's entries masked out.  Rows that need the joint second phase take the
+// general routine.
+template <typename R, typename Data, int NV>
+__device__ __forceinline__ FastStatus fast_two_simplex(const RegRow<Data, NV>& row, int p, R rhs,
+                                                       Data* slots, int* counter, int lane,
+                                                       R& t_a, R& t_b) {
+  if (!(rhs > 0)) return kFastNeedsFullRow;
+  const R eps = num<R>::eps() * max_(R(1), rhs);
+  constexpr int VN = RegRow<Data, NV>::VN;
+  R t[2];
+#pragma unroll
+  for (int block = 0; block < 2; ++block) {
+    RegRow<Data, NV> part;
+    part.m = row.m;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      part.v[j] = row.v[j];
+      Data* e = reinterpret_cast<Data*>(&part.v[j]);
+#pragma unroll
+      for (int c = 0; c < VN; ++c) {
+        const bool first = ((j * 32 + lane) * VN + c) < p;
+        if (first != (block == 0)) e[c] = -num<Data>::inf();
+      }
+    }
+    Thr<R> thr;
+    if (fast_knapsack_eq<R>(part, num<R>::inf(), rhs, slots, counter, lane, thr) != kFastDone)
+      return kFastNeedsFullRow;
+    t[block] = thr.t;
+  }
+  if (!(t[0] + t[1] >= -eps)) return kFastNeedsFullRow;
+  t_a = t[0]; t_b = t[1];
+  return kFastDone;
+}
+
 // ---- entropic projections of float rows --------------------------------------
 // For float data the stated accuracy of outputs and thresholds is 1e-5, so the
 // m exponentials of a log-sum-exp are evaluated in float (1e-7 each) and added
@@ -934,6 +989,13 @@ __device__ __noinline__ Thr<R> full_row_thresholds(const Data* buf, int m, const
   return compute_thresholds<R>(PROX, view, *q);
 }
 
+template <typename R, typename Data>
+__device__ __noinline__ void full_row_two_simplex(const Data* buf, int m, int p, R rhs, R& t_a, R& t_b) {
+  StridedRow<Data> ra(buf, p), rb(buf + p, m - p);
+  const ThrPair<R> pr = thr_two_simplex<R>(ra, rb, rhs);
+  t_a = pr.a.t; t_b = pr.b.t;
+}
+
 template <typename Data, typename R, int PROX, int NV>
 __global__ void __launch_bounds__(kFastThreads, FastMinBlocks<Data, R, PROX, NV>::value)
 fast_rows_kernel(const Data* a, Data* out, int m, long long n,
@@ -953,7 +1015,7 @@ fast_rows_kernel(const Data* a, Data* out, int m, long long n,
                           PROX == kTopkCone || PROX == kTopkConeBiased);
   // operators with a fast path that can decline a row
   constexpr bool kKnap = (PROX == kKnapsackEq || PROX == kKnapsackLe || PROX == kKnapsackLeBiased);
-  constexpr bool kStaged = kTopk || KnapsackStaged<PROX, NV>::value ||
+  constexpr bool kStaged = kTopk || KnapsackStaged<PROX, NV>::value || PROX == kTwoSimplex ||
                            (std::is_same<Data, float>::value && (PROX == kTopkEntropy || PROX == kEntropy));
   const R rho_used = (PROX == kTopkSimplexBiased || PROX == kTopkConeBiased) ? static_cast<R>(q.rho) : R(0);
   const TopkConsts<R> tc(q.k > 0 ? q.k : 1, static_cast<R>(q.rhs), rho_used);
@@ -976,6 +1038,9 @@ fast_rows_kernel(const Data* a, Data* out, int m, long long n,
                : fast_topk_cone<R>(row, q.k, rho_used, tc, slots, counter, sorted_all[warp], lane, thr);
     }
     if (kKnap && kStaged) st = fast_knapsack_family<R, PROX>(row, q, slots, counter, lane, thr);
+    R t_a = 0, t_b = 0;   // two_simplex: the thresholds of the two blocks
+    if (PROX == kTwoSimplex)
+      st = fast_two_simplex<R>(row, static_cast<int>(q.p), static_cast<R>(q.rhs), slots, counter, lane, t_a, t_b);
     if (std::is_same<Data, float>::value && PROX == kTopkEntropy) {
       st = fast_topk_entropy<R, NV>(reinterpret_cast<const RegRow<float, NV>&>(row), q.k,
                                     reinterpret_cast<float*>(slots), counter, lane, thr);
@@ -988,13 +1053,27 @@ fast_rows_kernel(const Data* a, Data* out, int m, long long n,
         if (kTwice) row.load(a + r * m, lane);
         row.for_each([&](Data x, int i) { stage[i] = x; });
         __syncwarp();
-        thr = full_row_thresholds<R, Data, PROX>(stage, m, &q);
+        if (PROX == kTwoSimplex)
+          full_row_two_simplex<R, Data>(stage, m, static_cast<int>(q.p), static_cast<R>(q.rhs), t_a, t_b);
+        else
+          thr = full_row_thresholds<R, Data, PROX>(stage, m, &q);
         __syncwarp();
       }
     } else {
       bool done = false;
       if (kKnap) done = fast_knapsack_family<R, PROX>(row, q, slots, counter, lane, thr) == kFastDone;
       if (!done) thr = compute_thresholds<R>(PROX, row, q);
+    }
+    if (PROX == kTwoSimplex) {
+      // x = clip(a - t, 0, rhs) on the first block, y = clip(b - s, 0, rhs) on the second
+      const Data ta = static_cast<Data>(t_a), tb = static_cast<Data>(t_b), top = static_cast<Data>(static_cast<R>(q.rhs));
+      const int p = static_cast<int>(q.p);
+      RegRow<Data, NV> again;
+      again.m = m;
+      again.load(a + r * m, lane);
+      again.store_indexed(out + r * m, lane,
+                          [&](Data x, int i) { return clip_(x - (i < p ? ta : tb), Data(0), top); });
+      continue;
     }
     Applier<Data> f(thr, prox_map(PROX), q.alpha);
     if (kTwice) {
@@ -1019,7 +1098,7 @@ int launch_fast(const Data* a, Data* out, int m, long long n, const ProxParams& 
                           PROX == kTopkCone || PROX == kTopkConeBiased) ||
                          (std::is_same<Data, float>::value && (PROX == kTopkEntropy || PROX == kEntropy));
   const int m_pad = (m + 15) & ~15;
-  const size_t smem = (kTopk || KnapsackStaged<PROX, NV>::value)
+  const size_t smem = (kTopk || KnapsackStaged<PROX, NV>::value || PROX == kTwoSimplex)
                           ? static_cast<size_t>(kFastThreads / 32) * m_pad * sizeof(Data) : 0;
   int per_sm = 0;
   SDCAB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFastThreads, smem));
@@ -1060,6 +1139,7 @@ int launch_fast_rows(int prox, const Data* a, Data* out, int m, long long n,
     case kKnapsackEq: return launch_fast_nv<Data, R, kKnapsackEq>(a, out, m, n, q, stream);
     case kKnapsackLe: return launch_fast_nv<Data, R, kKnapsackLe>(a, out, m, n, q, stream);
     case kKnapsackLeBiased: return launch_fast_nv<Data, R, kKnapsackLeBiased>(a, out, m, n, q, stream);
+    case kTwoSimplex: return launch_fast_nv<Data, R, kTwoSimplex>(a, out, m, n, q, stream);
     case kEntropy: return launch_fast_nv<Data, R, kEntropy>(a, out, m, n, q, stream);
     case kTopkEntropy: return launch_fast_nv<Data, R, kTopkEntropy>(a, out, m, n, q, stream);
     default: break;

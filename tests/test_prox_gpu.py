@@ -85,7 +85,8 @@ def test_knapsack_family_and_biased_cone_candidate_paths(ref, cuda_lib, dtype, p
     """Long rows of knapsack_eq / _le / _le_biased (cut from the largest lane maxima, the
     clipped-sum test, the t >= rho * rhs test) and of the biased top-k cone (lane u solving
     the size-u search on the sorted candidates) against the reference, on rows that take the
-    candidate paths and on rows that must fall back (bunched values, ties, tiny rho)."""
+    candidate paths and on rows that must fall back (bunched values, ties, tiny rho); and
+    two_simplex, whose first phase is the simplex projection of each block."""
     from libsdca_b200 import synth
     rng = np.random.default_rng(stable_seed("candidate-paths", str(dtype), precision))
     for m in (64, 200, 1000):
@@ -102,6 +103,9 @@ def test_knapsack_family_and_biased_cone_candidate_paths(ref, cuda_lib, dtype, p
         for k in (1, 3, 5, 8):
             for rho in (1e-6, 0.05, 1.0, 7.0):
                 cases.append(("topk_cone_biased", dict(k=k, rho=rho)))
+        for p_ in (1, m // 4, m // 2 + 1, m - 1):
+            for rhs in (0.2, 1.0, 50.0):
+                cases.append(("two_simplex", dict(p=p_, rhs=rhs)))
         for name, kw in cases:
             x = run_dev(cuda_lib, name, a, precision=precision, **kw)
             x_ref = ref.prox(name, a, result=precision, **kw)
