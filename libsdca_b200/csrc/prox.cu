@@ -165,9 +165,11 @@ int launch_two_simplex_sort(const Data* a, Data* out, int m, long long n, const 
   const int warps = kSortThreads / 32;
   const size_t smem = static_cast<size_t>(warps) * (pa + pb) * sizeof(Data);
   // the sorted copies of both blocks live in shared memory: rows beyond that are refused
-  if (smem > info.smem_optin) return SDCAB_ERR_TOO_LARGE;
+  if (smem + 2048 > info.smem_optin) return SDCAB_ERR_TOO_LARGE;
   auto kernel = two_simplex_sort_kernel<Data, R>;
-  if (smem > 48 * 1024)
+  // the kernel also has about 1 KB of static shared memory, which counts towards the 48 KB
+  // that need no opt-in
+  if (smem + 2048 > 48 * 1024)
     SDCAB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(smem)));
   const long long want = (n + warps - 1) / warps;

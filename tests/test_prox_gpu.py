@@ -106,15 +106,21 @@ def test_knapsack_family_and_biased_cone_candidate_paths(ref, cuda_lib, dtype, p
         for p_ in (1, m // 4, m // 2 + 1, m - 1):
             for rhs in (0.2, 1.0, 50.0):
                 cases.append(("two_simplex", dict(p=p_, rhs=rhs)))
+        cases.append(("two_simplex_sort", dict(p=m // 2, rhs=1.0)))
+        cases.append(("two_simplex_sort", dict(p=m // 3, rhs=30.0)))
         for name, kw in cases:
-            x = run_dev(cuda_lib, name, a, precision=precision, **kw)
-            x_ref = ref.prox(name, a, result=precision, **kw)
+            rows = a
+            if name == "two_simplex_sort":
+                # rows on which the reference's walk stays inside its arrays
+                rows = a[two_simplex_sort_defined(ref, a, result=precision, **kw)]
+            x = run_dev(cuda_lib, name, rows, precision=precision, **kw)
+            x_ref = ref.prox(name, rows, result=precision, **kw)
             tol = tolerance(dtype, precision, m)
             if precision == "double":
-                err = scaled_error(x, x_ref, a).max()
+                err = scaled_error(x, x_ref, rows).max()
                 assert err <= tol, (name, m, kw, err)
             else:
-                ok, err = float_precision_ok(x, x_ref, ref.prox(name, a, result="double", **kw), a, tol)
+                ok, err = float_precision_ok(x, x_ref, ref.prox(name, rows, result="double", **kw), rows, tol)
                 assert ok, (name, m, kw, err)
 
 
