@@ -105,8 +105,8 @@ gemm_f64_pipe_kernel(const double* __restrict__ A, const double* __restrict__ B,
   constexpr int BK_PAIRS = B_KMAJOR ? BN * (kBK / 2) : kBK * (BN / 2);
   constexpr int B_PER = (BK_PAIRS + NT - 1) / NT;
   const double* b_rows[B_KMAJOR ? B_PER : 1];
-  (void)b_ok;
-  if (B_KMAJOR) {
+  (void)b_ok; (void)b_rows;
+  if constexpr (B_KMAJOR) {
 #pragma unroll
     for (int it = 0; it < B_PER; ++it) {
       const int idx = tid + it * NT;
@@ -130,7 +130,7 @@ gemm_f64_pipe_kernel(const double* __restrict__ A, const double* __restrict__ B,
       const int valid = ((a_ok >> it) & 1u) ? (left >= 2 ? 2 : (left > 0 ? left : 0)) : 0;
       copy_pair(smem_addr(As + r * kRowK + kk), a_rows[it] + k0 + kk, A, valid, a_vec);
     }
-    if (B_KMAJOR) {
+    if constexpr (B_KMAJOR) {
 #pragma unroll
       for (int it = 0; it < B_PER; ++it) {
         const int idx = tid + it * NT;
