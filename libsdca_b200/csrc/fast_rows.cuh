@@ -789,32 +789,26 @@ __device__ __forceinline__ FastStatus fast_knapsack_le(const RegRow<Data, NV>& r
   R sum_mid = 0;
   constexpr bool kFloatSums = std::is_same<Data, float>::value && std::is_same<R, double>::value;
   if (kFloatSums) {
-    // Float data, double thresholds: the sum only decides which branch is taken, so it is
-    // formed per lane in float (four chains) and across lanes in R; a sum within 1e-4 of
-    // rhs is not clear-cut and is left to the general routine.  x >= hi is tested against the
-    // smallest float not below hi, which is the same test on float data.
-    const float hi_up = __double2float_ru(static_cast<double>(hi));
+    // Float data, double thresholds: the sum of the row clipped to [0, hi] only decides which
+    // branch is taken, so it is formed per lane in float (four chains, hi rounded to float)
+    // and across lanes in R; a sum within 1e-4 of rhs is not clear-cut and is left to the
+    // general routine.  The set sizes are not counted here: this path only feeds the map
+    // x -> clip(x - t, 0, hi), which does not use them.
+    const float hif = static_cast<float>(hi);
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    int chi[4] = {0, 0, 0, 0}, cmid[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int jv = 0; jv < NV; ++jv) {
       const float* e = reinterpret_cast<const float*>(&row.v[jv]);   // padding holds -inf
 #pragma unroll
-      for (int cc = 0; cc < RegRow<Data, NV>::VN; ++cc) {
-        const float x = static_cast<float>(e[cc]);
-        const bool at_hi = x >= hi_up;
-        const bool mid = !at_hi && x > 0.0f;
-        chi[cc & 3] += at_hi ? 1 : 0;
-        cmid[cc & 3] += mid ? 1 : 0;
-        acc[cc & 3] += mid ? x : 0.0f;
-      }
+      for (int cc = 0; cc < RegRow<Data, NV>::VN; ++cc)
+        acc[cc & 3] += fminf(fmaxf(static_cast<float>(e[cc]), 0.0f), hif);
     }
-    n_hi = warp_sum((chi[0] + chi[1]) + (chi[2] + chi[3]));
-    n_mid = warp_sum((cmid[0] + cmid[1]) + (cmid[2] + cmid[3]));
-    sum_mid = warp_sum((static_cast<R>(acc[0]) + static_cast<R>(acc[1])) +
-                       (static_cast<R>(acc[2]) + static_cast<R>(acc[3])));
-    const R s_est = sum_mid + hi * static_cast<R>(n_hi);
+    const R s_est = warp_sum((static_cast<R>(acc[0]) + static_cast<R>(acc[1])) +
+                             (static_cast<R>(acc[2]) + static_cast<R>(acc[3])));
     if (!(abs_(s_est - rhs) > R(1e-4) * max_(abs_(s_est), abs_(rhs)))) return kFastNeedsFullRow;
+    if (s_est > rhs) return fast_knapsack_eq<R>(row, hi, rhs, slots, counter, lane, thr);
+    thr = make_thr(R(0), R(0), hi, 0, 0, hi, R(0));
+    return kFastDone;
   } else {
     row.for_each([&](Data xd, int) {
       const R x = static_cast<R>(xd);
