@@ -694,6 +694,79 @@ def fit_config(args, rank, world, local_rank):
     print(json.dumps(out))
 
 
+FIT_SWEEP = (("l2_topk_hinge", 4, False), ("l2_topk_hinge_smooth", 5, False), ("l2_hinge_topk", 2, False),
+             ("l2_hinge_topk_smooth", 3, False), ("l2_entropy", 0, False), ("l2_entropy_topk", 1, False),
+             ("l2_multilabel_hinge", 6, True), ("l2_multilabel_hinge_smooth", 7, True),
+             ("l2_multilabel_entropy", 8, True))
+
+
+def fit_sweep_config(args, rank, world, local_rank):
+    """`--config 8`: the update steps of all nine objectives (update_dual_variables of
+    include/sdca/solver/objective/*.h), not a configuration of the benchmark definition:
+    three epochs of each on class-conditional Gaussian blobs, N = 16384 (or --rows), m = 100,
+    float64, as a Gram matrix (kernel input) and as d = 256 features; microseconds per step
+    from the device time of the update steps, the reference's solver on 2048 examples beside it."""
+    import torch
+    import libsdca_b200 as sd
+    from oracle import refapi
+    if rank != 0:
+        return
+    torch.cuda.set_device(local_rank)
+    n = args.rows if args.rows != FULL_ROWS else 16384
+    m, d, k, epochs = 100, 256, 3, 3
+    rng = np.random.default_rng(11)
+    means = rng.standard_normal((m, d))
+    labels = rng.integers(0, m, n).astype(np.int64)
+    X = (means[labels] + 1.5 * rng.standard_normal((n, d))) / np.sqrt(d)
+    extra = rng.integers(0, m, (n, 2))
+    ml_lists = [sorted(set([int(labels[i])] + [int(e) for e in extra[i][: int(rng.integers(0, 3))]])) for i in range(n)]
+    ml_labels = np.array([c_ for l in ml_lists for c_ in l], dtype=np.int64)
+    ml_offsets = np.concatenate([[0], np.cumsum([len(l) for l in ml_lists])]).astype(np.int64)
+    tX = torch.from_numpy(X).cuda()
+    tK = tX @ tX.T
+    have_ref = (not args.no_cpu_baseline) and refapi.have_reference()
+    n_ref = min(n, 2048)
+    per = {}
+    for name, oid, ml in FIT_SWEEP:
+        lab = torch.from_numpy(ml_labels if ml else labels).cuda()
+        off = torch.from_numpy(ml_offsets).cuda() if ml else None
+        row = {}
+        for kernel in (True, False):
+            A = torch.zeros(n, m, device="cuda", dtype=torch.float64)
+            W = None if kernel else torch.zeros(m, d, device="cuda", dtype=torch.float64)
+            r = sd.fit_(oid, tK if kernel else tX, lab, A, W=W, kernel=kernel, offsets=off, c=1.0, gamma=1.0,
+                        k=k, max_epoch=epochs, eval_epoch=epochs, epsilon=1e-12)
+            torch.cuda.synchronize()
+            last = r["history"][-1]
+            row["kernel" if kernel else "features"] = {
+                "us_per_step": 1e6 * r["solve_seconds"] / (n * max(1, r["epoch"])), "epochs": r["epoch"],
+                "seconds_per_evaluation": r["eval_seconds"] / max(1, r["num_evals"]),
+                "relative_gap": last["relative_gap"], "status": r["status"]}
+        if have_ref:
+            nl = ml_offsets[n_ref]
+            A_ref = np.zeros((n_ref, m)); W_ref = np.zeros((m, d))
+            t0 = time.perf_counter()
+            rr = refapi.reference().fit(name, X[:n_ref], A_ref, (ml_labels[:nl] if ml else labels[:n_ref]), W=W_ref,
+                                        offsets=(ml_offsets[: n_ref + 1] if ml else None), c=1.0, gamma=1.0, k=k,
+                                        max_epoch=epochs, eval_epoch=epochs, epsilon=1e-12)
+            dt = time.perf_counter() - t0
+            row["reference_features"] = {"us_per_step": 1e6 * dt / (n_ref * max(1, rr["epoch"])), "examples": n_ref,
+                                         "cores": 1, "note": "whole call including its one evaluation"}
+        per[name] = row
+    slow = max(per, key=lambda q: per[q]["kernel"]["us_per_step"])
+    print(json.dumps({
+        "metric": "SDCA update microseconds per step, all objectives", "value": per[slow]["kernel"]["us_per_step"],
+        "unit": "us/step", "n_gpus": 1, "steps": epochs, "warmup": 0, "ms_per_step": None,
+        "higher_is_better": False, "scaling": "replicas only", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": "fit sweep: %d examples, m=%d, d=%d, k=%d, c=1, gamma=1, float64, %d epochs per "
+                               "objective, kernel and feature input" % (n, m, d, k, epochs)},
+        "roofline": {"bound": "latency (a chain of dependent steps)", "achieved": per[slow]["kernel"]["us_per_step"],
+                     "peak": None, "unit": "us/step", "frac": None, "traffic": None, "kernel": slow,
+                     "per_objective": per},
+        "gpu_launches": None}))
+
+
 def fit_cpu_baseline(n_small, sd, torch):
     """The reference's solver on a bounded problem of the same family (the full size
     would take it hours: an epoch reads A once per example, N^2 m multiply-adds), and
@@ -739,7 +812,7 @@ def main():
     ap.add_argument("--max-epoch", type=int, default=100, help="config 5: epoch limit")
     ap.add_argument("--cpu-fit-examples", type=int, default=4000,
                     help="config 5: size of the problem the reference's solver is timed on")
-    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5, 6, 7],
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5, 6, 7, 8],
                     help="benchmark configuration; 2 (default) is the headline")
     ap.add_argument("--no-gap", action="store_true",
                     help="leave the duality-gap evaluation (config 4) out of the default line")
@@ -765,6 +838,8 @@ def main():
         return other_prox_config(args, rank, world, local_rank)
     if args.config == 4:
         return gap_config(args, rank, world, local_rank)
+    if args.config == 8:
+        return fit_sweep_config(args, rank, world, local_rank)
     if args.config == 5:
         return fit_config(args, rank, world, local_rank)
 
