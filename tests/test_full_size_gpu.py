@@ -66,6 +66,41 @@ def test_config2_topk_262144_by_1000_f32(cuda_lib, name):
     assert (np.abs(x[idx].cpu().numpy().astype(np.float64) - ref) / scale).max() <= 1e-5
 
 
+@pytest.mark.parametrize("name,kw", [("knapsack", dict(lo=0.0, hi=1.0, rhs=1.0)),
+                                     ("knapsack_le", dict(lo=0.0, hi=1.0, rhs=1.0)),
+                                     ("knapsack_le_biased", dict(lo=0.0, hi=1.0, rhs=1.0, rho=1.0)),
+                                     ("topk_cone_biased", dict(k=5, rho=1.0)),
+                                     ("two_simplex", dict(p=500, rhs=1.0))])
+def test_operator_sweep_131072_by_1000_f32(cuda_lib, name, kw):
+    """The operators of the sweep (bench config 6) at its size: feasibility of every row,
+    idempotence where the operator is a Euclidean projection, run-to-run bit equality, and a
+    sample of rows against the reference."""
+    import torch
+    from libsdca_b200 import synth
+    a = torch.from_numpy(synth.topk_rows(rows=131072)).cuda()
+    x = cuda_lib.prox(a, name, **kw)
+    assert x.shape == a.shape and bool(torch.isfinite(x).all())
+    assert float(x.min()) >= 0.0
+    total = x.double().sum(dim=1)
+    if name == "knapsack":
+        assert float((total - 1).abs().max()) <= 1e-5 and float(x.max()) <= 1.0
+    elif name.startswith("knapsack_le"):
+        assert float(total.max()) <= 1.0 + 1e-5 and float(x.max()) <= 1.0
+    elif name == "topk_cone_biased":
+        assert float((x.double().max(dim=1).values - total / kw["k"]).max()) <= 1e-6
+    elif name == "two_simplex":
+        sa, sb = x[:, :500].double().sum(dim=1), x[:, 500:].double().sum(dim=1)
+        assert float((sa - sb).abs().max()) <= 1e-5 and float(sa.max()) <= 1.0 + 1e-5
+    if name in ("knapsack", "knapsack_le", "two_simplex"):
+        again = cuda_lib.prox(x, name, **kw)
+        assert float((again - x).abs().max()) <= 2e-6
+    assert torch.equal(cuda_lib.prox(a, name, **kw), x)
+    idx, rows = sample_rows(a, 2048, 6)
+    ref = checker().prox(name, rows, **kw)
+    scale = np.maximum(1, np.abs(rows).max(axis=1, keepdims=True))
+    assert (np.abs(x[idx].cpu().numpy().astype(np.float64) - ref) / scale).max() <= 1e-5
+
+
 @pytest.mark.parametrize("k", [1, 10])
 def test_config3_topk_entropy_1048576_by_200_f32(cuda_lib, k):
     import torch
