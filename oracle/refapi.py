@@ -220,6 +220,20 @@ class Restatement(_Backend):
     prefix = "sdca_oracle_"
     path = os.path.join(HERE, "libsdca_oracle.so")
 
+    def two_simplex_sort_defined(self, a, p=1, rhs=1.0, result="double", **_):
+        """Rows on which the reference's two_simplex_sort stays inside its arrays
+        (prox/two_simplex_sort.h:84-97): worked out by the restatement's memory-safe walk,
+        never by running the reference on a row that would read past a block."""
+        a = np.ascontiguousarray(a)
+        n, m = a.shape
+        flags = np.zeros(n, dtype=np.int32)
+        rc = self._fn("two_simplex_sort_defined")(
+            _dtype_code(a.dtype), _dtype_code(np.float64 if result == "double" else np.float32),
+            _ptr(a), C.c_int64(m), C.c_int64(n), C.c_int64(int(p)), C.c_double(float(rhs)), _ptr(flags))
+        if rc != 0:
+            raise RuntimeError("two_simplex_sort_defined -> %d" % rc)
+        return flags.astype(bool)
+
 
 _cache = {}
 

@@ -186,6 +186,18 @@ int sdca_oracle_thresholds(const char* prox, int dtype, int result, const void* 
   return -2;
 }
 
+/* Rows on which the reference's two_simplex_sort (prox/two_simplex_sort.h:84-97) stays inside its
+ * arrays; on the others it reads past the end of a block and has no defined result. */
+int sdca_oracle_two_simplex_sort_defined(int dtype, int result, const void* a, int64_t m, int64_t n,
+                                         int64_t p, double rhs, int32_t* defined) {
+  if (p < 1 || p > m - 1) return -3;
+  if (dtype == 0 && result == 0) return two_simplex_sort_defined_ff((const float*)a, m, n, p, (float)rhs, defined);
+  if (dtype == 0 && result == 1) return two_simplex_sort_defined_fd((const float*)a, m, n, p, rhs, defined);
+  if (dtype == 1 && result == 0) return two_simplex_sort_defined_df((const double*)a, m, n, p, (float)rhs, defined);
+  if (dtype == 1 && result == 1) return two_simplex_sort_defined_dd((const double*)a, m, n, p, rhs, defined);
+  return -2;
+}
+
 int sdca_oracle_eval(const oracle_eval_args* a, int dtype, int result, double* out, double* acc) {
   if (dtype == 0 && result == 0) return eval_ff(a, out, acc);
   if (dtype == 0 && result == 1) return eval_fd(a, out, acc);

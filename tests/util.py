@@ -129,9 +129,13 @@ def two_simplex_sort_defined(ref, a, p=1, **kw):
     """Rows on which the reference's two_simplex_sort is well defined.  When one block is
     used up and rounding leaves the grid value of its pseudo point a few ulps below rhs,
     the reference's walk (prox/two_simplex_sort.h:84-97) steps past the end of the block
-    and reads whatever follows in memory; it then reports more active entries than the
-    block has.  Those rows have no reference value and are left out of comparisons."""
-    thr = ref.thresholds("two_simplex_sort", a, p=p, **kw)
-    nm = thr["num_mid"].reshape(-1, 2)
-    m = a.shape[1]
-    return (nm[:, 0] <= p) & (nm[:, 1] <= m - p)
+    and reads whatever follows in memory (at the end of an allocation that is a crash).
+    Those rows have no reference value and are left out of comparisons; they are found by
+    the restatement's memory-safe walk, so the reference itself never runs on them (`ref`
+    is unused and kept for the callers' signature)."""
+    from oracle import build_oracle, refapi
+    import os
+    if not os.path.exists(refapi.Restatement.path):
+        build_oracle.build_restatement()
+    return refapi.restatement().two_simplex_sort_defined(
+        a, p=p, rhs=kw.get("rhs", 1.0), result=kw.get("result", "double"))
