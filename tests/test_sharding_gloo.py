@@ -70,20 +70,20 @@ def _worker(rank, world, port, kernel, out_dir):
 @pytest.mark.parametrize("kernel", [False, True])
 def test_two_rank_sums_equal_unsharded(tmp_path, kernel):
     import torch.multiprocessing as mp
-    # A rank writes its verdict before it leaves the process group; a rendezvous that loses
+    # A rank writes its result before it leaves the process group; a rendezvous that loses
     # the race for its port, or a worker that dies while the interpreter shuts down after
-    # the verdict is on disk, is retried once with a new port.
+    # the result is on disk, is retried once with a new port.
     failure = None
     for attempt in range(2):
         out = tmp_path / ("attempt%d" % attempt)
         out.mkdir()
         try:
             mp.spawn(_worker, args=(2, _free_port(), kernel, str(out)), nprocs=2, join=True)
-        except Exception as e:          # noqa: BLE001 - the verdict files decide
+        except Exception as e:          # noqa: BLE001 - the result files decide
             failure = e
-        verdicts = [(out / ("rank%d.txt" % r)) for r in range(2)]
-        if all(v.exists() for v in verdicts):
-            for v in verdicts:
+        results = [(out / ("rank%d.txt" % r)) for r in range(2)]
+        if all(v.exists() for v in results):
+            for v in results:
                 assert v.read_text() == "ok"
             return
-    raise AssertionError("no verdict from the ranks: %r" % (failure,))
+    raise AssertionError("no result from the ranks: %r" % (failure,))
